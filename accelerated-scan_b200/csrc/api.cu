@@ -1,0 +1,259 @@
+// extern "C" entry points of the library (declared in include/ascan_b200.h):
+// argument validation, planning, kernel dispatch, launch-error reporting.
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <mutex>
+#include <set>
+#include <utility>
+
+#include "../../include/ascan_b200.h"
+#include "planner.h"
+#include "rowstream.cuh"
+
+namespace ascan {
+
+static int cached_sm_count(int *out) {
+    static int counts[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return ASCAN_ERR_DEVICE;
+    if (dev >= 0 && dev < 64 && counts[dev] > 0) {
+        *out = counts[dev];
+        return ASCAN_OK;
+    }
+    int n = 0, major = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return ASCAN_ERR_DEVICE;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return ASCAN_ERR_DEVICE;
+    if (major != 10 || n < 1) return ASCAN_ERR_DEVICE;   // built for sm_100a only
+    if (dev >= 0 && dev < 64) counts[dev] = n;
+    *out = n;
+    return ASCAN_OK;
+}
+
+// Opt in to the large dynamic shared-memory carve-out once per (kernel, device).
+static int ensure_smem(const void *fn, size_t bytes) {
+    static std::mutex mu;
+    static std::set<std::pair<const void *, int>> done;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return ASCAN_ERR_DEVICE;
+    std::lock_guard<std::mutex> lock(mu);
+    if (done.count({fn, dev})) return ASCAN_OK;
+    (void)bytes;
+    if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemPerCta) != cudaSuccess) {
+        cudaGetLastError();
+        return ASCAN_ERR_LAUNCH;
+    }
+    done.insert({fn, dev});
+    return ASCAN_OK;
+}
+
+template <class TR, int NCH, int KIND, bool REVERSE, bool BULK>
+static int launch_one(const RowStreamParams &p, const ascan_plan &pl, cudaStream_t stream) {
+    auto kfn = rowstream_kernel<TR, NCH, KIND, REVERSE, BULK>;
+    int rc = ensure_smem(reinterpret_cast<const void *>(kfn), pl.smem_bytes);
+    if (rc != ASCAN_OK) return rc;
+    kfn<<<pl.grid, pl.warps_per_cta * 32, pl.smem_bytes, stream>>>(p);
+    return cudaGetLastError() == cudaSuccess ? ASCAN_OK : ASCAN_ERR_LAUNCH;
+}
+
+template <class TR, int NCH, int KIND, bool REVERSE>
+static int launch_loader(const RowStreamParams &p, const ascan_plan &pl, cudaStream_t stream) {
+    return pl.loader == 0 ? launch_one<TR, NCH, KIND, REVERSE, true>(p, pl, stream)
+                          : launch_one<TR, NCH, KIND, REVERSE, false>(p, pl, stream);
+}
+
+template <class TR, int KIND, bool REVERSE>
+static int launch_nch(const RowStreamParams &p, const ascan_plan &pl, cudaStream_t stream) {
+    switch (pl.chunks_per_lane) {
+        case 3: return launch_loader<TR, 3, KIND, REVERSE>(p, pl, stream);
+        case 5: return launch_loader<TR, 5, KIND, REVERSE>(p, pl, stream);
+        default: return ASCAN_ERR_UNSUPPORTED;
+    }
+}
+
+template <int KIND, bool REVERSE>
+static int launch_dtype(int dtype, const RowStreamParams &p, const ascan_plan &pl, cudaStream_t stream) {
+    switch (dtype) {
+        case ASCAN_F32: return launch_nch<TraitsF32, KIND, REVERSE>(p, pl, stream);
+        case ASCAN_BF16: return launch_nch<TraitsBF16, KIND, REVERSE>(p, pl, stream);
+        case ASCAN_F16: return launch_nch<TraitsF16, KIND, REVERSE>(p, pl, stream);
+        case ASCAN_C64: return launch_nch<TraitsC64, KIND, REVERSE>(p, pl, stream);
+        default: return ASCAN_ERR_INVALID_ARG;
+    }
+}
+
+static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static int plan_for(int64_t rows, int64_t seqlen, int dtype, int kind, bool aligned, ascan_plan *pl) {
+    PlanInput in;
+    in.rows = rows;
+    in.seqlen = seqlen;
+    in.dtype = dtype;
+    in.kind = kind;
+    in.aligned = aligned;
+    int rc = cached_sm_count(&in.sm_count);
+    if (rc != ASCAN_OK) return rc;
+    return make_plan(in, pl);
+}
+
+static uint32_t *status_word(void *ws, size_t ws_bytes) {
+    if (!ws || ws_bytes < 16 || (reinterpret_cast<uintptr_t>(ws) & 3u)) return nullptr;
+    return static_cast<uint32_t *>(ws);
+}
+
+}  // namespace ascan
+
+using namespace ascan;
+
+extern "C" {
+
+int ascan_version(void) { return 100; }   // 0.1.0
+
+const char *ascan_strerror(int status) {
+    switch (status) {
+        case ASCAN_OK: return "success";
+        case ASCAN_ERR_INVALID_ARG: return "invalid argument";
+        case ASCAN_ERR_UNSUPPORTED: return "unsupported combination";
+        case ASCAN_ERR_LAUNCH: return "CUDA launch failed";
+        case ASCAN_ERR_TIMEOUT: return "a bounded device-side wait expired";
+        case ASCAN_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+        case ASCAN_ERR_DEVICE: return "no usable sm_100 device";
+        default: return "unknown status";
+    }
+}
+
+int ascan_forward(const void *gates, const void *tokens, void *out, int64_t rows, int64_t seqlen, int dtype,
+                  int reverse, const void *carry_in, void *ws, size_t ws_bytes, void *stream) {
+    if (rows < 0 || seqlen < 1 || dtype_size(dtype) == 0) return ASCAN_ERR_INVALID_ARG;
+    if (rows == 0) return ASCAN_OK;
+    if (!gates || !tokens || !out) return ASCAN_ERR_INVALID_ARG;
+    ascan_plan pl;
+    const bool al = aligned16(gates) && aligned16(tokens) && aligned16(out);
+    int rc = plan_for(rows, seqlen, dtype, ASCAN_KIND_FORWARD, al, &pl);
+    if (rc != ASCAN_OK) return rc;
+    RowStreamParams p = {};
+    p.in0 = gates;
+    p.in1 = tokens;
+    p.out0 = out;
+    p.carry_in = carry_in;
+    p.rows = rows;
+    p.T = seqlen;
+    p.rows_per_item = pl.rows_per_item;
+    p.items = pl.items;
+    p.status = status_word(ws, ws_bytes);
+    p.stages = pl.stages;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return reverse ? launch_dtype<K_SCAN, true>(dtype, p, pl, st) : launch_dtype<K_SCAN, false>(dtype, p, pl, st);
+}
+
+int ascan_backward(const void *gates, const void *states, const void *grad_out, void *d_gates, void *d_tokens,
+                   int64_t rows, int64_t seqlen, int dtype, const void *carry_in, const void *halo_gate_right,
+                   const void *halo_state_left, void *ws, size_t ws_bytes, void *stream) {
+    if (rows < 0 || seqlen < 1 || dtype_size(dtype) == 0) return ASCAN_ERR_INVALID_ARG;
+    if (rows == 0) return ASCAN_OK;
+    if (!gates || !states || !grad_out || !d_gates || !d_tokens) return ASCAN_ERR_INVALID_ARG;
+    if (carry_in && !halo_gate_right) return ASCAN_ERR_INVALID_ARG;
+    ascan_plan pl;
+    const bool al = aligned16(gates) && aligned16(states) && aligned16(grad_out) && aligned16(d_gates) &&
+                    aligned16(d_tokens);
+    int rc = plan_for(rows, seqlen, dtype, ASCAN_KIND_BACKWARD, al, &pl);
+    if (rc != ASCAN_OK) return rc;
+    RowStreamParams p = {};
+    p.in0 = gates;
+    p.in1 = grad_out;
+    p.in2 = states;
+    p.out0 = d_tokens;
+    p.out1 = d_gates;
+    p.carry_in = carry_in;
+    p.halo_gate = halo_gate_right;
+    p.halo_state = halo_state_left;
+    p.rows = rows;
+    p.T = seqlen;
+    p.rows_per_item = pl.rows_per_item;
+    p.items = pl.items;
+    p.status = status_word(ws, ws_bytes);
+    p.stages = pl.stages;
+    return launch_dtype<K_BWD, true>(dtype, p, pl, static_cast<cudaStream_t>(stream));
+}
+
+int ascan_reduce_forward(const void *gates, const void *tokens, void *carry_out, int64_t rows, int64_t seqlen,
+                         int dtype, void *ws, size_t ws_bytes, void *stream) {
+    if (rows < 0 || seqlen < 1 || dtype_size(dtype) == 0) return ASCAN_ERR_INVALID_ARG;
+    if (rows == 0) return ASCAN_OK;
+    if (!gates || !tokens || !carry_out) return ASCAN_ERR_INVALID_ARG;
+    ascan_plan pl;
+    const bool al = aligned16(gates) && aligned16(tokens);
+    int rc = plan_for(rows, seqlen, dtype, ASCAN_KIND_REDUCE_FORWARD, al, &pl);
+    if (rc != ASCAN_OK) return rc;
+    RowStreamParams p = {};
+    p.in0 = gates;
+    p.in1 = tokens;
+    p.carry_out = carry_out;
+    p.rows = rows;
+    p.T = seqlen;
+    p.rows_per_item = pl.rows_per_item;
+    p.items = pl.items;
+    p.status = status_word(ws, ws_bytes);
+    p.stages = pl.stages;
+    return launch_dtype<K_REDUCE, false>(dtype, p, pl, static_cast<cudaStream_t>(stream));
+}
+
+int ascan_reduce_backward(const void *gates, const void *grad_out, const void *halo_gate_right, void *carry_out,
+                          int64_t rows, int64_t seqlen, int dtype, void *ws, size_t ws_bytes, void *stream) {
+    if (rows < 0 || seqlen < 1 || dtype_size(dtype) == 0) return ASCAN_ERR_INVALID_ARG;
+    if (rows == 0) return ASCAN_OK;
+    if (!gates || !grad_out || !carry_out) return ASCAN_ERR_INVALID_ARG;
+    ascan_plan pl;
+    const bool al = aligned16(gates) && aligned16(grad_out);
+    int rc = plan_for(rows, seqlen, dtype, ASCAN_KIND_REDUCE_BACKWARD, al, &pl);
+    if (rc != ASCAN_OK) return rc;
+    RowStreamParams p = {};
+    p.in0 = gates;
+    p.in1 = grad_out;
+    p.halo_gate = halo_gate_right;
+    p.carry_out = carry_out;
+    p.rows = rows;
+    p.T = seqlen;
+    p.rows_per_item = pl.rows_per_item;
+    p.items = pl.items;
+    p.status = status_word(ws, ws_bytes);
+    p.stages = pl.stages;
+    return launch_dtype<K_REDUCE_BWD, true>(dtype, p, pl, static_cast<cudaStream_t>(stream));
+}
+
+size_t ascan_workspace_bytes(int64_t rows, int64_t seqlen, int dtype, int kind) {
+    (void)rows;
+    (void)seqlen;
+    (void)dtype;
+    (void)kind;
+    return 0;
+}
+
+int ascan_plan_describe(int64_t rows, int64_t seqlen, int dtype, int kind, int aligned, int sm_count,
+                        ascan_plan *plan) {
+    PlanInput in;
+    in.rows = rows;
+    in.seqlen = seqlen;
+    in.dtype = dtype;
+    in.kind = kind;
+    in.aligned = aligned != 0;
+    in.sm_count = sm_count;
+    if (sm_count <= 0) {
+        int rc = cached_sm_count(&in.sm_count);
+        if (rc != ASCAN_OK) return rc;
+    }
+    return make_plan(in, plan);
+}
+
+int ascan_check(void *ws, void *stream) {
+    if (!ws) return ASCAN_ERR_INVALID_ARG;
+    uint32_t host[4] = {0, 0, 0, 0};
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (cudaMemcpyAsync(host, ws, sizeof(host), cudaMemcpyDeviceToHost, st) != cudaSuccess) return ASCAN_ERR_LAUNCH;
+    if (cudaStreamSynchronize(st) != cudaSuccess) return ASCAN_ERR_LAUNCH;
+    if (host[0] == 0) return ASCAN_OK;
+    if (cudaMemsetAsync(ws, 0, sizeof(uint32_t), st) != cudaSuccess) return ASCAN_ERR_LAUNCH;
+    return ASCAN_ERR_TIMEOUT;
+}
+
+}  // extern "C"

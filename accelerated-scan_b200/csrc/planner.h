@@ -1,0 +1,30 @@
+// Chunking / launch planner: pure host arithmetic that turns (rows, T, dtype, kind,
+// alignment, SM count) into a launch plan.  It replaces the reference's 12-case
+// sequence-length ladder (warp.cuh:282-380), which accepts powers of two from 32 to
+// 65536 only and fixes one CTA per row; this planner accepts any T >= 1.
+#pragma once
+
+#include <stdint.h>
+
+#include "../../include/ascan_b200.h"
+
+namespace ascan {
+
+constexpr int kMaxSmemPerCta = 227 * 1024;   // opt-in dynamic shared memory per CTA on sm_100
+constexpr int kMaxWarpsPerCta = 12;   // kernels are compiled for at most 384 threads per CTA
+
+struct PlanInput {
+    int64_t rows;
+    int64_t seqlen;
+    int dtype;      // ascan_dtype
+    int kind;       // ascan_kind
+    bool aligned;   // every pointer 16-byte aligned
+    int sm_count;
+};
+
+int dtype_size(int dtype);   // bytes per element, 0 if unknown
+
+// Fills `plan`; returns an ascan_status.
+int make_plan(const PlanInput &in, ascan_plan *plan);
+
+}  // namespace ascan

@@ -1,0 +1,154 @@
+/*
+ * ascan_b200 — C ABI of the B200 (sm_100a) first-order scan library.
+ *
+ *     x[t] = gate[t] * x[t-1] + token[t]          (forward)
+ *     g[t] = grad_out[t] + conj(gate[t+1]) * g[t+1]
+ *     d_token[t] = g[t],  d_gate[t] = conj(x[t-1]) * g[t]   (backward)
+ *
+ * Every array is a dense row-major matrix of `rows` x `seqlen` elements (the
+ * reference's contiguous (B, C, T) tensors with rows = B*C; warp.cuh:267-276).
+ * All pointers are DEVICE pointers on the current CUDA device; the library
+ * allocates nothing, keeps no state between calls and launches asynchronously on
+ * the stream it is given (a cudaStream_t passed as void*; NULL = default stream).
+ * Every function returns an ascan_status; 0 is success.
+ *
+ * This header replaces the reference's pybind/ATen boundary
+ * (accelerated_scan/warp.py:8-11,29-30 and accelerated_scan/warp.cuh:394-424) and
+ * the Triton launch sites of accelerated_scan/complex.py:174-180,205-213.
+ */
+#ifndef ASCAN_B200_H
+#define ASCAN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    ASCAN_OK = 0,
+    ASCAN_ERR_INVALID_ARG = 1,   /* null pointer, rows < 0, seqlen < 1, bad enum          */
+    ASCAN_ERR_UNSUPPORTED = 2,   /* combination the library does not implement            */
+    ASCAN_ERR_LAUNCH = 3,        /* the CUDA runtime rejected the launch                  */
+    ASCAN_ERR_TIMEOUT = 4,       /* a bounded device-side wait gave up (see ascan_check)  */
+    ASCAN_ERR_WORKSPACE = 5,     /* workspace missing, misaligned or too small            */
+    ASCAN_ERR_DEVICE = 6         /* no sm_100 device / runtime query failed               */
+} ascan_status;
+
+/* Storage type of gates/tokens/outputs.  Arithmetic is always fp32 (complex64:
+ * pairs of fp32).  Replaces the dtype switch of warp.cuh:383-392. */
+typedef enum {
+    ASCAN_F32 = 0,
+    ASCAN_BF16 = 1,
+    ASCAN_F16 = 2,
+    ASCAN_C64 = 3                /* interleaved (re, im) fp32 pairs, complex.py:171-173   */
+} ascan_dtype;
+
+/* Which computation a plan / workspace query is for. */
+typedef enum {
+    ASCAN_KIND_FORWARD = 0,
+    ASCAN_KIND_BACKWARD = 1,
+    ASCAN_KIND_REDUCE_FORWARD = 2,
+    ASCAN_KIND_REDUCE_BACKWARD = 3
+} ascan_kind;
+
+/* Launch plan chosen by the planner; replaces the 12-case sequence-length ladder
+ * of warp.cuh:282-380.  Pure host arithmetic, usable without a GPU when
+ * sm_count > 0 is passed. */
+typedef struct {
+    int32_t kernel;            /* 0 = row-stream (each warp owns whole rows), 1 = split-row (rows span CTAs, look-back) */
+    int32_t loader;            /* 0 = bulk-async copies into shared-memory stages, 1 = plain element loads (unaligned data) */
+    int32_t chunks_per_lane;   /* 16-byte chunks each lane owns per tile                 */
+    int32_t stages;            /* shared-memory stages per warp                           */
+    int32_t warps_per_cta;
+    int32_t grid;              /* CTAs                                                    */
+    int32_t tile_elems;        /* elements per warp tile                                  */
+    int32_t reserved;
+    int64_t rows_per_item;     /* rows grouped so every item starts 16-byte aligned       */
+    int64_t items;
+    int64_t tiles_per_row;     /* split-row kernel only                                   */
+    uint64_t smem_bytes;       /* dynamic shared memory per CTA                           */
+    uint64_t workspace_bytes;  /* scratch the launch needs (0 for the row-stream kernel)  */
+} ascan_plan;
+
+/* Library version: major*10000 + minor*100 + patch. */
+int ascan_version(void);
+
+/* Static message for a status code. */
+const char *ascan_strerror(int status);
+
+/*
+ * Forward scan.  Replaces warpscan_forward(gates, tokens, out, reverse)
+ * (warp.cuh:394-405) and complex forward_scan (complex.py:20-65).
+ *   reverse  != 0 solves x[t] = gate[t]*x[t+1] + token[t] from the last step.
+ *   carry_in (nullable): `rows` values of the compute type (float, or float2 for
+ *            ASCAN_C64): the state before the first step of every row (after the
+ *            last step when reverse).  NULL means zero.
+ *   ws/ws_bytes: scratch of at least ascan_workspace_bytes(...) bytes, 256-byte
+ *            aligned, zero-filled once by the caller before its first use; may be
+ *            NULL when that size is 0.
+ */
+int ascan_forward(const void *gates, const void *tokens, void *out,
+                  int64_t rows, int64_t seqlen, int dtype, int reverse,
+                  const void *carry_in, void *ws, size_t ws_bytes, void *stream);
+
+/*
+ * Fused backward.  Replaces warpscan_backward(gates, output, outGrad, gateGradOut,
+ * tokenGradOut) (warp.cuh:407-424) and complex backward_scan (complex.py:68-154).
+ * The three nullable arrays serve time-sharded callers and hold `rows` values of
+ * the compute type:
+ *   carry_in         g just after the last step of the row (NULL = 0)
+ *   halo_gate_right  gate of the step after the last one    (only read with carry_in)
+ *   halo_state_left  state before the first step            (NULL = 0)
+ */
+int ascan_backward(const void *gates, const void *states, const void *grad_out,
+                   void *d_gates, void *d_tokens,
+                   int64_t rows, int64_t seqlen, int dtype,
+                   const void *carry_in, const void *halo_gate_right,
+                   const void *halo_state_left,
+                   void *ws, size_t ws_bytes, void *stream);
+
+/*
+ * Carry of every row without writing the scan: carry_out[2*r] = product of the
+ * row's gates, carry_out[2*r+1] = last state of the row started from zero
+ * (compute type).  No counterpart in the reference (it has no multi-GPU path);
+ * it is the local step of the time-sharded scan.
+ */
+int ascan_reduce_forward(const void *gates, const void *tokens, void *carry_out,
+                         int64_t rows, int64_t seqlen, int dtype,
+                         void *ws, size_t ws_bytes, void *stream);
+
+/*
+ * Carry of the backward recurrence: carry_out[2*r] = product over the row of
+ * conj(gate[t+1]) (gate[seqlen] := halo_gate_right[r], or 1 when NULL),
+ * carry_out[2*r+1] = g[0] of the row started from zero.  No counterpart in the
+ * reference.
+ */
+int ascan_reduce_backward(const void *gates, const void *grad_out,
+                          const void *halo_gate_right, void *carry_out,
+                          int64_t rows, int64_t seqlen, int dtype,
+                          void *ws, size_t ws_bytes, void *stream);
+
+/* Scratch bytes a call of `kind` with these sizes needs (0 = none). */
+size_t ascan_workspace_bytes(int64_t rows, int64_t seqlen, int dtype, int kind);
+
+/*
+ * The plan the library would use.  `aligned` says whether every pointer is
+ * 16-byte aligned; sm_count <= 0 queries the current device.  Host only.
+ */
+int ascan_plan_describe(int64_t rows, int64_t seqlen, int dtype, int kind,
+                        int aligned, int sm_count, ascan_plan *plan);
+
+/*
+ * Reads the device status word at the start of a workspace after synchronising
+ * `stream`.  Returns ASCAN_OK, or ASCAN_ERR_TIMEOUT when a bounded device-side
+ * wait expired in an earlier launch that used this workspace (the word is then
+ * cleared).  Optional: the hot path never synchronises.
+ */
+int ascan_check(void *ws, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ASCAN_B200_H */

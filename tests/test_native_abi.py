@@ -1,0 +1,101 @@
+"""The C-ABI library: it loads, exports every symbol the public header declares,
+rejects bad arguments before touching the GPU, and the planner covers the
+reference's domain and beyond.  Runs without a GPU (no compute calls)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from conftest import ROOT
+from accelerated_scan import _native
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "ascan_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ascan_[a-z_]+)\s*\(", text)))
+
+
+def test_header_symbols_exported():
+    names = declared_symbols()
+    assert set(names) >= set(_native.EXPORTS)
+    for name in names:
+        assert hasattr(_native.lib, name), name
+
+
+def test_version_and_strerror():
+    assert _native.lib.ascan_version() >= 100
+    assert _native.strerror(0) == "success"
+    assert "invalid" in _native.strerror(1)
+    assert "unknown" in _native.strerror(12345)
+
+
+def test_bad_arguments_rejected_without_gpu():
+    lib = _native.lib
+    null = ctypes.c_void_p(None)
+    fake = ctypes.c_void_p(256)   # never dereferenced: validation fails first
+    assert lib.ascan_forward(fake, fake, fake, -1, 8, 0, 0, null, null, 0, null) == 1
+    assert lib.ascan_forward(fake, fake, fake, 4, 0, 0, 0, null, null, 0, null) == 1
+    assert lib.ascan_forward(fake, fake, fake, 4, 8, 99, 0, null, null, 0, null) == 1
+    assert lib.ascan_forward(null, fake, fake, 4, 8, 0, 0, null, null, 0, null) == 1
+    assert lib.ascan_forward(fake, fake, fake, 0, 8, 0, 0, null, null, 0, null) == 0   # empty: nothing to do
+    assert lib.ascan_backward(fake, fake, fake, fake, null, 4, 8, 0, null, null, null, null, 0, null) == 1
+    assert lib.ascan_backward(fake, fake, fake, fake, fake, 4, 8, 0, fake, null, null, null, 0, null) == 1
+    assert lib.ascan_reduce_forward(fake, fake, null, 4, 8, 0, null, 0, null) == 1
+    assert lib.ascan_reduce_backward(fake, null, null, fake, 4, 8, 0, null, 0, null) == 1
+    assert lib.ascan_check(null, null) == 1
+
+
+@pytest.mark.parametrize("T", [1, 7, 32, 64, 128, 1024, 4096, 65536, 16323, 8000, 33753, 127323, 1 << 20])
+@pytest.mark.parametrize("dtype", [_native.F32, _native.BF16, _native.F16, _native.C64])
+@pytest.mark.parametrize("kind", [0, 1, 2, 3])
+def test_planner_invariants(T, dtype, kind):
+    esize = {0: 4, 1: 2, 2: 2, 3: 8}[dtype]
+    for rows in (1, 16, 512, 12288):
+        pl = _native.plan(rows, T, dtype, kind, aligned=True, sm_count=148)
+        assert pl["grid"] >= 1 and pl["warps_per_cta"] >= 1
+        assert pl["warps_per_cta"] * 32 <= 384
+        assert pl["smem_bytes"] <= 227 * 1024
+        assert pl["items"] * pl["rows_per_item"] >= rows
+        assert pl["tile_elems"] == 32 * pl["chunks_per_lane"] * (16 // esize)
+        if pl["loader"] == 0:
+            # bulk copies: every item starts on a 16-byte boundary and the matrix ends on one
+            assert (pl["rows_per_item"] * T * esize) % 16 == 0
+            assert (rows * T * esize) % 16 == 0
+        # no more warps than items, spread over the SMs
+        assert pl["grid"] * pl["warps_per_cta"] <= max(pl["items"], 1) + pl["warps_per_cta"] * 148
+        unaligned = _native.plan(rows, T, dtype, kind, aligned=False, sm_count=148)
+        assert unaligned["loader"] == 1 and unaligned["rows_per_item"] == 1
+
+
+def test_planner_rejects_bad_input():
+    pl = _native.Plan()
+    assert _native.lib.ascan_plan_describe(4, 0, 0, 0, 1, 148, ctypes.byref(pl)) == 1
+    assert _native.lib.ascan_plan_describe(4, 8, 7, 0, 1, 148, ctypes.byref(pl)) == 1
+    assert _native.lib.ascan_plan_describe(4, 8, 0, 9, 1, 148, ctypes.byref(pl)) == 1
+    assert _native.lib.ascan_plan_describe(4, 8, 0, 0, 1, 148, None) == 1
+
+
+def test_python_api_mirrors_reference_names():
+    import accelerated_scan.warp as warp
+    import accelerated_scan.complex as cplx
+
+    for name in ("scan", "Scan", "scan_forward", "warpscan_forward", "warpscan_backward"):
+        assert hasattr(warp, name)
+    for name in ("scan", "Scan", "forward_scan", "backward_scan"):
+        assert hasattr(cplx, name)
+
+
+def test_cpu_tensors_fail_loudly():
+    import torch
+    import accelerated_scan.warp as warp
+    import accelerated_scan.complex as cplx
+
+    g = torch.rand(1, 2, 32)
+    with pytest.raises(RuntimeError):
+        warp.scan(g, g.clone())
+    with pytest.raises(TypeError):
+        cplx.scan(g, g.clone())
+    with pytest.raises(AssertionError):
+        warp.Scan.apply(g, torch.rand(1, 2, 16))
