@@ -1,0 +1,396 @@
+"""Benchmark of the scan hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    torchrun ... bench.py --gpus N ...          (one rank per GPU)
+
+A step is one forward + one fused backward scan over the (8, 1536, 65536) bf16
+tensors (per GPU; rows are sharded over ranks with no communication, weak scaling).
+Prints one JSON line on rank 0:
+
+  value      fwd+bwd algorithmic GB/s (8 bytes-per-element-size * N / time), inputs resident in HBM
+  e2e        the same metric through the drop-in autograd API with pinned HOST buffers,
+             host<->device copies inside the timed region
+  roofline   the dominant kernel (fused backward) against the measured HBM copy bandwidth
+  cpu_baseline  the CPU oracle (a port of the reference's ref.py tree) on the host cores, bounded sample
+
+`--impl reference` times that CPU port alone on the same workload definition.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "accelerated-scan_b200"))
+sys.path.insert(0, ROOT)
+
+METRIC = "scan_fwd_bwd_algorithmic_GBps"
+UNIT = "GB/s"
+B, C = 8, 1536
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--seqlen", type=int, default=65536)
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"])
+    ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    return ap.parse_args()
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+def config_dict(args, n_gpus):
+    return {
+        "workload": f"first-order scan forward + fused backward, ({B},{C},{args.seqlen}) {args.dtype} per GPU, "
+                    "gates 0.999+0.001*U(0,1), tokens U(0,1), grad_out N(0,1)",
+        "rows_per_gpu": B * C, "seqlen": args.seqlen, "storage": args.dtype, "accumulation": "fp32",
+        "sharding": f"rows x{n_gpus} (no collective)",
+        "l2": "inputs larger than L2 (each tensor >= 1.6 GB at the default size), no flush needed",
+    }
+
+
+# ------------------------------------------------------------------ CPU oracle leg
+
+def cpu_oracle_run(seqlen, rows, repeats=1):
+    """fwd + bwd of the CPU oracle on `rows` rows; returns seconds per pass."""
+    import numpy as np
+    from oracle import scan_oracle
+
+    rng = np.random.default_rng(0)
+    g = (0.999 + 0.001 * rng.random((1, rows, seqlen), dtype=np.float32))
+    x = rng.random((1, rows, seqlen), dtype=np.float32)
+    go = rng.standard_normal((1, rows, seqlen), dtype=np.float32)
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        out = scan_oracle.scan(g, x)
+        scan_oracle.scan_backward(g, out, go)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return best
+
+
+def cpu_baseline(args, esize):
+    from oracle import scan_oracle
+
+    scan_oracle.build()
+    cores = scan_oracle.num_threads()
+    total_rows = B * C
+    probe_rows = max(cores, 32)
+    t_probe = cpu_oracle_run(args.seqlen, probe_rows)
+    rows = int(min(total_rows, max(probe_rows, probe_rows * args.cpu_seconds / max(t_probe, 1e-6))))
+    rows = max(cores, rows // cores * cores)
+    t = cpu_oracle_run(args.seqlen, rows)
+    gbs = 8 * esize * rows * args.seqlen / t / 1e9
+    return {
+        "value": round(gbs, 4), "unit": UNIT, "cores": cores, "kind": "port",
+        "sample": f"{rows} of {total_rows} rows x {args.seqlen} steps, fwd+bwd in fp32 by the C port of ref.py's tree "
+                  f"(OpenMP over rows), {t:.2f} s; bytes counted at the benchmark's storage size",
+    }, rows, t
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    esize = 2 if args.dtype == "bf16" else 4
+    from oracle import scan_oracle
+
+    scan_oracle.build()
+    cores = scan_oracle.num_threads()
+    probe_rows = max(cores, 32)
+    t_probe = cpu_oracle_run(args.seqlen, probe_rows)
+    budget = 120.0 / max(1, args.steps + args.warmup)
+    rows = int(min(B * C, max(probe_rows, probe_rows * min(budget, 10.0) / max(t_probe, 1e-6))))
+    rows = max(cores, rows // cores * cores)
+    for _ in range(args.warmup):
+        cpu_oracle_run(args.seqlen, rows)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_oracle_run(args.seqlen, rows)
+    dt = (time.perf_counter() - t0) / max(1, args.steps)
+    gbs = 8 * esize * rows * args.seqlen / dt / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(gbs, 4), "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": config_dict(args, args.gpus),
+        "cpu_baseline": {"value": round(gbs, 4), "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"each step: {rows} of {B * C} rows x {args.seqlen} steps, fwd+bwd, C port of "
+                                   "ref.py's tree with OpenMP over rows"},
+        "e2e": {"value": round(gbs, 4), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------ clocks sampler
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.perf_counter(), line.strip()))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            pass
+        rows = [l for (t, l) in self.lines if t0 - 0.05 <= t <= t1 + 0.15] or [l for (_, l) in self.lines]
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for l in rows:
+            f = [x.strip() for x in l.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------ GPU legs
+
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+
+    from accelerated_scan import _native
+    import accelerated_scan.warp as warp
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float32
+    esize = 2 if args.dtype == "bf16" else 4
+    T = args.seqlen
+    N = B * C * T
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    gates = (0.999 + 0.001 * torch.rand(B, C, T, device=dev, generator=gen)).to(dtype)
+    tokens = torch.rand(B, C, T, device=dev, generator=gen).to(dtype)
+    grad_out = torch.randn(B, C, T, device=dev, generator=gen).to(dtype)
+    out = torch.empty_like(tokens)
+    d_gates = torch.empty_like(tokens)
+    d_tokens = torch.empty_like(tokens)
+
+    def step():
+        _native.forward(gates, tokens, out)
+        _native.backward(gates, out, grad_out, d_gates, d_tokens)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+
+    K = args.steps
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    barrier()
+    t_host0 = time.perf_counter()
+    start = torch.cuda.Event(enable_timing=True)
+    end = torch.cuda.Event(enable_timing=True)
+    start.record()
+    for k in range(K):
+        ev[k][0].record()
+        _native.forward(gates, tokens, out)
+        ev[k][1].record()
+        _native.backward(gates, out, grad_out, d_gates, d_tokens)
+        ev[k][2].record()
+    end.record()
+    barrier()
+    t_host1 = time.perf_counter()
+    clocks = sampler.stop(t_host0, t_host1) if rank == 0 else None
+    total_ms = start.elapsed_time(end)
+    fwd_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / K
+    bwd_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / K
+    if world > 1:
+        t = torch.tensor([total_ms, fwd_ms, bwd_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms, fwd_ms, bwd_ms = (float(v) for v in t.tolist())
+    ms_per_step = total_ms / K
+    bytes_step = 8 * esize * N
+    value = world * bytes_step / (ms_per_step * 1e-3) / 1e9
+    _native.check_status(dev)
+
+    # ---- end to end through the drop-in autograd API with pinned host buffers
+    e2e = None
+    launches = 2 * K
+    if not args.no_e2e:
+        e2e, e2e_launches = run_e2e(args, torch, dist, warp, dev, world, dtype, esize)
+        launches += e2e_launches
+
+    if world > 1:
+        dist.barrier()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_kind = measured_peak()
+    bwd_gbs = 5 * esize * N / (bwd_ms * 1e-3) / 1e9
+    fwd_gbs = 3 * esize * N / (fwd_ms * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": max(3, args.warmup),
+        "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": config_dict(args, world),
+        "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+        "roofline": {
+            "kernel": "rowstream_kernel<backward>", "bound": "hbm", "achieved": round(bwd_gbs, 1), "peak": peak,
+            "unit": UNIT, "frac": round(bwd_gbs / peak, 4), "peak_kind": f"of {peak_kind}",
+            "algorithmic_bytes_per_launch": 5 * esize * N, "ms_per_launch": round(bwd_ms, 5),
+            "traffic": TRAFFIC_BWD_BYTES_PER_ELEM * N if TRAFFIC_BWD_BYTES_PER_ELEM and args.dtype == "bf16" else None,
+        },
+        "roofline_forward": {
+            "kernel": "rowstream_kernel<forward>", "bound": "hbm", "achieved": round(fwd_gbs, 1), "peak": peak,
+            "unit": UNIT, "frac": round(fwd_gbs / peak, 4), "algorithmic_bytes_per_launch": 3 * esize * N,
+            "ms_per_launch": round(fwd_ms, 5),
+        },
+        "pct_of_nominal_8TBs": round(100 * value / world / 8000.0, 2),
+    }
+    if not args.no_cpu_baseline and world == 1:
+        cb, _, _ = cpu_baseline(args, esize)
+        line["cpu_baseline"] = cb
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# DRAM bytes per element of the backward kernel from the ncu capture summarised under
+# profiles/ (dram__bytes_read.sum + dram__bytes_write.sum, scaled per element); None until captured.
+TRAFFIC_BWD_BYTES_PER_ELEM = None
+
+
+def run_e2e(args, torch, dist, warp, dev, world, dtype, esize):
+    """fwd+bwd through accelerated_scan.warp.scan from pinned host buffers: every step
+    copies gates, tokens and grad_out host->device and out, d_gates, d_tokens back.
+    Rows are independent, so the step is pipelined in row slabs over three streams."""
+    T = args.seqlen
+    slabs = 8
+    rows_slab = B * C // slabs
+    shape = (1, rows_slab, T)
+    pin = lambda: [torch.empty(shape, dtype=dtype).pin_memory() for _ in range(slabs)]
+    h_g, h_x, h_go = pin(), pin(), pin()
+    h_out, h_dg, h_dx = pin(), pin(), pin()
+    gen = torch.Generator().manual_seed(99)
+    for i in range(slabs):
+        h_g[i].copy_((0.999 + 0.001 * torch.rand(shape, generator=gen)).to(dtype))
+        h_x[i].copy_(torch.rand(shape, generator=gen).to(dtype))
+        h_go[i].copy_(torch.randn(shape, generator=gen).to(dtype))
+    streams = [torch.cuda.Stream(device=dev) for _ in range(3)]
+    bufs = [[torch.empty(shape, dtype=dtype, device=dev) for _ in range(3)] for _ in streams]
+    launches = 0
+
+    def one_step():
+        n = 0
+        for i in range(slabs):
+            s = streams[i % len(streams)]
+            dg_, dx_, dgo_ = bufs[i % len(streams)]
+            with torch.cuda.stream(s):
+                dg_.copy_(h_g[i], non_blocking=True)
+                dx_.copy_(h_x[i], non_blocking=True)
+                dgo_.copy_(h_go[i], non_blocking=True)
+                g = dg_.detach().requires_grad_(True)
+                x = dx_.detach().requires_grad_(True)
+                o = warp.scan(g, x)
+                o.backward(dgo_)
+                h_out[i].copy_(o.detach(), non_blocking=True)
+                h_dg[i].copy_(g.grad, non_blocking=True)
+                h_dx[i].copy_(x.grad, non_blocking=True)
+                n += 2
+        for s in streams:
+            s.synchronize()
+        return n
+
+    one_step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.e2e_steps):
+        launches += one_step()
+    torch.cuda.synchronize()
+    dt = (time.perf_counter() - t0) / args.e2e_steps
+    if world > 1:
+        t = torch.tensor([dt], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = float(t.item())
+    n_elems = B * C * T
+    gbs = world * 8 * esize * n_elems / dt / 1e9
+    return ({"value": round(gbs, 2), "unit": UNIT, "h2d_bytes_per_step": 3 * esize * n_elems,
+             "d2h_bytes_per_step": 3 * esize * n_elems, "ms_per_step": round(dt * 1e3, 3), "steps": args.e2e_steps,
+             "api": "accelerated_scan.warp.scan + autograd backward, 8 row slabs pipelined on 3 streams"}, launches)
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()
