@@ -31,8 +31,9 @@ class Plan(ctypes.Structure):
     _fields_ = [
         ("kernel", ctypes.c_int32), ("loader", ctypes.c_int32), ("chunks_per_lane", ctypes.c_int32),
         ("stages", ctypes.c_int32), ("warps_per_cta", ctypes.c_int32), ("grid", ctypes.c_int32),
-        ("tile_elems", ctypes.c_int32), ("reserved", ctypes.c_int32),
-        ("rows_per_item", ctypes.c_int64), ("items", ctypes.c_int64), ("tiles_per_row", ctypes.c_int64),
+        ("tile_elems", ctypes.c_int32), ("dynamic", ctypes.c_int32),
+        ("rows_per_item", ctypes.c_int64), ("row_groups", ctypes.c_int64), ("seg_elems", ctypes.c_int64),
+        ("segs_per_row", ctypes.c_int64), ("items", ctypes.c_int64),
         ("smem_bytes", ctypes.c_uint64), ("workspace_bytes", ctypes.c_uint64),
     ]
 
@@ -110,21 +111,26 @@ def _require_cuda(*tensors):
 _workspaces = {}
 
 
-def workspace(device: torch.device, nbytes: int = 256) -> torch.Tensor:
-    """Zero-initialised scratch per (device, stream), owned by torch's allocator.
-    Its first word is the device status word."""
+def workspace(device: torch.device, rows: int = 0) -> torch.Tensor:
+    """Scratch per (device, stream), owned by torch's allocator and zero-filled once
+    when it is created (the kernels rearm it themselves).  It holds the status word,
+    the work ticket and one carry record per row; launches on different streams get
+    different workspaces because they may overlap."""
+    nbytes = int(lib.ascan_workspace_bytes(int(rows), 1, 0, 0))
     stream = torch.cuda.current_stream(device).cuda_stream
     key = (device.index, stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
-        ws = torch.zeros(max(256, int(nbytes)), dtype=torch.uint8, device=device)
+        ws = torch.zeros(max(4096, 2 * nbytes), dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws
 
 
-def plan(rows: int, seqlen: int, dtype: int, kind: int, aligned: bool = True, sm_count: int = 148) -> dict:
+def plan(rows: int, seqlen: int, dtype: int, kind: int, aligned: bool = True, workspace: bool = True,
+         sm_count: int = 148) -> dict:
     pl = Plan()
-    check(lib.ascan_plan_describe(rows, seqlen, dtype, kind, int(aligned), sm_count, ctypes.byref(pl)),
+    flags = int(bool(aligned)) | (int(bool(workspace)) << 1)
+    check(lib.ascan_plan_describe(rows, seqlen, dtype, kind, flags, sm_count, ctypes.byref(pl)),
           "ascan_plan_describe")
     return pl.as_dict()
 
@@ -134,7 +140,7 @@ def forward(gates, tokens, out, reverse=False, carry_in=None):
     rows = gates.numel() // gates.shape[-1] if gates.shape[-1] else 0
     T = gates.shape[-1]
     with torch.cuda.device(gates.device):
-        ws = workspace(gates.device)
+        ws = workspace(gates.device, rows)
         rc = lib.ascan_forward(_ptr(gates), _ptr(tokens), _ptr(out), rows, T, dtype_code(gates), int(bool(reverse)),
                                _ptr(carry_in), _ptr(ws), ws.numel(), _stream(gates))
     check(rc, "ascan_forward")
@@ -145,7 +151,7 @@ def backward(gates, states, grad_out, d_gates, d_tokens, carry_in=None, halo_gat
     rows = gates.numel() // gates.shape[-1] if gates.shape[-1] else 0
     T = gates.shape[-1]
     with torch.cuda.device(gates.device):
-        ws = workspace(gates.device)
+        ws = workspace(gates.device, rows)
         rc = lib.ascan_backward(_ptr(gates), _ptr(states), _ptr(grad_out), _ptr(d_gates), _ptr(d_tokens), rows, T,
                                 dtype_code(gates), _ptr(carry_in), _ptr(halo_gate_right), _ptr(halo_state_left),
                                 _ptr(ws), ws.numel(), _stream(gates))
@@ -156,7 +162,7 @@ def reduce_forward(gates, tokens, carry_out):
     _require_cuda(gates, tokens, carry_out)
     rows = gates.numel() // gates.shape[-1]
     with torch.cuda.device(gates.device):
-        ws = workspace(gates.device)
+        ws = workspace(gates.device, rows)
         rc = lib.ascan_reduce_forward(_ptr(gates), _ptr(tokens), _ptr(carry_out), rows, gates.shape[-1],
                                       dtype_code(gates), _ptr(ws), ws.numel(), _stream(gates))
     check(rc, "ascan_reduce_forward")
@@ -166,7 +172,7 @@ def reduce_backward(gates, grad_out, halo_gate_right, carry_out):
     _require_cuda(gates, grad_out, halo_gate_right, carry_out)
     rows = gates.numel() // gates.shape[-1]
     with torch.cuda.device(gates.device):
-        ws = workspace(gates.device)
+        ws = workspace(gates.device, rows)
         rc = lib.ascan_reduce_backward(_ptr(gates), _ptr(grad_out), _ptr(halo_gate_right), _ptr(carry_out), rows,
                                        gates.shape[-1], dtype_code(gates), _ptr(ws), ws.numel(), _stream(gates))
     check(rc, "ascan_reduce_backward")

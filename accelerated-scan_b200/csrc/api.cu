@@ -2,6 +2,7 @@
 // argument validation, planning, kernel dispatch, launch-error reporting.
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include <mutex>
 #include <set>
@@ -9,7 +10,7 @@
 
 #include "../../include/ascan_b200.h"
 #include "planner.h"
-#include "rowstream.cuh"
+#include "stream.cuh"
 
 namespace ascan {
 
@@ -48,8 +49,8 @@ static int ensure_smem(const void *fn, size_t bytes) {
 }
 
 template <class TR, int NCH, int KIND, bool REVERSE, bool BULK>
-static int launch_one(const RowStreamParams &p, const ascan_plan &pl, cudaStream_t stream) {
-    auto kfn = rowstream_kernel<TR, NCH, KIND, REVERSE, BULK>;
+static int launch_one(const StreamParams &p, const ascan_plan &pl, cudaStream_t stream) {
+    auto kfn = stream_kernel<TR, NCH, KIND, REVERSE, BULK>;
     int rc = ensure_smem(reinterpret_cast<const void *>(kfn), pl.smem_bytes);
     if (rc != ASCAN_OK) return rc;
     kfn<<<pl.grid, pl.warps_per_cta * 32, pl.smem_bytes, stream>>>(p);
@@ -57,13 +58,13 @@ static int launch_one(const RowStreamParams &p, const ascan_plan &pl, cudaStream
 }
 
 template <class TR, int NCH, int KIND, bool REVERSE>
-static int launch_loader(const RowStreamParams &p, const ascan_plan &pl, cudaStream_t stream) {
+static int launch_loader(const StreamParams &p, const ascan_plan &pl, cudaStream_t stream) {
     return pl.loader == 0 ? launch_one<TR, NCH, KIND, REVERSE, true>(p, pl, stream)
                           : launch_one<TR, NCH, KIND, REVERSE, false>(p, pl, stream);
 }
 
 template <class TR, int KIND, bool REVERSE>
-static int launch_nch(const RowStreamParams &p, const ascan_plan &pl, cudaStream_t stream) {
+static int launch_nch(const StreamParams &p, const ascan_plan &pl, cudaStream_t stream) {
     switch (pl.chunks_per_lane) {
         case 3: return launch_loader<TR, 3, KIND, REVERSE>(p, pl, stream);
         case 5: return launch_loader<TR, 5, KIND, REVERSE>(p, pl, stream);
@@ -72,7 +73,7 @@ static int launch_nch(const RowStreamParams &p, const ascan_plan &pl, cudaStream
 }
 
 template <int KIND, bool REVERSE>
-static int launch_dtype(int dtype, const RowStreamParams &p, const ascan_plan &pl, cudaStream_t stream) {
+static int launch_dtype(int dtype, const StreamParams &p, const ascan_plan &pl, cudaStream_t stream) {
     switch (dtype) {
         case ASCAN_F32: return launch_nch<TraitsF32, KIND, REVERSE>(p, pl, stream);
         case ASCAN_BF16: return launch_nch<TraitsBF16, KIND, REVERSE>(p, pl, stream);
@@ -82,23 +83,44 @@ static int launch_dtype(int dtype, const RowStreamParams &p, const ascan_plan &p
     }
 }
 
+static int l2_hints_env() {
+    const char *v = getenv("ASCAN_L2_HINTS");
+    return (v && *v) ? atoi(v) : 0;
+}
+
 static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-static int plan_for(int64_t rows, int64_t seqlen, int dtype, int kind, bool aligned, ascan_plan *pl) {
+static bool workspace_usable(const void *ws, size_t ws_bytes, int64_t rows) {
+    return ws && (reinterpret_cast<uintptr_t>(ws) & 255u) == 0 && ws_bytes >= workspace_bytes(rows);
+}
+
+static int plan_for(int64_t rows, int64_t seqlen, int dtype, int kind, bool aligned, const void *ws, size_t ws_bytes,
+                    ascan_plan *pl) {
     PlanInput in;
     in.rows = rows;
     in.seqlen = seqlen;
     in.dtype = dtype;
     in.kind = kind;
     in.aligned = aligned;
+    in.workspace = workspace_usable(ws, ws_bytes, rows);
     int rc = cached_sm_count(&in.sm_count);
     if (rc != ASCAN_OK) return rc;
     return make_plan(in, pl);
 }
 
-static uint32_t *status_word(void *ws, size_t ws_bytes) {
-    if (!ws || ws_bytes < 16 || (reinterpret_cast<uintptr_t>(ws) & 3u)) return nullptr;
-    return static_cast<uint32_t *>(ws);
+// Copies the plan's decomposition and the workspace pointers into the kernel parameters.
+static void fill_common(StreamParams &p, const ascan_plan &pl, int64_t rows, int64_t seqlen, void *ws) {
+    p.rows = rows;
+    p.T = seqlen;
+    p.rows_per_item = pl.rows_per_item;
+    p.row_groups = pl.row_groups;
+    p.seg_elems = pl.seg_elems;
+    p.segs_per_row = pl.segs_per_row;
+    p.items = pl.items;
+    p.ctrl = pl.dynamic ? static_cast<uint32_t *>(ws) : nullptr;
+    p.records = pl.dynamic ? static_cast<unsigned char *>(ws) + CTRL_BYTES : nullptr;
+    p.stages = pl.stages;
+    p.l2_hints = l2_hints_env();
 }
 
 }  // namespace ascan
@@ -129,19 +151,14 @@ int ascan_forward(const void *gates, const void *tokens, void *out, int64_t rows
     if (!gates || !tokens || !out) return ASCAN_ERR_INVALID_ARG;
     ascan_plan pl;
     const bool al = aligned16(gates) && aligned16(tokens) && aligned16(out);
-    int rc = plan_for(rows, seqlen, dtype, ASCAN_KIND_FORWARD, al, &pl);
+    int rc = plan_for(rows, seqlen, dtype, ASCAN_KIND_FORWARD, al, ws, ws_bytes, &pl);
     if (rc != ASCAN_OK) return rc;
-    RowStreamParams p = {};
+    StreamParams p = {};
     p.in0 = gates;
     p.in1 = tokens;
     p.out0 = out;
     p.carry_in = carry_in;
-    p.rows = rows;
-    p.T = seqlen;
-    p.rows_per_item = pl.rows_per_item;
-    p.items = pl.items;
-    p.status = status_word(ws, ws_bytes);
-    p.stages = pl.stages;
+    fill_common(p, pl, rows, seqlen, ws);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return reverse ? launch_dtype<K_SCAN, true>(dtype, p, pl, st) : launch_dtype<K_SCAN, false>(dtype, p, pl, st);
 }
@@ -156,9 +173,9 @@ int ascan_backward(const void *gates, const void *states, const void *grad_out, 
     ascan_plan pl;
     const bool al = aligned16(gates) && aligned16(states) && aligned16(grad_out) && aligned16(d_gates) &&
                     aligned16(d_tokens);
-    int rc = plan_for(rows, seqlen, dtype, ASCAN_KIND_BACKWARD, al, &pl);
+    int rc = plan_for(rows, seqlen, dtype, ASCAN_KIND_BACKWARD, al, ws, ws_bytes, &pl);
     if (rc != ASCAN_OK) return rc;
-    RowStreamParams p = {};
+    StreamParams p = {};
     p.in0 = gates;
     p.in1 = grad_out;
     p.in2 = states;
@@ -167,12 +184,7 @@ int ascan_backward(const void *gates, const void *states, const void *grad_out, 
     p.carry_in = carry_in;
     p.halo_gate = halo_gate_right;
     p.halo_state = halo_state_left;
-    p.rows = rows;
-    p.T = seqlen;
-    p.rows_per_item = pl.rows_per_item;
-    p.items = pl.items;
-    p.status = status_word(ws, ws_bytes);
-    p.stages = pl.stages;
+    fill_common(p, pl, rows, seqlen, ws);
     return launch_dtype<K_BWD, true>(dtype, p, pl, static_cast<cudaStream_t>(stream));
 }
 
@@ -183,18 +195,13 @@ int ascan_reduce_forward(const void *gates, const void *tokens, void *carry_out,
     if (!gates || !tokens || !carry_out) return ASCAN_ERR_INVALID_ARG;
     ascan_plan pl;
     const bool al = aligned16(gates) && aligned16(tokens);
-    int rc = plan_for(rows, seqlen, dtype, ASCAN_KIND_REDUCE_FORWARD, al, &pl);
+    int rc = plan_for(rows, seqlen, dtype, ASCAN_KIND_REDUCE_FORWARD, al, ws, ws_bytes, &pl);
     if (rc != ASCAN_OK) return rc;
-    RowStreamParams p = {};
+    StreamParams p = {};
     p.in0 = gates;
     p.in1 = tokens;
     p.carry_out = carry_out;
-    p.rows = rows;
-    p.T = seqlen;
-    p.rows_per_item = pl.rows_per_item;
-    p.items = pl.items;
-    p.status = status_word(ws, ws_bytes);
-    p.stages = pl.stages;
+    fill_common(p, pl, rows, seqlen, ws);
     return launch_dtype<K_REDUCE, false>(dtype, p, pl, static_cast<cudaStream_t>(stream));
 }
 
@@ -205,38 +212,33 @@ int ascan_reduce_backward(const void *gates, const void *grad_out, const void *h
     if (!gates || !grad_out || !carry_out) return ASCAN_ERR_INVALID_ARG;
     ascan_plan pl;
     const bool al = aligned16(gates) && aligned16(grad_out);
-    int rc = plan_for(rows, seqlen, dtype, ASCAN_KIND_REDUCE_BACKWARD, al, &pl);
+    int rc = plan_for(rows, seqlen, dtype, ASCAN_KIND_REDUCE_BACKWARD, al, ws, ws_bytes, &pl);
     if (rc != ASCAN_OK) return rc;
-    RowStreamParams p = {};
+    StreamParams p = {};
     p.in0 = gates;
     p.in1 = grad_out;
     p.halo_gate = halo_gate_right;
     p.carry_out = carry_out;
-    p.rows = rows;
-    p.T = seqlen;
-    p.rows_per_item = pl.rows_per_item;
-    p.items = pl.items;
-    p.status = status_word(ws, ws_bytes);
-    p.stages = pl.stages;
+    fill_common(p, pl, rows, seqlen, ws);
     return launch_dtype<K_REDUCE_BWD, true>(dtype, p, pl, static_cast<cudaStream_t>(stream));
 }
 
 size_t ascan_workspace_bytes(int64_t rows, int64_t seqlen, int dtype, int kind) {
-    (void)rows;
     (void)seqlen;
     (void)dtype;
     (void)kind;
-    return 0;
+    return static_cast<size_t>(workspace_bytes(rows));
 }
 
-int ascan_plan_describe(int64_t rows, int64_t seqlen, int dtype, int kind, int aligned, int sm_count,
+int ascan_plan_describe(int64_t rows, int64_t seqlen, int dtype, int kind, int flags, int sm_count,
                         ascan_plan *plan) {
     PlanInput in;
     in.rows = rows;
     in.seqlen = seqlen;
     in.dtype = dtype;
     in.kind = kind;
-    in.aligned = aligned != 0;
+    in.aligned = (flags & 1) != 0;
+    in.workspace = (flags & 2) != 0;
     in.sm_count = sm_count;
     if (sm_count <= 0) {
         int rc = cached_sm_count(&in.sm_count);

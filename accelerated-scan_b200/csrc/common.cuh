@@ -49,6 +49,42 @@ __device__ __forceinline__ float2 shfl_idx(float2 v, int l) {
     return make_float2(__shfl_sync(0xffffffffu, v.x, l), __shfl_sync(0xffffffffu, v.y, l));
 }
 
+// Values handed from one warp to another through global memory travel in 64-bit words
+// that carry their own tag: {fp32 payload, 32-bit tag}.  A 64-bit access is a single
+// transaction, so a reader either sees the old word or the new word, payload and tag
+// together; no fence or acquire/release pair is needed on either side.  A complex value
+// uses two such words.  `slot` selects one of two values per 32-byte record.
+__device__ __forceinline__ void st_relaxed_u64(void *p, uint64_t v) {
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint64_t ld_relaxed_u64(const void *p) {
+    uint64_t v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint64_t tagged_word(float payload, uint32_t tag) {
+    return (static_cast<uint64_t>(tag) << 32) | __float_as_uint(payload);
+}
+__device__ __forceinline__ void publish_tagged(unsigned char *rec, int slot, float v, uint32_t tag) {
+    st_relaxed_u64(rec + slot * 16, tagged_word(v, tag));
+}
+__device__ __forceinline__ void publish_tagged(unsigned char *rec, int slot, float2 v, uint32_t tag) {
+    st_relaxed_u64(rec + slot * 16, tagged_word(v.x, tag));
+    st_relaxed_u64(rec + slot * 16 + 8, tagged_word(v.y, tag));
+}
+// Returns true and fills `v` when every word of the value carries `tag`.
+__device__ __forceinline__ bool read_tagged(const unsigned char *rec, int slot, uint32_t tag, float &v) {
+    const uint64_t w = ld_relaxed_u64(rec + slot * 16);
+    v = __uint_as_float(static_cast<uint32_t>(w));
+    return static_cast<uint32_t>(w >> 32) == tag;
+}
+__device__ __forceinline__ bool read_tagged(const unsigned char *rec, int slot, uint32_t tag, float2 &v) {
+    const uint64_t w0 = ld_relaxed_u64(rec + slot * 16);
+    const uint64_t w1 = ld_relaxed_u64(rec + slot * 16 + 8);
+    v = make_float2(__uint_as_float(static_cast<uint32_t>(w0)), __uint_as_float(static_cast<uint32_t>(w1)));
+    return static_cast<uint32_t>(w0 >> 32) == tag && static_cast<uint32_t>(w1 >> 32) == tag;
+}
+
 // ------------------------------------------------------------ element traits
 // EPC = elements per 16-byte chunk.  unpack/pack convert one chunk between its
 // storage form and EPC compute values.
@@ -203,6 +239,31 @@ __device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src_gmem, u
 __device__ __forceinline__ void bulk_s2g(void *dst_gmem, const void *src_smem, uint32_t bytes) {
     asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst_gmem),
                  "r"(smem_u32(src_smem)), "r"(bytes)
+                 : "memory");
+}
+
+// L2 eviction-priority policies for streaming data (every byte is touched once).
+__device__ __forceinline__ uint64_t policy_evict_first() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ uint64_t policy_evict_last() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void bulk_g2s_hint(void *dst_smem, const void *src_gmem, uint32_t bytes, uint64_t *bar,
+                                              uint64_t pol) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+            smem_u32(dst_smem)),
+        "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar)), "l"(pol)
+        : "memory");
+}
+__device__ __forceinline__ void bulk_s2g_hint(void *dst_gmem, const void *src_smem, uint32_t bytes, uint64_t pol) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group.L2::cache_hint [%0], [%1], %2, %3;" ::"l"(dst_gmem),
+                 "r"(smem_u32(src_smem)), "r"(bytes), "l"(pol)
                  : "memory");
 }
 

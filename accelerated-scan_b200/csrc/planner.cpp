@@ -14,6 +14,11 @@ int dtype_size(int dtype) {
     }
 }
 
+uint64_t workspace_bytes(int64_t rows) {
+    if (rows < 0) rows = 0;
+    return static_cast<uint64_t>(kCtrlBytes) + static_cast<uint64_t>(rows) * kCarryRecordBytes;
+}
+
 static int env_int(const char *name, int fallback) {
     const char *v = getenv(name);
     if (!v || !*v) return fallback;
@@ -25,8 +30,8 @@ static int nout_of(int kind) {
     return kind == ASCAN_KIND_FORWARD ? 1 : (kind == ASCAN_KIND_BACKWARD ? 2 : 0);
 }
 
-// Shared memory one warp of the row-stream kernel needs (must match
-// rowstream_warp_smem in rowstream.cuh).
+// Shared memory one warp of the stream kernel needs (must match stream_warp_smem
+// in stream.cuh).
 static int warp_smem(int nch, int stages, int kind, bool bulk) {
     const int tb = 32 * nch * 16;
     const int nstg = bulk ? stages : 1;
@@ -42,27 +47,52 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
 
     ascan_plan pl = {};
     pl.kernel = 0;
+    pl.dynamic = in.workspace ? 1 : 0;
 
     // 16-byte chunks per lane: odd, so that the 16-byte shared accesses of a
     // quarter-warp hit distinct bank groups.  Tuning override: ASCAN_NCH (3 or 5).
     int nch = env_int("ASCAN_NCH", 3);
     if (nch != 3 && nch != 5) nch = 3;
     pl.chunks_per_lane = nch;
-    pl.tile_elems = 32 * nch * (16 / esize);
+    const int64_t te = 32 * nch * (16 / esize);
+    pl.tile_elems = static_cast<int32_t>(te);
 
     // Bulk copies need every item to start on a 16-byte boundary and to be a
-    // multiple of 16 bytes long: group rows until that holds.
-    const int64_t row_bytes_mod = (in.seqlen % 16) * esize % 16;
-    int64_t rpi = 1;
-    while ((rpi * row_bytes_mod) % 16 != 0) rpi *= 2;          // at most 16
-    // ... and the whole matrix must end on a 16-byte boundary (last item may be short)
+    // multiple of 16 bytes long: group `align_rows` rows until that holds ...
+    const int64_t row_bytes_mod = ((in.seqlen % 16) * esize) % 16;
+    int64_t align_rows = 1;
+    while ((align_rows * row_bytes_mod) % 16 != 0) align_rows *= 2;          // at most 16
+    // ... and the whole matrix must end on a 16-byte boundary (the last item may be short)
     const bool total_ok = ((in.rows % 16) * row_bytes_mod) % 16 == 0;
     const bool bulk = in.aligned && total_ok && env_int("ASCAN_FORCE_PLAIN", 0) == 0;
     pl.loader = bulk ? 0 : 1;
-    pl.rows_per_item = bulk ? rpi : 1;
-    pl.items = (in.rows + pl.rows_per_item - 1) / pl.rows_per_item;
 
-    int stages = env_int("ASCAN_STAGES", in.kind == ASCAN_KIND_BACKWARD ? 3 : 4);
+    // Item size: about `seg_tiles` tiles.  Rows at least twice that long are split into
+    // segments (needs the workspace for the per-row carry records and rows that start
+    // 16-byte aligned when the bulk loader is used); shorter rows are grouped.
+    int seg_tiles = env_int("ASCAN_SEG_TILES", 16);
+    if (seg_tiles < 1) seg_tiles = 1;
+    int64_t seg = seg_tiles * te;
+    // carry tags hold the segment number in 15 bits
+    while ((in.seqlen + seg - 1) / seg > 32767) seg *= 2;
+    const bool can_split = in.workspace && (!bulk || align_rows == 1) && env_int("ASCAN_NO_SPLIT", 0) == 0;
+    if (can_split && in.seqlen >= 2 * seg) {
+        pl.rows_per_item = 1;
+        pl.row_groups = in.rows;
+        pl.seg_elems = seg;
+        pl.segs_per_row = (in.seqlen + seg - 1) / seg;
+    } else {
+        int64_t rpi = seg / in.seqlen;
+        if (rpi < 1) rpi = 1;
+        if (bulk) rpi = (rpi + align_rows - 1) / align_rows * align_rows;
+        pl.rows_per_item = rpi;
+        pl.row_groups = (in.rows + rpi - 1) / rpi;
+        pl.seg_elems = in.seqlen;
+        pl.segs_per_row = 1;
+    }
+    pl.items = pl.row_groups * pl.segs_per_row;
+
+    int stages = env_int("ASCAN_STAGES", 2);
     if (stages < 1) stages = 1;
     if (stages > 8) stages = 8;
     pl.stages = bulk ? stages : 1;
@@ -72,10 +102,11 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     if (wpc > kMaxWarpsPerCta) wpc = kMaxWarpsPerCta;
     const int wpc_env = env_int("ASCAN_WPC", 0);
     if (wpc_env > 0 && wpc_env < wpc) wpc = wpc_env;
+    else if (wpc > 12) wpc = 12;
     if (wpc < 1) return ASCAN_ERR_UNSUPPORTED;
 
-    // One CTA per SM.  With fewer items than warps, spread the items over all SMs
-    // before filling the warps of a CTA.
+    // One persistent CTA per SM.  With fewer items than warps, spread the items over
+    // all SMs before filling the warps of a CTA.
     int64_t grid = in.sm_count;
     if (pl.items < grid * wpc) {
         int64_t w = (pl.items + grid - 1) / grid;
@@ -86,9 +117,8 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     }
     pl.warps_per_cta = wpc;
     pl.grid = static_cast<int32_t>(grid);
-    pl.tiles_per_row = 0;
     pl.smem_bytes = static_cast<uint64_t>(wpc) * wsm;
-    pl.workspace_bytes = 0;
+    pl.workspace_bytes = in.workspace ? workspace_bytes(in.rows) : 0;
     *plan = pl;
     return ASCAN_OK;
 }

@@ -1,7 +1,7 @@
 // Chunking / launch planner: pure host arithmetic that turns (rows, T, dtype, kind,
-// alignment, SM count) into a launch plan.  It replaces the reference's 12-case
-// sequence-length ladder (warp.cuh:282-380), which accepts powers of two from 32 to
-// 65536 only and fixes one CTA per row; this planner accepts any T >= 1.
+// alignment, workspace, SM count) into a launch plan.  It replaces the reference's
+// 12-case sequence-length ladder (warp.cuh:282-380), which accepts powers of two from
+// 32 to 65536 only and fixes one CTA per row; this planner accepts any T >= 1.
 #pragma once
 
 #include <stdint.h>
@@ -11,18 +11,24 @@
 namespace ascan {
 
 constexpr int kMaxSmemPerCta = 227 * 1024;   // opt-in dynamic shared memory per CTA on sm_100
-constexpr int kMaxWarpsPerCta = 12;   // kernels are compiled for at most 384 threads per CTA
+constexpr int kMaxWarpsPerCta = 12;          // kernels are compiled for at most 384 threads per CTA
+constexpr int kCtrlBytes = 256;              // control block at the start of a workspace
+constexpr int kCarryRecordBytes = 32;        // per-row carry record behind it
 
 struct PlanInput {
     int64_t rows;
     int64_t seqlen;
-    int dtype;      // ascan_dtype
-    int kind;       // ascan_kind
-    bool aligned;   // every pointer 16-byte aligned
+    int dtype;        // ascan_dtype
+    int kind;         // ascan_kind
+    bool aligned;     // every pointer 16-byte aligned
+    bool workspace;   // a workspace of workspace_bytes() is available
     int sm_count;
 };
 
 int dtype_size(int dtype);   // bytes per element, 0 if unknown
+
+// Workspace a launch over `rows` rows wants: control block + one carry record per row.
+uint64_t workspace_bytes(int64_t rows);
 
 // Fills `plan`; returns an ascan_status.
 int make_plan(const PlanInput &in, ascan_plan *plan);

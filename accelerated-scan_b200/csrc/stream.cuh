@@ -1,0 +1,673 @@
+// Warp-stream scan kernel.
+//
+// Work decomposition
+//   * The rows x T matrix is cut into ITEMS.  Short rows are grouped (an item is a
+//     few whole rows); long rows are split into segments of `seg_elems` steps (an item
+//     is one segment of one row).  Items are numbered segment-major: all first
+//     segments, then all second segments, ...  (processing order; the reverse
+//     directions start from the last segment of every row).
+//   * Persistent warps draw item numbers from a global ticket counter, so faster SMs
+//     take more items and all SMs finish together.  Without a workspace the items are
+//     dealt round-robin instead and rows are never split.
+//   * The state leaving a segment is published in a per-row record (value + tag);
+//     the warp that draws the next segment of that row reads it.  Because of the
+//     segment-major order the record is normally written long before it is needed;
+//     if it is not there yet the reader polls with a bound, records a status bit on
+//     expiry and carries on, so the kernel always terminates.
+//
+// Inside an item (see the per-tile steps in the loop below)
+//   * An item is a flat range of the matrix; fixed-size tiles of it move through the
+//     warp's own shared-memory ring.  Row boundaries inside a tile are handled by
+//     forcing the gate of the row's first processed element to zero, which resets the
+//     running state, so any T works and tiles need not divide rows.
+//   * Bulk loader: one lane issues 1-D bulk asynchronous copies (global -> shared,
+//     mbarrier completion, no multicast) up to `stages` tiles ahead, across item
+//     boundaries; results leave through bulk asynchronous stores from a
+//     double-buffered staging area.  Each lane owns NCH consecutive 16-byte chunks of a
+//     tile; with NCH odd the 16-byte shared accesses of a quarter-warp fall in
+//     distinct bank groups.
+//   * Plain loader: the same arithmetic fed by element-wise loads/stores, for data
+//     that is not 16-byte aligned.
+//   * Per tile: sequential pass over the lane's elements for the lane aggregate
+//     (A, B) of x -> A*x + B, Kogge-Stone combine across lanes by shuffles, then a
+//     second sequential pass from the lane's incoming state.  The state crossing
+//     tiles is one register per warp; there is no block-level barrier in the loop.
+//
+// Kinds: forward scan (optionally reversed), fused backward (reverse scan over the
+// gates shifted by one step plus the d_gates epilogue; shifted operands come from
+// neighbouring lanes by shuffle, tile halos from one scalar load), and the two
+// carry-only reductions used by time-sharded callers.
+#pragma once
+
+#include "common.cuh"
+
+namespace ascan {
+
+enum : int { K_SCAN = 0, K_BWD = 1, K_REDUCE = 2, K_REDUCE_BWD = 3 };
+
+// Control words at the start of the workspace (uint32 each).
+enum : int { CTRL_STATUS = 0, CTRL_TICKET = 1, CTRL_DONE = 2, CTRL_EPOCH = 3 };
+constexpr int CTRL_BYTES = 256;        // control block, then one CarryRecord per row
+constexpr int CARRY_RECORD_BYTES = 32;
+
+struct StreamParams {
+    const void *in0;         // gates
+    const void *in1;         // tokens (scan, reduce) or grad_out (backward kinds)
+    const void *in2;         // saved states (backward only)
+    void *out0;              // out (scan) or d_tokens (backward)
+    void *out1;              // d_gates (backward)
+    const void *carry_in;    // rows values of V, or null
+    const void *halo_gate;   // rows values of V, or null (backward kinds)
+    const void *halo_state;  // rows values of V, or null (backward)
+    void *carry_out;         // rows x 2 values of V (reduce kinds)
+    int64_t rows, T;
+    int64_t rows_per_item;   // rows grouped into one item when rows are not split
+    int64_t row_groups;      // ceil(rows / rows_per_item)
+    int64_t seg_elems;       // steps per segment (multiple of the tile) when rows are split
+    int64_t segs_per_row;    // 1 = rows are not split
+    int64_t items;           // row_groups * segs_per_row
+    uint32_t *ctrl;          // control words, or null (static dealing, no status)
+    unsigned char *records;  // per-row carry records (segs_per_row > 1)
+    int32_t stages;          // shared-memory stages per warp (bulk loader)
+    int32_t l2_hints;        // bits 0-1: loads (0 none, 1 evict_first, 2 evict_last); bits 2-3: stores
+};
+
+__host__ __device__ constexpr int stream_nin(int kind) { return kind == K_BWD ? 3 : 2; }
+__host__ __device__ constexpr int stream_nout(int kind) { return kind == K_SCAN ? 1 : (kind == K_BWD ? 2 : 0); }
+__host__ __device__ constexpr int stream_warp_smem(int nch, int stages, int kind, bool bulk) {
+    const int tb = 32 * nch * 16;
+    const int nstg = bulk ? stages : 1;
+    const int outbufs = bulk ? 2 : 1;
+    return nstg * stream_nin(kind) * tb + outbufs * stream_nout(kind) * tb + 128;
+}
+
+constexpr uint32_t LOAD_WAIT_POLLS = 1u << 22;
+constexpr uint32_t CARRY_WAIT_POLLS = 1u << 20;
+
+struct ItemDesc {
+    int64_t e_begin;   // first element of the item in the flat matrix
+    int64_t row0;      // row of that element
+    int64_t pos0;      // its position inside the row
+    int64_t s_log;     // segment index in processing order
+    int64_t n;         // elements in the item
+    int32_t nt;        // tiles in the item
+    bool valid;
+};
+
+template <class TR, int NCH, int KIND, bool REVERSE, bool BULK>
+__global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
+    using V = typename TR::V;
+    using Raw = typename TR::Raw;
+    constexpr int EPC = TR::EPC;
+    constexpr int K = NCH * EPC;          // elements per lane per tile
+    constexpr int TE = 32 * K;            // elements per tile
+    constexpr int TB = 32 * NCH * 16;     // bytes per tile per stream
+    constexpr bool BACK = (KIND == K_BWD || KIND == K_REDUCE_BWD);
+    constexpr bool REV = REVERSE || BACK;
+    constexpr bool REDUCE = (KIND == K_REDUCE || KIND == K_REDUCE_BWD);
+    constexpr int NIN = stream_nin(KIND);
+    constexpr int NOUT = stream_nout(KIND);
+    constexpr int OUTBUFS = BULK ? 2 : 1;
+    const int NSTG = BULK ? p.stages : 1;
+    const int WARP_SMEM = stream_warp_smem(NCH, p.stages, KIND, BULK);
+
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int lane = threadIdx.x & 31;
+    const int wib = threadIdx.x >> 5;
+    const int wpc = blockDim.x >> 5;
+    unsigned char *wsm = smem_raw + static_cast<size_t>(wib) * WARP_SMEM;
+    unsigned char *stage_base = wsm;
+    unsigned char *out_base = wsm + NSTG * NIN * TB;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(out_base + OUTBUFS * NOUT * TB);
+
+    const int64_t w = static_cast<int64_t>(blockIdx.x) * wpc + wib;
+    const int64_t W = static_cast<int64_t>(gridDim.x) * wpc;
+    const int64_t T = p.T;
+    const bool dynamic = (p.ctrl != nullptr);
+    const bool split = p.segs_per_row > 1;
+    const unsigned char *gbase[3] = {static_cast<const unsigned char *>(p.in0), static_cast<const unsigned char *>(p.in1),
+                                     static_cast<const unsigned char *>(p.in2)};
+    unsigned char *obase[2] = {static_cast<unsigned char *>(p.out0), static_cast<unsigned char *>(p.out1)};
+    const V *cin = static_cast<const V *>(p.carry_in);
+    const V *hgate = static_cast<const V *>(p.halo_gate);
+    const V *hstate = static_cast<const V *>(p.halo_state);
+
+    // tag of a carry word: launch epoch above the segment number (segments < 2^15).  A
+    // launch rewrites a row's record before reading it, so an old word with an equal tag
+    // (the epoch wraps after 2^17 launches) could only be mistaken for a new one by a
+    // reader that also arrives before its writer.
+    uint32_t epoch = 0;
+    if (dynamic) epoch = *reinterpret_cast<volatile uint32_t *>(p.ctrl + CTRL_EPOCH) << 15;
+
+    // ---- item numbers: a global ticket (dynamic) or round-robin (static)
+    // draw() only issues the atomic (its result sits in lane 0); resolve() broadcasts it.
+    // The two are called an item apart so that the atomic's latency is never waited for.
+    int64_t static_next = w;
+    auto draw = [&]() -> uint32_t {
+        uint32_t t = 0;
+        if (dynamic) {
+            if (lane == 0) t = atomicAdd(p.ctrl + CTRL_TICKET, 1u);
+        }
+        return t;
+    };
+    auto resolve = [&](uint32_t raw) -> int64_t {
+        int64_t q;
+        if (dynamic) {
+            q = __shfl_sync(0xffffffffu, raw, 0);
+        } else {
+            q = static_next;
+            static_next += W;
+        }
+        return q;
+    };
+    auto describe = [&](int64_t q) -> ItemDesc {
+        ItemDesc d;
+        d.valid = q < p.items;
+        d.e_begin = 0; d.row0 = 0; d.pos0 = 0; d.s_log = 0; d.n = 0; d.nt = 0;
+        if (!d.valid) return d;
+        if (!split) {
+            const int64_t r0 = q * p.rows_per_item;
+            int64_t r1 = r0 + p.rows_per_item;
+            if (r1 > p.rows) r1 = p.rows;
+            d.row0 = r0;
+            d.e_begin = r0 * T;
+            d.n = (r1 - r0) * T;
+        } else {
+            d.s_log = q / p.row_groups;
+            d.row0 = q - d.s_log * p.row_groups;
+            const int64_t s = REV ? p.segs_per_row - 1 - d.s_log : d.s_log;
+            d.pos0 = s * p.seg_elems;
+            d.e_begin = d.row0 * T + d.pos0;
+            const int64_t left = T - d.pos0;
+            d.n = left < p.seg_elems ? left : p.seg_elems;
+        }
+        d.nt = static_cast<int32_t>((d.n + TE - 1) / TE);
+        return d;
+    };
+
+    const int ld_hint = p.l2_hints & 3, st_hint = (p.l2_hints >> 2) & 3;
+    const uint64_t ld_pol = ld_hint == 2 ? policy_evict_last() : policy_evict_first();
+    const uint64_t st_pol = st_hint == 2 ? policy_evict_last() : policy_evict_first();
+
+    auto tile_of_step = [&](const ItemDesc &d, int i) -> int { return REV ? d.nt - 1 - i : i; };
+    auto tile_valid = [&](const ItemDesc &d, int t) -> int {
+        const int64_t left = d.n - static_cast<int64_t>(t) * TE;
+        return left < TE ? static_cast<int>(left) : TE;
+    };
+    // bulk loader: lane 0 arms the stage's mbarrier and issues one copy per stream
+    auto issue = [&](const ItemDesc &d, int t, int s) {
+        const uint32_t bytes = static_cast<uint32_t>(tile_valid(d, t)) * TR::ESIZE;
+        const int64_t goff = (d.e_begin + static_cast<int64_t>(t) * TE) * TR::ESIZE;
+        mbar_expect_tx(&bars[s], bytes * NIN);
+#pragma unroll
+        for (int k = 0; k < NIN; ++k) {
+            if (ld_hint)
+                bulk_g2s_hint(stage_base + (s * NIN + k) * TB, gbase[k] + goff, bytes, &bars[s], ld_pol);
+            else
+                bulk_g2s(stage_base + (s * NIN + k) * TB, gbase[k] + goff, bytes, &bars[s]);
+        }
+    };
+
+    if (BULK) {
+        if (lane == 0) {
+            for (int s = 0; s < NSTG; ++s) mbar_init(&bars[s], 1);
+            mbar_init_fence();
+        }
+        __syncwarp();
+    }
+
+    ItemDesc cur = describe(resolve(draw()));
+    uint32_t raw_next = draw();    // ticket of the item after `cur`, not yet looked at
+    bool nxt_ready = false;        // `nxt` has been derived from raw_next
+    ItemDesc nxt = cur;
+    auto need_next = [&]() {
+        if (!nxt_ready) {
+            nxt = describe(cur.valid ? resolve(raw_next) : p.items);
+            nxt_ready = true;
+        }
+    };
+
+    // producer cursor: tiles are issued in consumption order, at most NSTG ahead, and
+    // at most one item ahead of the consumer
+    bool prod_in_next = false;
+    int p_i = 0;          // next step of the producer's item to issue
+    int in_flight = 0;    // issued and not yet consumed
+    int ps = 0;           // ring stage the producer fills next
+    auto produce = [&]() {
+        while (in_flight < NSTG) {
+            if (!prod_in_next) {
+                if (p_i < cur.nt) {
+                    if (lane == 0) issue(cur, tile_of_step(cur, p_i), ps);
+                } else {
+                    need_next();
+                    if (!nxt.valid) break;
+                    prod_in_next = true;
+                    p_i = 0;
+                    continue;
+                }
+            } else {
+                if (p_i < nxt.nt) {
+                    if (lane == 0) issue(nxt, tile_of_step(nxt, p_i), ps);
+                } else {
+                    break;
+                }
+            }
+            ++p_i;
+            ++in_flight;
+            if (++ps == NSTG) ps = 0;
+        }
+    };
+    if (BULK && cur.valid) produce();
+
+#ifdef ASCAN_WARP_TIMING
+    unsigned long long t_begin;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_begin));
+#endif
+    bool failed = false;
+    uint32_t status_bits = 0;
+    int cs = 0;                // ring stage of the tile being consumed
+    uint32_t parity = 0;       // mbarrier phase parity of that stage
+    uint32_t step_count = 0;   // tiles consumed by this warp (selects the staging buffer)
+
+    // Item header: what an item needs from outside its own range -- the state published
+    // by the previous segment of its row and (backward kinds) the gate of the step right
+    // after it.  It is fetched during the last tile of the item before, so its latency
+    // hides behind that tile's arithmetic; `tag` tells whether the state was there yet.
+    struct ItemHeader {
+        bool have_state;
+        V x, x2, gate;
+    };
+    auto fetch_header = [&](const ItemDesc &d) -> ItemHeader {
+        ItemHeader h;
+        h.have_state = false;
+        h.x = vzero(V());
+        h.x2 = vzero(V());
+        h.gate = vone(V());
+        if (!d.valid) return h;
+        if (split && d.s_log > 0) {
+            const unsigned char *rec = p.records + d.row0 * CARRY_RECORD_BYTES;
+            const uint32_t want = epoch | static_cast<uint32_t>(d.s_log);
+            h.have_state = read_tagged(rec, 0, want, h.x);
+            if (REDUCE) h.have_state = read_tagged(rec, 1, want, h.x2) && h.have_state;
+        }
+        if (BACK) {
+            // unless the item ends its row
+            if (split && d.pos0 + d.n < T) h.gate = TR::load_one(p.in0, d.e_begin + d.n);
+        }
+        return h;
+    };
+    ItemHeader head = fetch_header(cur);
+
+    while (cur.valid && !failed) {
+        // ---------------- item prologue: incoming state, halo gate, running position
+        V x_carry = vzero(V());    // state entering the tile
+        V x2_carry = vzero(V());   // reduce kinds: response to a unit incoming state
+        V next_gate = head.gate;   // backward kinds: gate of the first element above the tile
+        if (split && cur.s_log > 0) {
+            // state published by the warp that processed the previous segment of this row
+            const unsigned char *rec = p.records + cur.row0 * CARRY_RECORD_BYTES;
+            const uint32_t want = epoch | static_cast<uint32_t>(cur.s_log);
+            bool got = head.have_state;
+            x_carry = head.x;
+            if (REDUCE) x2_carry = head.x2;
+            // not published when the header was fetched: poll, with a bound
+            for (uint32_t poll = 0; !got && poll < CARRY_WAIT_POLLS; ++poll) {
+                __nanosleep(64);
+                got = read_tagged(rec, 0, want, x_carry);
+                if (REDUCE) got = read_tagged(rec, 1, want, x2_carry) && got;
+            }
+            if (!got) {
+                status_bits |= STATUS_LOOKBACK_TIMEOUT;
+                x_carry = vzero(V());
+                x2_carry = vzero(V());
+            }
+        }
+        int64_t ts_mod, row_ts;   // (tile start) mod T and the row of the tile start
+        {
+            const int64_t pos = cur.pos0 + static_cast<int64_t>(tile_of_step(cur, 0)) * TE;
+            if (pos < T) {
+                ts_mod = pos;
+                row_ts = cur.row0;
+            } else {
+                ts_mod = pos % T;
+                row_ts = cur.row0 + pos / T;
+            }
+        }
+
+        for (int i = 0; i < cur.nt; ++i) {
+            const int t = tile_of_step(cur, i);
+            const int64_t toff = static_cast<int64_t>(t) * TE;
+            const int nvalid = tile_valid(cur, t);
+            const unsigned char *stg = stage_base + cs * NIN * TB;
+
+            // backward: the state just below the tile, needed by lane 0 for d_gates
+            V x_halo = vzero(V());
+            if (KIND == K_BWD) {
+                if (ts_mod != 0) x_halo = TR::load_one(p.in2, cur.e_begin + toff - 1);
+            }
+            // last tile of the item: fetch the header of the next one now
+            ItemHeader head_next = head;
+            if (i == cur.nt - 1) {
+                need_next();
+                head_next = fetch_header(nxt);
+            }
+
+            if (BULK) {
+                bool ok = mbar_wait_bounded(&bars[cs], parity, LOAD_WAIT_POLLS);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) {
+                    failed = true;
+                    status_bits |= STATUS_LOAD_TIMEOUT;
+                    break;
+                }
+            } else {
+                // plain loader: element-wise copy of the valid part of the tile
+                __syncwarp();
+#pragma unroll
+                for (int k = 0; k < NIN; ++k) {
+                    const Raw *src = reinterpret_cast<const Raw *>(gbase[k]) + cur.e_begin + toff;
+                    Raw *dst = reinterpret_cast<Raw *>(wsm + k * TB);
+                    for (int idx = lane; idx < nvalid; idx += 32) dst[idx] = src[idx];
+                }
+                __syncwarp();
+            }
+
+            // ---- shared -> registers
+            V a[K], b[K];
+#pragma unroll
+            for (int c = 0; c < NCH; ++c) {
+                const uint4 qa = *reinterpret_cast<const uint4 *>(stg + 0 * TB + (lane * NCH + c) * 16);
+                const uint4 qb = *reinterpret_cast<const uint4 *>(stg + 1 * TB + (lane * NCH + c) * 16);
+                TR::unpack(qa, &a[c * EPC]);
+                TR::unpack(qb, &b[c * EPC]);
+            }
+            V xp[KIND == K_BWD ? K : 1];
+            if (KIND == K_BWD) {
+#pragma unroll
+                for (int c = 0; c < NCH; ++c) {
+                    const uint4 qx = *reinterpret_cast<const uint4 *>(stg + 2 * TB + (lane * NCH + c) * 16);
+                    TR::unpack(qx, &xp[c * EPC]);
+                }
+            }
+            if (BULK) {
+                // the stage is free again: refill the ring
+                __syncwarp();
+                --in_flight;
+                if (++cs == NSTG) {
+                    cs = 0;
+                    parity ^= 1u;
+                }
+                if (lane == 0) fence_async_smem();
+                produce();
+            }
+
+            // ---- backward kinds: shift the gates by one step inside registers
+            if (BACK) {
+                const V g0 = a[0];
+                V up = shfl_down(g0, 1);
+                if (lane == 31) up = next_gate;
+#pragma unroll
+                for (int j = 0; j < K - 1; ++j) a[j] = vconj(a[j + 1]);
+                a[K - 1] = vconj(up);
+                next_gate = shfl_idx(g0, 0);
+            }
+
+            // ---- row boundaries and the ragged last tile
+            V b2[REDUCE ? K : 1];
+            if (REDUCE) {
+#pragma unroll
+                for (int j = 0; j < K; ++j) b2[j] = vzero(V());
+            }
+            const bool has_boundary = (ts_mod == 0) || (ts_mod + nvalid >= T);
+            const bool slow = has_boundary || (nvalid < TE);
+            uint32_t start_mask_lo = 0, start_mask_hi = 0;   // backward: elements that open a row
+            if (slow) {
+#pragma unroll
+                for (int j = 0; j < K; ++j) {
+                    const int o = lane * K + j;
+                    const int64_t pos = ts_mod + o;
+                    int64_t q, rem;
+                    if (T > TE) {
+                        q = pos >= T ? 1 : 0;
+                        rem = pos - (q ? T : 0);
+                    } else {
+                        const int pi = static_cast<int>(pos), ti = static_cast<int>(T);
+                        q = pi / ti;
+                        rem = pi - static_cast<int>(q) * ti;
+                    }
+                    const bool is_start = (rem == 0);
+                    const bool is_end = (rem == T - 1);
+                    const bool first = REV ? is_end : is_start;
+                    const int64_t row = row_ts + q;
+                    if (o >= nvalid) {
+                        a[j] = vone(V());
+                        b[j] = vzero(V());
+                    } else {
+                        if (first) {
+                            V a_orig = a[j];
+                            if (BACK) a_orig = hgate ? vconj(hgate[row]) : vone(V());
+                            if (cin) b[j] = vfma(a_orig, cin[row], b[j]);
+                            if (REDUCE) b2[j] = a_orig;
+                            a[j] = vzero(V());
+                        }
+                        if (KIND == K_BWD && is_start) {
+                            if (j < 32) start_mask_lo |= 1u << (j & 31);
+                            else start_mask_hi |= 1u << (j & 31);
+                        }
+                    }
+                }
+            }
+
+            // ---- pass 1: lane aggregate in processing order
+            constexpr int JF = REV ? K - 1 : 0;
+            V A = a[JF], B = b[JF];
+            V B2 = REDUCE ? b2[JF] : vzero(V());
+#pragma unroll
+            for (int q = 1; q < K; ++q) {
+                const int j = REV ? K - 1 - q : q;
+                B = vfma(a[j], B, b[j]);
+                if (REDUCE) B2 = vfma(a[j], B2, b2[j]);
+                A = vmul(A, a[j]);
+            }
+            // the warp's incoming state enters through the first lane in processing order
+            const int ll = REV ? 31 - lane : lane;
+            if (ll == 0) {
+                B = vfma(A, x_carry, B);
+                if (REDUCE) B2 = vfma(A, x2_carry, B2);
+            }
+            // ---- Kogge-Stone inclusive combine across lanes
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const V Ap = REV ? shfl_down(A, d) : shfl_up(A, d);
+                const V Bp = REV ? shfl_down(B, d) : shfl_up(B, d);
+                V B2p = vzero(V());
+                if (REDUCE) B2p = REV ? shfl_down(B2, d) : shfl_up(B2, d);
+                if (ll >= d) {
+                    B = vfma(A, Bp, B);
+                    if (REDUCE) B2 = vfma(A, B2p, B2);
+                    if (d < 16) A = vmul(A, Ap);
+                }
+            }
+            // state entering this lane = inclusive result of the previous lane
+            V x = REV ? shfl_down(B, 1) : shfl_up(B, 1);
+            if (ll == 0) x = x_carry;
+            V x2 = vzero(V());
+            if (REDUCE) {
+                x2 = REV ? shfl_down(B2, 1) : shfl_up(B2, 1);
+                if (ll == 0) x2 = x2_carry;
+            }
+            x_carry = shfl_idx(B, REV ? 0 : 31);
+            if (REDUCE) x2_carry = shfl_idx(B2, REV ? 0 : 31);
+
+            if (!REDUCE) {
+                // ---- pass 2: the recurrence itself from the lane's incoming state
+#pragma unroll
+                for (int q = 0; q < K; ++q) {
+                    const int j = REV ? K - 1 - q : q;
+                    x = vfma(a[j], x, b[j]);
+                    b[j] = x;
+                }
+                if (KIND == K_BWD) {
+                    // d_gates[t] = conj(x[t-1]) * g[t]: the previous state comes from the
+                    // element below (neighbouring lane by shuffle, tile halo for lane 0)
+                    V dn = shfl_up(xp[K - 1], 1);
+                    if (lane == 0) dn = x_halo;
+#pragma unroll
+                    for (int j = K - 1; j > 0; --j) a[j] = vmul(vconj(xp[j - 1]), b[j]);
+                    a[0] = vmul(vconj(dn), b[0]);
+                    if (start_mask_lo | start_mask_hi) {
+#pragma unroll
+                        for (int j = 0; j < K; ++j) {
+                            const bool st = j < 32 ? (start_mask_lo >> (j & 31)) & 1u : (start_mask_hi >> (j & 31)) & 1u;
+                            if (st) {
+                                const int64_t pos = ts_mod + lane * K + j;
+                                const int64_t row = row_ts + (T > TE ? (pos >= T ? 1 : 0) : pos / T);
+                                const V xs = hstate ? hstate[row] : vzero(V());
+                                a[j] = vmul(vconj(xs), b[j]);
+                            }
+                        }
+                    }
+                }
+                // ---- registers -> staging -> global
+                unsigned char *ob = out_base + (BULK ? static_cast<int>(step_count & 1u) : 0) * NOUT * TB;
+                if (BULK) {
+                    if (lane == 0) bulk_wait_read<1>();
+                }
+                __syncwarp();
+#pragma unroll
+                for (int c = 0; c < NCH; ++c) {
+                    *reinterpret_cast<uint4 *>(ob + (lane * NCH + c) * 16) = TR::pack(&b[c * EPC]);
+                    if (NOUT > 1) *reinterpret_cast<uint4 *>(ob + TB + (lane * NCH + c) * 16) = TR::pack(&a[c * EPC]);
+                }
+                if (BULK) {
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        const uint32_t bytes = static_cast<uint32_t>(nvalid) * TR::ESIZE;
+                        const int64_t goff = (cur.e_begin + toff) * TR::ESIZE;
+#pragma unroll
+                        for (int k = 0; k < NOUT; ++k) {
+                            if (st_hint)
+                                bulk_s2g_hint(obase[k] + goff, ob + k * TB, bytes, st_pol);
+                            else
+                                bulk_s2g(obase[k] + goff, ob + k * TB, bytes);
+                        }
+                        bulk_commit();
+                    }
+                } else {
+                    __syncwarp();
+#pragma unroll
+                    for (int k = 0; k < NOUT; ++k) {
+                        const Raw *src = reinterpret_cast<const Raw *>(ob + k * TB);
+                        Raw *dst = reinterpret_cast<Raw *>(obase[k]) + cur.e_begin + toff;
+                        for (int idx = lane; idx < nvalid; idx += 32) dst[idx] = src[idx];
+                    }
+                }
+            } else if (has_boundary) {
+                // reduce kinds: only tiles that finish a row need the element states
+                V *cout = static_cast<V *>(p.carry_out);
+#pragma unroll
+                for (int q = 0; q < K; ++q) {
+                    const int j = REV ? K - 1 - q : q;
+                    x = vfma(a[j], x, b[j]);
+                    x2 = vfma(a[j], x2, b2[j]);
+                    const int o = lane * K + j;
+                    const int64_t pos = ts_mod + o;
+                    int64_t qq, rem;
+                    if (T > TE) {
+                        qq = pos >= T ? 1 : 0;
+                        rem = pos - (qq ? T : 0);
+                    } else {
+                        const int pi = static_cast<int>(pos), ti = static_cast<int>(T);
+                        qq = pi / ti;
+                        rem = pi - static_cast<int>(qq) * ti;
+                    }
+                    const bool last = REV ? (rem == 0) : (rem == T - 1);
+                    if (last && o < nvalid) {
+                        const int64_t row = row_ts + qq;
+                        cout[2 * row] = x2;
+                        cout[2 * row + 1] = x;
+                    }
+                }
+            }
+            ++step_count;
+            head = head_next;
+
+            // ---- advance the running tile position
+            if (!REV) {
+                ts_mod += TE;
+                if (ts_mod >= T) {
+                    if (T > TE) {
+                        ts_mod -= T;
+                        row_ts += 1;
+                    } else {
+                        row_ts += ts_mod / T;
+                        ts_mod %= T;
+                    }
+                }
+            } else {
+                ts_mod -= TE;
+                if (ts_mod < 0) {
+                    if (T > TE) {
+                        ts_mod += T;
+                        row_ts -= 1;
+                    } else {
+                        const int64_t k = (-ts_mod + T - 1) / T;
+                        ts_mod += k * T;
+                        row_ts -= k;
+                    }
+                }
+            }
+        }
+        if (failed) break;
+
+        // ---------------- item epilogue: publish the outgoing state, move to the next item
+        if (split && cur.s_log + 1 < p.segs_per_row) {
+            if (lane == 0) {
+                unsigned char *rec = p.records + cur.row0 * CARRY_RECORD_BYTES;
+                const uint32_t tag = epoch | static_cast<uint32_t>(cur.s_log + 1);
+                publish_tagged(rec, 0, x_carry, tag);
+                if (REDUCE) publish_tagged(rec, 1, x2_carry, tag);
+            }
+        }
+        need_next();
+        cur = nxt;
+        raw_next = cur.valid ? draw() : 0u;
+        nxt_ready = false;
+        if (prod_in_next) {
+            prod_in_next = false;      // the producer's item is now the current one
+        } else {
+            p_i = 0;                   // the producer had nothing to run ahead into
+        }
+        if (BULK && cur.valid) produce();
+    }
+
+    if (BULK) {
+        if (lane == 0) bulk_wait_read<0>();
+        __syncwarp();
+    }
+    if (dynamic && lane == 0) {
+        if (status_bits) atomicOr(p.ctrl + CTRL_STATUS, status_bits);
+#ifdef ASCAN_WARP_TIMING
+        {
+            unsigned long long t_end;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_end));
+            unsigned long long *trec = reinterpret_cast<unsigned long long *>(
+                reinterpret_cast<unsigned char *>(p.ctrl) + CTRL_BYTES + p.rows * CARRY_RECORD_BYTES) + 2 * w;
+            trec[0] = t_begin;
+            trec[1] = t_end;
+        }
+#endif
+        // the last warp to leave rearms the ticket for the next launch and opens a new epoch
+        __threadfence();
+        const uint32_t done = atomicAdd(p.ctrl + CTRL_DONE, 1u);
+        if (done == static_cast<uint32_t>(W - 1)) {
+            p.ctrl[CTRL_TICKET] = 0;
+            p.ctrl[CTRL_DONE] = 0;
+            p.ctrl[CTRL_EPOCH] = p.ctrl[CTRL_EPOCH] + 1;
+            __threadfence();
+        }
+    }
+}
+
+}  // namespace ascan

@@ -57,19 +57,21 @@ typedef enum {
  * of warp.cuh:282-380.  Pure host arithmetic, usable without a GPU when
  * sm_count > 0 is passed. */
 typedef struct {
-    int32_t kernel;            /* 0 = row-stream (each warp owns whole rows), 1 = split-row (rows span CTAs, look-back) */
+    int32_t kernel;            /* 0 = warp-stream kernel                                   */
     int32_t loader;            /* 0 = bulk-async copies into shared-memory stages, 1 = plain element loads (unaligned data) */
-    int32_t chunks_per_lane;   /* 16-byte chunks each lane owns per tile                 */
-    int32_t stages;            /* shared-memory stages per warp                           */
+    int32_t chunks_per_lane;   /* 16-byte chunks each lane owns per tile                  */
+    int32_t stages;            /* shared-memory stages per warp                            */
     int32_t warps_per_cta;
-    int32_t grid;              /* CTAs                                                    */
-    int32_t tile_elems;        /* elements per warp tile                                  */
-    int32_t reserved;
-    int64_t rows_per_item;     /* rows grouped so every item starts 16-byte aligned       */
-    int64_t items;
-    int64_t tiles_per_row;     /* split-row kernel only                                   */
-    uint64_t smem_bytes;       /* dynamic shared memory per CTA                           */
-    uint64_t workspace_bytes;  /* scratch the launch needs (0 for the row-stream kernel)  */
+    int32_t grid;              /* persistent CTAs                                          */
+    int32_t tile_elems;        /* elements per warp tile                                   */
+    int32_t dynamic;           /* 1 = items drawn from a ticket counter in the workspace   */
+    int64_t rows_per_item;     /* rows grouped into one item when rows are not split       */
+    int64_t row_groups;        /* ceil(rows / rows_per_item)                               */
+    int64_t seg_elems;         /* steps per segment when rows are split                    */
+    int64_t segs_per_row;      /* 1 = rows are not split                                   */
+    int64_t items;             /* row_groups * segs_per_row                                */
+    uint64_t smem_bytes;       /* dynamic shared memory per CTA                            */
+    uint64_t workspace_bytes;  /* scratch the plan uses (0 = none)                         */
 } ascan_plan;
 
 /* Library version: major*10000 + minor*100 + patch. */
@@ -85,9 +87,10 @@ const char *ascan_strerror(int status);
  *   carry_in (nullable): `rows` values of the compute type (float, or float2 for
  *            ASCAN_C64): the state before the first step of every row (after the
  *            last step when reverse).  NULL means zero.
- *   ws/ws_bytes: scratch of at least ascan_workspace_bytes(...) bytes, 256-byte
- *            aligned, zero-filled once by the caller before its first use; may be
- *            NULL when that size is 0.
+ *   ws/ws_bytes: scratch of ascan_workspace_bytes(...) bytes, 256-byte aligned,
+ *            zero-filled ONCE by the caller before its first use and then left
+ *            alone (the kernels rearm it); one workspace must not be shared by
+ *            launches that can overlap (use one per stream).  NULL = static mode.
  */
 int ascan_forward(const void *gates, const void *tokens, void *out,
                   int64_t rows, int64_t seqlen, int dtype, int reverse,
@@ -130,15 +133,22 @@ int ascan_reduce_backward(const void *gates, const void *grad_out,
                           int64_t rows, int64_t seqlen, int dtype,
                           void *ws, size_t ws_bytes, void *stream);
 
-/* Scratch bytes a call of `kind` with these sizes needs (0 = none). */
+/*
+ * Scratch bytes a call of `kind` with these sizes can use: a control block
+ * (status word, work ticket) plus one carry record per row.  With at least that
+ * much scratch the kernels balance work over the SMs dynamically and split long
+ * rows across warps; with less (or NULL) they fall back to a static deal of whole
+ * rows, which is correct but slower.
+ */
 size_t ascan_workspace_bytes(int64_t rows, int64_t seqlen, int dtype, int kind);
 
 /*
- * The plan the library would use.  `aligned` says whether every pointer is
- * 16-byte aligned; sm_count <= 0 queries the current device.  Host only.
+ * The plan the library would use.  flags: bit 0 = every pointer is 16-byte
+ * aligned, bit 1 = a workspace of ascan_workspace_bytes() is supplied;
+ * sm_count <= 0 queries the current device.  Host only.
  */
 int ascan_plan_describe(int64_t rows, int64_t seqlen, int dtype, int kind,
-                        int aligned, int sm_count, ascan_plan *plan);
+                        int flags, int sm_count, ascan_plan *plan);
 
 /*
  * Reads the device status word at the start of a workspace after synchronising

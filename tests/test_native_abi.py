@@ -57,16 +57,26 @@ def test_planner_invariants(T, dtype, kind):
         assert pl["grid"] >= 1 and pl["warps_per_cta"] >= 1
         assert pl["warps_per_cta"] * 32 <= 384
         assert pl["smem_bytes"] <= 227 * 1024
-        assert pl["items"] * pl["rows_per_item"] >= rows
         assert pl["tile_elems"] == 32 * pl["chunks_per_lane"] * (16 // esize)
+        assert pl["items"] == pl["row_groups"] * pl["segs_per_row"]
+        assert pl["row_groups"] * pl["rows_per_item"] >= rows
+        assert pl["segs_per_row"] * pl["seg_elems"] >= T
+        assert pl["dynamic"] == 1 and pl["workspace_bytes"] == 256 + 32 * rows
+        if pl["segs_per_row"] > 1:
+            # split rows: one row per item, segments are whole tiles
+            assert pl["rows_per_item"] == 1 and pl["seg_elems"] % pl["tile_elems"] == 0
+            assert (pl["segs_per_row"] - 1) * pl["seg_elems"] < T
         if pl["loader"] == 0:
             # bulk copies: every item starts on a 16-byte boundary and the matrix ends on one
             assert (pl["rows_per_item"] * T * esize) % 16 == 0
+            assert (pl["seg_elems"] * esize) % 16 == 0 or pl["segs_per_row"] == 1
             assert (rows * T * esize) % 16 == 0
         # no more warps than items, spread over the SMs
         assert pl["grid"] * pl["warps_per_cta"] <= max(pl["items"], 1) + pl["warps_per_cta"] * 148
         unaligned = _native.plan(rows, T, dtype, kind, aligned=False, sm_count=148)
-        assert unaligned["loader"] == 1 and unaligned["rows_per_item"] == 1
+        assert unaligned["loader"] == 1
+        static = _native.plan(rows, T, dtype, kind, workspace=False, sm_count=148)
+        assert static["dynamic"] == 0 and static["segs_per_row"] == 1 and static["workspace_bytes"] == 0
 
 
 def test_planner_rejects_bad_input():
