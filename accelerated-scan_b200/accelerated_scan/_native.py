@@ -65,6 +65,8 @@ def _load():
     lib.ascan_plan_describe.argtypes = [i64, i64, i32, i32, i32, i32, ctypes.POINTER(Plan)]
     lib.ascan_check.restype = i32
     lib.ascan_check.argtypes = [vp, vp]
+    lib.ascan_forward_no_alloc.restype = i32
+    lib.ascan_forward_no_alloc.argtypes = [vp, vp, vp, i64, i64, i32, i32, vp]
     return lib
 
 
@@ -73,6 +75,7 @@ lib = _load()
 EXPORTS = (
     "ascan_version", "ascan_strerror", "ascan_forward", "ascan_backward", "ascan_reduce_forward",
     "ascan_reduce_backward", "ascan_workspace_bytes", "ascan_plan_describe", "ascan_check",
+    "ascan_forward_no_alloc",
 )
 
 

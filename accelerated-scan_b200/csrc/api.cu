@@ -140,6 +140,8 @@ const char *ascan_strerror(int status) {
         case ASCAN_ERR_TIMEOUT: return "a bounded device-side wait expired";
         case ASCAN_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
         case ASCAN_ERR_DEVICE: return "no usable sm_100 device";
+        case ASCAN_ERR_TOO_LARGE:
+            return "more rows than the built-in scratch of ascan_forward_no_alloc holds (16384)";
         default: return "unknown status";
     }
 }
@@ -256,6 +258,70 @@ int ascan_check(void *ws, void *stream) {
     if (host[0] == 0) return ASCAN_OK;
     if (cudaMemsetAsync(ws, 0, sizeof(uint32_t), st) != cudaSuccess) return ASCAN_ERR_LAUNCH;
     return ASCAN_ERR_TIMEOUT;
+}
+
+// ---------------------------------------------------------------------------
+// Forward scan for callers that cannot supply scratch memory.
+//
+// The other entry points leave allocation to the caller: to get dynamic load balancing
+// and split rows they want a zero-filled workspace.  Some callers cannot provide one:
+// a host that reserved all device memory at start-up (a later cudaMalloc fails), a
+// serving loop that may not call cudaMalloc because it synchronises the whole device,
+// or a binding that can only pass the input and output buffers it already owns.  For
+// them the workspace below is part of the library image: every GPU that loads the
+// library holds these bytes until the process exits.
+constexpr int64_t kNoAllocMaxRows = 16384;
+static __device__ __align__(256) unsigned char g_no_alloc_scratch[CTRL_BYTES + CARRY_RECORD_BYTES * kNoAllocMaxRows];
+
+// Device address of g_no_alloc_scratch on the current device.  In host code the array's
+// name is only a handle for the runtime, not a pointer a kernel could use, so the address
+// is asked for once per device (with that device current) and remembered.
+static int no_alloc_scratch_address(unsigned char **out) {
+    static std::mutex mu;
+    static unsigned char *addr[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return ASCAN_ERR_DEVICE;
+    if (dev < 0 || dev >= 64) return ASCAN_ERR_DEVICE;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!addr[dev]) {
+        void *ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_no_alloc_scratch) != cudaSuccess || !ptr) {
+            cudaGetLastError();
+            return ASCAN_ERR_DEVICE;
+        }
+        addr[dev] = static_cast<unsigned char *>(ptr);
+    }
+    *out = addr[dev];
+    return ASCAN_OK;
+}
+
+int ascan_forward_no_alloc(const void *gates, const void *tokens, void *out, int64_t rows, int64_t seqlen, int dtype,
+                           int reverse, void *stream) {
+    if (rows < 0 || seqlen < 1 || dtype_size(dtype) == 0) return ASCAN_ERR_INVALID_ARG;
+    if (rows > kNoAllocMaxRows) return ASCAN_ERR_TOO_LARGE;
+    if (rows == 0) return ASCAN_OK;
+    if (!gates || !tokens || !out) return ASCAN_ERR_INVALID_ARG;
+    unsigned char *scratch = nullptr;
+    int rc = no_alloc_scratch_address(&scratch);
+    if (rc != ASCAN_OK) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // The array keeps whatever the previous call left.  The status word, the work ticket
+    // and the exit counter must start at zero; the launch epoch behind them must survive,
+    // because it is what tells this call's carry records from older ones.
+    if (cudaMemsetAsync(scratch, 0, 3 * sizeof(uint32_t), st) != cudaSuccess) {
+        cudaGetLastError();
+        return ASCAN_ERR_LAUNCH;
+    }
+    ascan_plan pl;
+    const bool al = aligned16(gates) && aligned16(tokens) && aligned16(out);
+    rc = plan_for(rows, seqlen, dtype, ASCAN_KIND_FORWARD, al, scratch, sizeof(g_no_alloc_scratch), &pl);
+    if (rc != ASCAN_OK) return rc;
+    StreamParams p = {};
+    p.in0 = gates;
+    p.in1 = tokens;
+    p.out0 = out;
+    fill_common(p, pl, rows, seqlen, scratch);
+    return reverse ? launch_dtype<K_SCAN, true>(dtype, p, pl, st) : launch_dtype<K_SCAN, false>(dtype, p, pl, st);
 }
 
 }  // extern "C"

@@ -33,7 +33,8 @@ typedef enum {
     ASCAN_ERR_LAUNCH = 3,        /* the CUDA runtime rejected the launch                  */
     ASCAN_ERR_TIMEOUT = 4,       /* a bounded device-side wait gave up (see ascan_check)  */
     ASCAN_ERR_WORKSPACE = 5,     /* workspace missing, misaligned or too small            */
-    ASCAN_ERR_DEVICE = 6         /* no sm_100 device / runtime query failed               */
+    ASCAN_ERR_DEVICE = 6,        /* no sm_100 device / runtime query failed               */
+    ASCAN_ERR_TOO_LARGE = 7      /* more rows than ascan_forward_no_alloc's scratch holds */
 } ascan_status;
 
 /* Storage type of gates/tokens/outputs.  Arithmetic is always fp32 (complex64:
@@ -157,6 +158,25 @@ int ascan_plan_describe(int64_t rows, int64_t seqlen, int dtype, int kind,
  * cleared).  Optional: the hot path never synchronises.
  */
 int ascan_check(void *ws, void *stream);
+
+/*
+ * Forward scan that needs no workspace from the caller.  It has no counterpart in
+ * the reference.  It is for callers that cannot hand over scratch memory: hosts
+ * that reserve all device memory at start-up (so a later cudaMalloc fails),
+ * serving loops that must not call cudaMalloc because it synchronises the device,
+ * and bindings that can only pass the buffers they already own.  The scratch is a
+ * fixed array inside the library (about 0.5 MB on every GPU that loads it), which
+ * limits the call to rows <= 16384; more rows return ASCAN_ERR_TOO_LARGE.  The
+ * function allocates nothing.  Its first call on a device looks up the array's
+ * device address (cudaGetSymbolAddress); make that first call outside any stream
+ * capture.  All calls on a device share the one array, so two calls that may run
+ * at the same time on that device (different streams or threads) race; order them.
+ * Same arithmetic and results as ascan_forward with a workspace; carry_in is not
+ * supported and device-side timeouts are not reported.
+ */
+int ascan_forward_no_alloc(const void *gates, const void *tokens, void *out,
+                           int64_t rows, int64_t seqlen, int dtype, int reverse,
+                           void *stream);
 
 #ifdef __cplusplus
 }

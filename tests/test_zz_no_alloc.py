@@ -1,0 +1,56 @@
+"""ascan_forward_no_alloc: the forward scan for callers that cannot provide scratch
+memory (hosts that reserved all device memory up front, loops that must not call
+cudaMalloc, bindings that only own their input and output buffers).  Its scratch is a
+fixed array inside the library, shared by every call on the device.
+
+The test calls the entry point through the C ABI twice in a row and compares each
+result with the regular entry point (caller-supplied workspace) on the same inputs;
+the second call runs on the leftovers of the first.  Collected last on purpose."""
+import ctypes
+
+import pytest
+import torch
+
+from helpers import real_inputs, rel_err, to_np
+
+pytestmark = pytest.mark.gpu
+
+FP32_REL = 1e-5
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr())
+
+
+@pytest.mark.parametrize("shape,dtype", [((2, 32, 65536), torch.float32), ((1, 48, 40000), torch.bfloat16)])
+def test_no_alloc_matches_workspace_entry_point(cuda_device, shape, dtype):
+    from accelerated_scan import _native
+
+    lib = _native.lib
+    rows, T = shape[0] * shape[1], shape[2]
+    code = _native.DTYPE_CODE[dtype]
+    # long rows: both entry points split them into segments and pass carries through scratch
+    assert _native.plan(rows, T, code, _native.KIND_FORWARD)["segs_per_row"] > 1
+    stream = ctypes.c_void_p(torch.cuda.current_stream(cuda_device).cuda_stream)
+    for call, seed in enumerate((21, 22)):
+        gates, tokens, _ = real_inputs(seed, shape, law="near_one", dtype=dtype, grad=False)
+        g, x = gates.to(cuda_device), tokens.to(cuda_device)
+        for reverse in (0, 1):
+            want = torch.empty_like(x)
+            _native.forward(g, x, want, reverse=bool(reverse))
+            got = torch.full_like(x, float("nan"))
+            rc = lib.ascan_forward_no_alloc(_ptr(g), _ptr(x), _ptr(got), rows, T, code, reverse, stream)
+            assert rc == 0, _native.strerror(rc)
+            torch.cuda.synchronize(cuda_device)
+            assert rel_err(to_np(got), to_np(want)) <= FP32_REL, (call, reverse)
+            assert torch.equal(got, want), (call, reverse)
+
+
+def test_no_alloc_rejects_too_many_rows(cuda_device):
+    from accelerated_scan import _native
+
+    x = torch.zeros(8, device=cuda_device)
+    rc = _native.lib.ascan_forward_no_alloc(_ptr(x), _ptr(x), _ptr(x), 16385, 8, _native.F32, 0, None)
+    assert rc == 7
+    assert "16384" in _native.strerror(rc)
+    assert _native.lib.ascan_forward_no_alloc(_ptr(x), _ptr(x), _ptr(x), 4, 0, _native.F32, 0, None) == 1
