@@ -33,6 +33,7 @@ class Plan(ctypes.Structure):
         ("stages", ctypes.c_int32), ("warps_per_cta", ctypes.c_int32), ("grid", ctypes.c_int32),
         ("tile_elems", ctypes.c_int32), ("dynamic", ctypes.c_int32),
         ("rows_per_item", ctypes.c_int64), ("row_groups", ctypes.c_int64), ("seg_elems", ctypes.c_int64),
+        ("fine_elems", ctypes.c_int64), ("coarse_segs", ctypes.c_int64), ("fine_segs", ctypes.c_int64),
         ("segs_per_row", ctypes.c_int64), ("items", ctypes.c_int64),
         ("smem_bytes", ctypes.c_uint64), ("workspace_bytes", ctypes.c_uint64),
     ]

@@ -48,26 +48,32 @@ static int ensure_smem(const void *fn, size_t bytes) {
     return ASCAN_OK;
 }
 
-template <class TR, int NCH, int KIND, bool REVERSE, bool BULK>
+template <class TR, int NCH, int KIND, bool REVERSE, bool BULK, bool INTERIOR>
 static int launch_one(const StreamParams &p, const ascan_plan &pl, cudaStream_t stream) {
-    auto kfn = stream_kernel<TR, NCH, KIND, REVERSE, BULK>;
+    auto kfn = stream_kernel<TR, NCH, KIND, REVERSE, BULK, INTERIOR>;
     int rc = ensure_smem(reinterpret_cast<const void *>(kfn), pl.smem_bytes);
     if (rc != ASCAN_OK) return rc;
     kfn<<<pl.grid, pl.warps_per_cta * 32, pl.smem_bytes, stream>>>(p);
     return cudaGetLastError() == cudaSuccess ? ASCAN_OK : ASCAN_ERR_LAUNCH;
 }
 
+// INTERIOR: items that group several rows have row boundaries inside their tiles.
+template <class TR, int NCH, int KIND, bool REVERSE, bool BULK>
+static int launch_interior(const StreamParams &p, const ascan_plan &pl, cudaStream_t stream) {
+    return pl.rows_per_item > 1 ? launch_one<TR, NCH, KIND, REVERSE, BULK, true>(p, pl, stream)
+                                : launch_one<TR, NCH, KIND, REVERSE, BULK, false>(p, pl, stream);
+}
+
 template <class TR, int NCH, int KIND, bool REVERSE>
 static int launch_loader(const StreamParams &p, const ascan_plan &pl, cudaStream_t stream) {
-    return pl.loader == 0 ? launch_one<TR, NCH, KIND, REVERSE, true>(p, pl, stream)
-                          : launch_one<TR, NCH, KIND, REVERSE, false>(p, pl, stream);
+    return pl.loader == 0 ? launch_interior<TR, NCH, KIND, REVERSE, true>(p, pl, stream)
+                          : launch_interior<TR, NCH, KIND, REVERSE, false>(p, pl, stream);
 }
 
 template <class TR, int KIND, bool REVERSE>
 static int launch_nch(const StreamParams &p, const ascan_plan &pl, cudaStream_t stream) {
     switch (pl.chunks_per_lane) {
         case 3: return launch_loader<TR, 3, KIND, REVERSE>(p, pl, stream);
-        case 5: return launch_loader<TR, 5, KIND, REVERSE>(p, pl, stream);
         default: return ASCAN_ERR_UNSUPPORTED;
     }
 }
@@ -95,8 +101,9 @@ static bool workspace_usable(const void *ws, size_t ws_bytes, int64_t rows) {
 }
 
 static int plan_for(int64_t rows, int64_t seqlen, int dtype, int kind, bool aligned, const void *ws, size_t ws_bytes,
-                    ascan_plan *pl) {
+                    ascan_plan *pl, bool reverse = false) {
     PlanInput in;
+    in.reverse = reverse;
     in.rows = rows;
     in.seqlen = seqlen;
     in.dtype = dtype;
@@ -115,6 +122,9 @@ static void fill_common(StreamParams &p, const ascan_plan &pl, int64_t rows, int
     p.rows_per_item = pl.rows_per_item;
     p.row_groups = pl.row_groups;
     p.seg_elems = pl.seg_elems;
+    p.fine_elems = pl.fine_elems;
+    p.coarse_segs = pl.coarse_segs;
+    p.fine_segs = pl.fine_segs;
     p.segs_per_row = pl.segs_per_row;
     p.items = pl.items;
     p.ctrl = pl.dynamic ? static_cast<uint32_t *>(ws) : nullptr;
@@ -153,7 +163,7 @@ int ascan_forward(const void *gates, const void *tokens, void *out, int64_t rows
     if (!gates || !tokens || !out) return ASCAN_ERR_INVALID_ARG;
     ascan_plan pl;
     const bool al = aligned16(gates) && aligned16(tokens) && aligned16(out);
-    int rc = plan_for(rows, seqlen, dtype, ASCAN_KIND_FORWARD, al, ws, ws_bytes, &pl);
+    int rc = plan_for(rows, seqlen, dtype, ASCAN_KIND_FORWARD, al, ws, ws_bytes, &pl, reverse != 0);
     if (rc != ASCAN_OK) return rc;
     StreamParams p = {};
     p.in0 = gates;
@@ -241,6 +251,7 @@ int ascan_plan_describe(int64_t rows, int64_t seqlen, int dtype, int kind, int f
     in.kind = kind;
     in.aligned = (flags & 1) != 0;
     in.workspace = (flags & 2) != 0;
+    in.reverse = (flags & 4) != 0;
     in.sm_count = sm_count;
     if (sm_count <= 0) {
         int rc = cached_sm_count(&in.sm_count);
@@ -314,7 +325,7 @@ int ascan_forward_no_alloc(const void *gates, const void *tokens, void *out, int
     }
     ascan_plan pl;
     const bool al = aligned16(gates) && aligned16(tokens) && aligned16(out);
-    rc = plan_for(rows, seqlen, dtype, ASCAN_KIND_FORWARD, al, scratch, sizeof(g_no_alloc_scratch), &pl);
+    rc = plan_for(rows, seqlen, dtype, ASCAN_KIND_FORWARD, al, scratch, sizeof(g_no_alloc_scratch), &pl, reverse != 0);
     if (rc != ASCAN_OK) return rc;
     StreamParams p = {};
     p.in0 = gates;

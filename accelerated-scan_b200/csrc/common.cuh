@@ -72,6 +72,24 @@ __device__ __forceinline__ void publish_tagged(unsigned char *rec, int slot, flo
     st_relaxed_u64(rec + slot * 16, tagged_word(v.x, tag));
     st_relaxed_u64(rec + slot * 16 + 8, tagged_word(v.y, tag));
 }
+// The words of one value, fetched now and checked later (see decode_tagged).
+struct TaggedWords {
+    uint64_t w0, w1;
+};
+__device__ __forceinline__ TaggedWords fetch_tagged(const unsigned char *rec, int slot, bool two_words) {
+    TaggedWords t;
+    t.w0 = ld_relaxed_u64(rec + slot * 16);
+    t.w1 = two_words ? ld_relaxed_u64(rec + slot * 16 + 8) : 0;
+    return t;
+}
+__device__ __forceinline__ bool decode_tagged(const TaggedWords &t, uint32_t tag, float &v) {
+    v = __uint_as_float(static_cast<uint32_t>(t.w0));
+    return static_cast<uint32_t>(t.w0 >> 32) == tag;
+}
+__device__ __forceinline__ bool decode_tagged(const TaggedWords &t, uint32_t tag, float2 &v) {
+    v = make_float2(__uint_as_float(static_cast<uint32_t>(t.w0)), __uint_as_float(static_cast<uint32_t>(t.w1)));
+    return static_cast<uint32_t>(t.w0 >> 32) == tag && static_cast<uint32_t>(t.w1 >> 32) == tag;
+}
 // Returns true and fills `v` when every word of the value carries `tag`.
 __device__ __forceinline__ bool read_tagged(const unsigned char *rec, int slot, uint32_t tag, float &v) {
     const uint64_t w = ld_relaxed_u64(rec + slot * 16);
@@ -105,6 +123,12 @@ struct TraitsF32 {
     __device__ __forceinline__ static V load_one(const void *base, int64_t i) {
         return __ldg(reinterpret_cast<const float *>(base) + i);
     }
+    // load_raw + decode = load_one, split so that the conversion (the first use of the
+    // loaded register) can sit where the value is needed instead of right after the load
+    __device__ __forceinline__ static Raw load_raw(const void *base, int64_t i) {
+        return __ldg(reinterpret_cast<const uint32_t *>(base) + i);
+    }
+    __device__ __forceinline__ static V decode(Raw r) { return __uint_as_float(r); }
 };
 
 struct TraitsBF16 {
@@ -133,6 +157,10 @@ struct TraitsBF16 {
         const uint16_t r = __ldg(reinterpret_cast<const uint16_t *>(base) + i);
         return __uint_as_float(static_cast<uint32_t>(r) << 16);
     }
+    __device__ __forceinline__ static Raw load_raw(const void *base, int64_t i) {
+        return __ldg(reinterpret_cast<const uint16_t *>(base) + i);
+    }
+    __device__ __forceinline__ static V decode(Raw r) { return __uint_as_float(static_cast<uint32_t>(r) << 16); }
 };
 
 struct TraitsF16 {
@@ -162,6 +190,10 @@ struct TraitsF16 {
         const unsigned short r = __ldg(reinterpret_cast<const unsigned short *>(base) + i);
         return __half2float(__ushort_as_half(r));
     }
+    __device__ __forceinline__ static Raw load_raw(const void *base, int64_t i) {
+        return __ldg(reinterpret_cast<const unsigned short *>(base) + i);
+    }
+    __device__ __forceinline__ static V decode(Raw r) { return __half2float(__ushort_as_half(r)); }
 };
 
 struct TraitsC64 {
@@ -179,6 +211,12 @@ struct TraitsC64 {
     }
     __device__ __forceinline__ static V load_one(const void *base, int64_t i) {
         return __ldg(reinterpret_cast<const float2 *>(base) + i);
+    }
+    __device__ __forceinline__ static Raw load_raw(const void *base, int64_t i) {
+        return __ldg(reinterpret_cast<const unsigned long long *>(base) + i);
+    }
+    __device__ __forceinline__ static V decode(Raw r) {
+        return make_float2(__uint_as_float(static_cast<uint32_t>(r)), __uint_as_float(static_cast<uint32_t>(r >> 32)));
     }
 };
 

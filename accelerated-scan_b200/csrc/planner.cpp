@@ -47,14 +47,16 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
 
     ascan_plan pl = {};
     pl.kernel = 0;
-    pl.dynamic = in.workspace ? 1 : 0;
+    const int nch = 3;
+    const int64_t te = 32 * nch * (16 / esize);
+    // tickets and split-row item numbers are 32-bit
+    const bool use_ws = in.workspace && env_int("ASCAN_STATIC", 0) == 0 && in.rows < (1ll << 30) &&
+                        in.rows * ((in.seqlen + te - 1) / te) < (1ll << 31);
+    pl.dynamic = use_ws ? 1 : 0;
 
     // 16-byte chunks per lane: odd, so that the 16-byte shared accesses of a
-    // quarter-warp hit distinct bank groups.  Tuning override: ASCAN_NCH (3 or 5).
-    int nch = env_int("ASCAN_NCH", 3);
-    if (nch != 3 && nch != 5) nch = 3;
+    // quarter-warp hit distinct bank groups.
     pl.chunks_per_lane = nch;
-    const int64_t te = 32 * nch * (16 / esize);
     pl.tile_elems = static_cast<int32_t>(te);
 
     // Bulk copies need every item to start on a 16-byte boundary and to be a
@@ -67,27 +69,69 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     const bool bulk = in.aligned && total_ok && env_int("ASCAN_FORCE_PLAIN", 0) == 0;
     pl.loader = bulk ? 0 : 1;
 
-    // Item size: about `seg_tiles` tiles.  Rows at least twice that long are split into
-    // segments (needs the workspace for the per-row carry records and rows that start
-    // 16-byte aligned when the bulk loader is used); shorter rows are grouped.
+    // Item size.  Long rows are split into segments (needs the workspace for the per-row
+    // carry records and, with the bulk loader, rows that start 16-byte aligned): coarse
+    // segments of `seg_tiles` tiles, then, in the part of every row that is processed last,
+    // fine segments of `fine_tiles` tiles, so that the warps run out of work within one
+    // small item of each other.  The fine part holds about one coarse item per warp.
+    // Short rows are grouped into items of about four per warp, at most `seg_tiles` tiles.
     int seg_tiles = env_int("ASCAN_SEG_TILES", 16);
     if (seg_tiles < 1) seg_tiles = 1;
-    int64_t seg = seg_tiles * te;
-    // carry tags hold the segment number in 15 bits
-    while ((in.seqlen + seg - 1) / seg > 32767) seg *= 2;
-    const bool can_split = in.workspace && (!bulk || align_rows == 1) && env_int("ASCAN_NO_SPLIT", 0) == 0;
-    if (can_split && in.seqlen >= 2 * seg) {
+    int fine_tiles = env_int("ASCAN_FINE_TILES", 4);
+    if (fine_tiles < 1) fine_tiles = 1;
+    if (fine_tiles > seg_tiles) fine_tiles = seg_tiles;
+    const int64_t max_warps = static_cast<int64_t>(in.sm_count) * kMaxWarpsPerCta;
+    const int64_t tiles_row = (in.seqlen + te - 1) / te;
+    const bool reverse_order = in.kind == ASCAN_KIND_BACKWARD || in.kind == ASCAN_KIND_REDUCE_BACKWARD || in.reverse;
+    const bool can_split = use_ws && (!bulk || align_rows == 1) && env_int("ASCAN_NO_SPLIT", 0) == 0;
+    const int64_t split_min = env_int("ASCAN_SPLIT_MIN_TILES", 32);   // shorter rows stay whole: an item switch costs about a tile
+    if (can_split && tiles_row >= split_min && tiles_row >= 2 * fine_tiles) {
+        int64_t fine_region = (static_cast<int64_t>(seg_tiles) * max_warps + in.rows - 1) / (in.rows > 0 ? in.rows : 1);
+        fine_region = (fine_region + fine_tiles - 1) / fine_tiles * fine_tiles;      // tiles, multiple of a fine item
+        if (fine_region > tiles_row) fine_region = tiles_row;
+        int64_t coarse_tiles = tiles_row - fine_region;                               // may be 0
+        int64_t seg_c = seg_tiles;
+        if (coarse_tiles < seg_c) seg_c = coarse_tiles;
+        // carry tags hold the segment number in 15 bits
+        while (seg_c > 0 && coarse_tiles / seg_c + (tiles_row + fine_tiles - 1) / fine_tiles > 30000) {
+            seg_c *= 2;
+            fine_tiles *= 2;
+        }
         pl.rows_per_item = 1;
         pl.row_groups = in.rows;
-        pl.seg_elems = seg;
-        pl.segs_per_row = (in.seqlen + seg - 1) / seg;
+        pl.fine_elems = fine_tiles * te;
+        if (seg_c <= 0) {
+            pl.seg_elems = pl.fine_elems;
+            pl.coarse_segs = 0;
+            pl.fine_segs = (in.seqlen + pl.fine_elems - 1) / pl.fine_elems;
+        } else if (!reverse_order) {
+            // coarse segments first, all full; the fine part takes the rest of the row
+            pl.seg_elems = seg_c * te;
+            pl.coarse_segs = coarse_tiles / seg_c;
+            const int64_t rest = in.seqlen - pl.coarse_segs * pl.seg_elems;
+            pl.fine_segs = (rest + pl.fine_elems - 1) / pl.fine_elems;
+        } else {
+            // processed from the row end: the fine part is the start of the row, all full
+            pl.seg_elems = seg_c * te;
+            pl.fine_segs = fine_region / fine_tiles;
+            const int64_t rest = in.seqlen - pl.fine_segs * pl.fine_elems;
+            pl.coarse_segs = (rest + pl.seg_elems - 1) / pl.seg_elems;
+        }
+        pl.segs_per_row = pl.coarse_segs + pl.fine_segs;
     } else {
-        int64_t rpi = seg / in.seqlen;
+        const int64_t total_tiles = (in.rows * in.seqlen + te - 1) / te;
+        int64_t fit = total_tiles / (4 * max_warps);
+        if (fit < 1) fit = 1;
+        if (fit < seg_tiles) seg_tiles = static_cast<int>(fit);
+        int64_t rpi = (seg_tiles * te) / in.seqlen;
         if (rpi < 1) rpi = 1;
         if (bulk) rpi = (rpi + align_rows - 1) / align_rows * align_rows;
         pl.rows_per_item = rpi;
         pl.row_groups = (in.rows + rpi - 1) / rpi;
         pl.seg_elems = in.seqlen;
+        pl.fine_elems = in.seqlen;
+        pl.coarse_segs = 1;
+        pl.fine_segs = 0;
         pl.segs_per_row = 1;
     }
     pl.items = pl.row_groups * pl.segs_per_row;
@@ -118,7 +162,7 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     pl.warps_per_cta = wpc;
     pl.grid = static_cast<int32_t>(grid);
     pl.smem_bytes = static_cast<uint64_t>(wpc) * wsm;
-    pl.workspace_bytes = in.workspace ? workspace_bytes(in.rows) : 0;
+    pl.workspace_bytes = use_ws ? workspace_bytes(in.rows) : 0;
     *plan = pl;
     return ASCAN_OK;
 }

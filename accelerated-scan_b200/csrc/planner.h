@@ -20,6 +20,7 @@ struct PlanInput {
     int64_t seqlen;
     int dtype;        // ascan_dtype
     int kind;         // ascan_kind
+    bool reverse;     // forward kind processed from the row end
     bool aligned;     // every pointer 16-byte aligned
     bool workspace;   // a workspace of workspace_bytes() is available
     int sm_count;

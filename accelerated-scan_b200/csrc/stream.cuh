@@ -1,25 +1,24 @@
 // Warp-stream scan kernel.
 //
 // Work decomposition
-//   * The rows x T matrix is cut into ITEMS.  Short rows are grouped (an item is a
-//     few whole rows); long rows are split into segments of `seg_elems` steps (an item
-//     is one segment of one row).  Items are numbered segment-major: all first
-//     segments, then all second segments, ...  (processing order; the reverse
-//     directions start from the last segment of every row).
-//   * Persistent warps draw item numbers from a global ticket counter, so faster SMs
-//     take more items and all SMs finish together.  Without a workspace the items are
-//     dealt round-robin instead and rows are never split.
-//   * The state leaving a segment is published in a per-row record (value + tag);
-//     the warp that draws the next segment of that row reads it.  Because of the
-//     segment-major order the record is normally written long before it is needed;
-//     if it is not there yet the reader polls with a bound, records a status bit on
-//     expiry and carries on, so the kernel always terminates.
+//   * The rows x T matrix is cut into ITEMS.  Short rows are grouped (an item is a few
+//     whole rows); longer rows are split into segments (an item is one segment of one
+//     row): coarse segments first and, in the part of each row that is processed last,
+//     fine segments, so that the warps run out of work within a small item of each
+//     other.  Items are numbered segment-major: all first segments, then all second
+//     segments, ... in processing order (the reverse directions start from the row end).
+//   * Persistent warps draw item numbers from a global ticket counter, so SMs that
+//     stream faster take more items and all SMs finish together.  Without a workspace
+//     the items are dealt round-robin instead and rows are never split.
+//   * The state leaving a segment is published in a per-row record of self-tagged
+//     64-bit words; the warp that draws the next segment of that row reads it.  Because
+//     of the segment-major order the record is normally written long before it is
+//     needed; if it is not there yet the reader polls with a bound, records a status
+//     bit on expiry and carries on, so the kernel always terminates.
 //
-// Inside an item (see the per-tile steps in the loop below)
+// Inside an item
 //   * An item is a flat range of the matrix; fixed-size tiles of it move through the
-//     warp's own shared-memory ring.  Row boundaries inside a tile are handled by
-//     forcing the gate of the row's first processed element to zero, which resets the
-//     running state, so any T works and tiles need not divide rows.
+//     warp's own shared-memory ring.
 //   * Bulk loader: one lane issues 1-D bulk asynchronous copies (global -> shared,
 //     mbarrier completion, no multicast) up to `stages` tiles ahead, across item
 //     boundaries; results leave through bulk asynchronous stores from a
@@ -32,6 +31,12 @@
 //     (A, B) of x -> A*x + B, Kogge-Stone combine across lanes by shuffles, then a
 //     second sequential pass from the lane's incoming state.  The state crossing
 //     tiles is one register per warp; there is no block-level barrier in the loop.
+//   * Row boundaries.  When an item is one row or one segment (INTERIOR = false) a row
+//     can only start where the item starts and end where it ends, so the incoming
+//     state is simply the warp's running state at the first tile, and only the ragged
+//     last tile of a row needs per-element masking.  When an item groups several short
+//     rows (INTERIOR = true) row starts fall inside tiles; the gate of a row's first
+//     processed element is forced to zero there, which resets the running state.
 //
 // Kinds: forward scan (optionally reversed), fused backward (reverse scan over the
 // gates shifted by one step plus the d_gates epilogue; shifted operands come from
@@ -47,7 +52,7 @@ enum : int { K_SCAN = 0, K_BWD = 1, K_REDUCE = 2, K_REDUCE_BWD = 3 };
 
 // Control words at the start of the workspace (uint32 each).
 enum : int { CTRL_STATUS = 0, CTRL_TICKET = 1, CTRL_DONE = 2, CTRL_EPOCH = 3 };
-constexpr int CTRL_BYTES = 256;        // control block, then one CarryRecord per row
+constexpr int CTRL_BYTES = 256;        // control block, then one carry record per row
 constexpr int CARRY_RECORD_BYTES = 32;
 
 struct StreamParams {
@@ -63,8 +68,11 @@ struct StreamParams {
     int64_t rows, T;
     int64_t rows_per_item;   // rows grouped into one item when rows are not split
     int64_t row_groups;      // ceil(rows / rows_per_item)
-    int64_t seg_elems;       // steps per segment (multiple of the tile) when rows are split
-    int64_t segs_per_row;    // 1 = rows are not split
+    int64_t seg_elems;       // steps per coarse segment (multiple of the tile) when rows are split
+    int64_t fine_elems;      // steps per fine segment (multiple of the tile)
+    int64_t coarse_segs;     // coarse segments per row
+    int64_t fine_segs;       // fine segments per row, processed after the coarse ones
+    int64_t segs_per_row;    // coarse_segs + fine_segs; 1 = rows are not split
     int64_t items;           // row_groups * segs_per_row
     uint32_t *ctrl;          // control words, or null (static dealing, no status)
     unsigned char *records;  // per-row carry records (segs_per_row > 1)
@@ -88,13 +96,13 @@ struct ItemDesc {
     int64_t e_begin;   // first element of the item in the flat matrix
     int64_t row0;      // row of that element
     int64_t pos0;      // its position inside the row
-    int64_t s_log;     // segment index in processing order
     int64_t n;         // elements in the item
+    int32_t s_log;     // segment index in processing order
     int32_t nt;        // tiles in the item
     bool valid;
 };
 
-template <class TR, int NCH, int KIND, bool REVERSE, bool BULK>
+template <class TR, int NCH, int KIND, bool REVERSE, bool BULK, bool INTERIOR>
 __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
     using V = typename TR::V;
     using Raw = typename TR::Raw;
@@ -173,13 +181,27 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
             d.e_begin = r0 * T;
             d.n = (r1 - r0) * T;
         } else {
-            d.s_log = q / p.row_groups;
-            d.row0 = q - d.s_log * p.row_groups;
-            const int64_t s = REV ? p.segs_per_row - 1 - d.s_log : d.s_log;
-            d.pos0 = s * p.seg_elems;
+            // item numbers and row counts of split plans fit 32 bits (planner)
+            const uint32_t qq = static_cast<uint32_t>(q), rg = static_cast<uint32_t>(p.row_groups);
+            const uint32_t sl = qq / rg;
+            d.s_log = static_cast<int32_t>(sl);
+            d.row0 = qq - sl * rg;
+            // Coarse segments are processed first, fine ones last.  Forward: coarse from the
+            // row start, the fine part is the rest of the row.  Reverse: coarse from the row
+            // end down to the fine part, which is the start of the row.
+            int64_t len;
+            if (d.s_log < p.coarse_segs) {
+                len = p.seg_elems;
+                d.pos0 = REV ? p.fine_segs * p.fine_elems + (p.coarse_segs - 1 - d.s_log) * p.seg_elems
+                             : d.s_log * p.seg_elems;
+            } else {
+                len = p.fine_elems;
+                const int64_t f = d.s_log - p.coarse_segs;
+                d.pos0 = REV ? (p.fine_segs - 1 - f) * p.fine_elems : p.coarse_segs * p.seg_elems + f * p.fine_elems;
+            }
             d.e_begin = d.row0 * T + d.pos0;
             const int64_t left = T - d.pos0;
-            d.n = left < p.seg_elems ? left : p.seg_elems;
+            d.n = left < len ? left : len;
         }
         d.nt = static_cast<int32_t>((d.n + TE - 1) / TE);
         return d;
@@ -272,27 +294,36 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
     // Item header: what an item needs from outside its own range -- the state published
     // by the previous segment of its row and (backward kinds) the gate of the step right
     // after it.  It is fetched during the last tile of the item before, so its latency
-    // hides behind that tile's arithmetic; `tag` tells whether the state was there yet.
+    // hides behind that tile's arithmetic; the tags tell whether the state was there yet.
+    // The header holds the loaded registers untouched; they are decoded in the next item's
+    // prologue, so the first use of each load sits a whole tile after its issue.
     struct ItemHeader {
-        bool have_state;
-        V x, x2, gate;
+        TaggedWords x, x2;
+        Raw gate;
+        int gate_kind;     // 0 = none (one), 1 = `gate` is a raw element of the gates, 2 = caller's halo gate
+        V halo;
     };
+    constexpr bool TWO_WORDS = sizeof(V) > 4;
     auto fetch_header = [&](const ItemDesc &d) -> ItemHeader {
         ItemHeader h;
-        h.have_state = false;
-        h.x = vzero(V());
-        h.x2 = vzero(V());
-        h.gate = vone(V());
+        h.x.w0 = 0; h.x.w1 = 0; h.x2.w0 = 0; h.x2.w1 = 0;
+        h.gate = 0;
+        h.gate_kind = 0;
+        h.halo = vone(V());
         if (!d.valid) return h;
         if (split && d.s_log > 0) {
             const unsigned char *rec = p.records + d.row0 * CARRY_RECORD_BYTES;
-            const uint32_t want = epoch | static_cast<uint32_t>(d.s_log);
-            h.have_state = read_tagged(rec, 0, want, h.x);
-            if (REDUCE) h.have_state = read_tagged(rec, 1, want, h.x2) && h.have_state;
+            h.x = fetch_tagged(rec, 0, TWO_WORDS);
+            if (REDUCE) h.x2 = fetch_tagged(rec, 1, TWO_WORDS);
         }
-        if (BACK) {
-            // unless the item ends its row
-            if (split && d.pos0 + d.n < T) h.gate = TR::load_one(p.in0, d.e_begin + d.n);
+        if (BACK && !INTERIOR) {
+            if (d.pos0 + d.n < T) {
+                h.gate = TR::load_raw(p.in0, d.e_begin + d.n);          // next step of the same row
+                h.gate_kind = 1;
+            } else if (hgate) {
+                h.halo = hgate[d.row0];                                  // the row ends here
+                h.gate_kind = 2;
+            }
         }
         return h;
     };
@@ -302,14 +333,15 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
         // ---------------- item prologue: incoming state, halo gate, running position
         V x_carry = vzero(V());    // state entering the tile
         V x2_carry = vzero(V());   // reduce kinds: response to a unit incoming state
-        V next_gate = head.gate;   // backward kinds: gate of the first element above the tile
+        // backward kinds: gate of the first element above the tile
+        const V item_end_gate = head.gate_kind == 1 ? TR::decode(head.gate) : (head.gate_kind == 2 ? head.halo : vone(V()));
+        V next_gate = item_end_gate;
         if (split && cur.s_log > 0) {
             // state published by the warp that processed the previous segment of this row
             const unsigned char *rec = p.records + cur.row0 * CARRY_RECORD_BYTES;
             const uint32_t want = epoch | static_cast<uint32_t>(cur.s_log);
-            bool got = head.have_state;
-            x_carry = head.x;
-            if (REDUCE) x2_carry = head.x2;
+            bool got = decode_tagged(head.x, want, x_carry);
+            if (REDUCE) got = decode_tagged(head.x2, want, x2_carry) && got;
             // not published when the header was fetched: poll, with a bound
             for (uint32_t poll = 0; !got && poll < CARRY_WAIT_POLLS; ++poll) {
                 __nanosleep(64);
@@ -321,6 +353,11 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
                 x_carry = vzero(V());
                 x2_carry = vzero(V());
             }
+        } else if (!INTERIOR) {
+            // the item opens its row: the caller's incoming state, and a unit state for the
+            // product carried by the reduce kinds
+            if (cin) x_carry = cin[cur.row0];
+            if (REDUCE) x2_carry = vone(V());
         }
         int64_t ts_mod, row_ts;   // (tile start) mod T and the row of the tile start
         {
@@ -341,9 +378,12 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
             const unsigned char *stg = stage_base + cs * NIN * TB;
 
             // backward: the state just below the tile, needed by lane 0 for d_gates
-            V x_halo = vzero(V());
+            Raw x_halo_raw = 0;
+            V x_halo_row = vzero(V());
+            const bool halo_in_row = (ts_mod != 0);
             if (KIND == K_BWD) {
-                if (ts_mod != 0) x_halo = TR::load_one(p.in2, cur.e_begin + toff - 1);
+                if (halo_in_row) x_halo_raw = TR::load_raw(p.in2, cur.e_begin + toff - 1);
+                else if (!INTERIOR && hstate) x_halo_row = hstate[row_ts];
             }
             // last tile of the item: fetch the header of the next one now
             ItemHeader head_next = head;
@@ -412,47 +452,95 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
                 next_gate = shfl_idx(g0, 0);
             }
 
-            // ---- row boundaries and the ragged last tile
-            V b2[REDUCE ? K : 1];
-            if (REDUCE) {
+            const int jv = nvalid - lane * K;   // elements j >= jv lie beyond the item
+            V b2[(REDUCE && INTERIOR) ? K : 1];
+            uint32_t start_mask_lo = 0, start_mask_hi = 0;   // INTERIOR backward: elements that open a row
+            bool has_boundary = false;
+            // Where the row boundaries fall among this lane's K elements (INTERIOR only).
+            const bool tiny = T < K;            // several rows inside one lane: per-element arithmetic
+            int js = -1, je = -1, jwrap = K;    // row start, row end, first element of the next row
+            int64_t rowq = row_ts;              // row of the lane's first element
+            auto classify = [&](int j, bool &is_start, bool &is_end, int64_t &row) {
+                if (!tiny) {
+                    is_start = (j == js);
+                    is_end = (j == je);
+                    row = rowq + (j >= jwrap ? 1 : 0);
+                } else {
+                    const int pi = static_cast<int>(ts_mod) + lane * K + j, ti = static_cast<int>(T);
+                    const int qi = pi / ti;
+                    const int rem = pi - qi * ti;
+                    is_start = (rem == 0);
+                    is_end = (rem == ti - 1);
+                    row = row_ts + qi;
+                }
+            };
+
+            if (!INTERIOR) {
+                // ---- the ragged last tile of a row: identity beyond the row's end
+                if (nvalid < TE) {
+                    V gate_end = vone(V());
+                    if (BACK) gate_end = vconj(item_end_gate);
 #pragma unroll
-                for (int j = 0; j < K; ++j) b2[j] = vzero(V());
-            }
-            const bool has_boundary = (ts_mod == 0) || (ts_mod + nvalid >= T);
-            const bool slow = has_boundary || (nvalid < TE);
-            uint32_t start_mask_lo = 0, start_mask_hi = 0;   // backward: elements that open a row
-            if (slow) {
-#pragma unroll
-                for (int j = 0; j < K; ++j) {
-                    const int o = lane * K + j;
-                    const int64_t pos = ts_mod + o;
-                    int64_t q, rem;
-                    if (T > TE) {
-                        q = pos >= T ? 1 : 0;
-                        rem = pos - (q ? T : 0);
-                    } else {
-                        const int pi = static_cast<int>(pos), ti = static_cast<int>(T);
-                        q = pi / ti;
-                        rem = pi - static_cast<int>(q) * ti;
-                    }
-                    const bool is_start = (rem == 0);
-                    const bool is_end = (rem == T - 1);
-                    const bool first = REV ? is_end : is_start;
-                    const int64_t row = row_ts + q;
-                    if (o >= nvalid) {
-                        a[j] = vone(V());
-                        b[j] = vzero(V());
-                    } else {
-                        if (first) {
-                            V a_orig = a[j];
-                            if (BACK) a_orig = hgate ? vconj(hgate[row]) : vone(V());
-                            if (cin) b[j] = vfma(a_orig, cin[row], b[j]);
-                            if (REDUCE) b2[j] = a_orig;
-                            a[j] = vzero(V());
+                    for (int j = 0; j < K; ++j) {
+                        // (range tests on purpose: an equality test on j invites the compiler to
+                        // turn the chain into one indexed store, which puts a[] in local memory)
+                        if (j >= jv) {
+                            a[j] = vone(V());
+                            b[j] = vzero(V());
+                        } else if (BACK && j + 1 >= jv) {
+                            // the last step of the row takes the gate of the step after the row
+                            a[j] = gate_end;
                         }
-                        if (KIND == K_BWD && is_start) {
-                            if (j < 32) start_mask_lo |= 1u << (j & 31);
-                            else start_mask_hi |= 1u << (j & 31);
+                    }
+                }
+            } else {
+                // ---- items that group rows: row boundaries inside the tile
+                if (REDUCE) {
+#pragma unroll
+                    for (int j = 0; j < K; ++j) b2[j] = vzero(V());
+                }
+                has_boundary = (ts_mod == 0) || (ts_mod + nvalid >= T);
+                const bool slow = has_boundary || (nvalid < TE);
+                if (slow && !tiny) {
+                    const int64_t p0 = ts_mod + lane * K;
+                    int64_t q0, r;
+                    if (T > TE) {
+                        q0 = p0 >= T ? 1 : 0;
+                        r = p0 - (q0 ? T : 0);
+                    } else {
+                        const int pi = static_cast<int>(p0), ti = static_cast<int>(T);
+                        const int qi = pi / ti;
+                        q0 = qi;
+                        r = pi - qi * ti;
+                    }
+                    rowq = row_ts + q0;
+                    const int64_t tr = T - r;       // distance to the next row start, 1..T
+                    jwrap = tr < K ? static_cast<int>(tr) : K;
+                    js = (r == 0) ? 0 : (tr < K ? static_cast<int>(tr) : -1);
+                    je = (tr <= K) ? static_cast<int>(tr - 1) : -1;
+                }
+                if (slow) {
+#pragma unroll
+                    for (int j = 0; j < K; ++j) {
+                        bool is_start, is_end;
+                        int64_t row;
+                        classify(j, is_start, is_end, row);
+                        const bool first = REV ? is_end : is_start;
+                        if (j >= jv) {
+                            a[j] = vone(V());
+                            b[j] = vzero(V());
+                        } else {
+                            if (first) {
+                                V a_orig = a[j];
+                                if (BACK) a_orig = hgate ? vconj(hgate[row]) : vone(V());
+                                if (cin) b[j] = vfma(a_orig, cin[row], b[j]);
+                                if (REDUCE) b2[j] = a_orig;
+                                a[j] = vzero(V());
+                            }
+                            if (KIND == K_BWD && is_start) {
+                                if (j < 32) start_mask_lo |= 1u << (j & 31);
+                                else start_mask_hi |= 1u << (j & 31);
+                            }
                         }
                     }
                 }
@@ -461,12 +549,12 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
             // ---- pass 1: lane aggregate in processing order
             constexpr int JF = REV ? K - 1 : 0;
             V A = a[JF], B = b[JF];
-            V B2 = REDUCE ? b2[JF] : vzero(V());
+            V B2 = (REDUCE && INTERIOR) ? b2[JF] : vzero(V());
 #pragma unroll
             for (int q = 1; q < K; ++q) {
                 const int j = REV ? K - 1 - q : q;
                 B = vfma(a[j], B, b[j]);
-                if (REDUCE) B2 = vfma(a[j], B2, b2[j]);
+                if (REDUCE && INTERIOR) B2 = vfma(a[j], B2, b2[j]);
                 A = vmul(A, a[j]);
             }
             // the warp's incoming state enters through the first lane in processing order
@@ -492,7 +580,7 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
             V x = REV ? shfl_down(B, 1) : shfl_up(B, 1);
             if (ll == 0) x = x_carry;
             V x2 = vzero(V());
-            if (REDUCE) {
+            if (REDUCE && INTERIOR) {
                 x2 = REV ? shfl_down(B2, 1) : shfl_up(B2, 1);
                 if (ll == 0) x2 = x2_carry;
             }
@@ -511,17 +599,18 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
                     // d_gates[t] = conj(x[t-1]) * g[t]: the previous state comes from the
                     // element below (neighbouring lane by shuffle, tile halo for lane 0)
                     V dn = shfl_up(xp[K - 1], 1);
-                    if (lane == 0) dn = x_halo;
+                    if (lane == 0) dn = halo_in_row ? TR::decode(x_halo_raw) : x_halo_row;
 #pragma unroll
-                    for (int j = K - 1; j > 0; --j) a[j] = vmul(vconj(xp[j - 1]), b[j]);
+                    for (int j = 1; j < K; ++j) a[j] = vmul(vconj(xp[j - 1]), b[j]);
                     a[0] = vmul(vconj(dn), b[0]);
-                    if (start_mask_lo | start_mask_hi) {
+                    if (INTERIOR && (start_mask_lo | start_mask_hi)) {
 #pragma unroll
                         for (int j = 0; j < K; ++j) {
                             const bool st = j < 32 ? (start_mask_lo >> (j & 31)) & 1u : (start_mask_hi >> (j & 31)) & 1u;
                             if (st) {
-                                const int64_t pos = ts_mod + lane * K + j;
-                                const int64_t row = row_ts + (T > TE ? (pos >= T ? 1 : 0) : pos / T);
+                                bool is_start, is_end;
+                                int64_t row;
+                                classify(j, is_start, is_end, row);
                                 const V xs = hstate ? hstate[row] : vzero(V());
                                 a[j] = vmul(vconj(xs), b[j]);
                             }
@@ -563,28 +652,19 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
                         for (int idx = lane; idx < nvalid; idx += 32) dst[idx] = src[idx];
                     }
                 }
-            } else if (has_boundary) {
-                // reduce kinds: only tiles that finish a row need the element states
+            } else if (INTERIOR && has_boundary) {
+                // reduce kinds over grouped rows: tiles that finish a row need the element states
                 V *cout = static_cast<V *>(p.carry_out);
 #pragma unroll
                 for (int q = 0; q < K; ++q) {
                     const int j = REV ? K - 1 - q : q;
                     x = vfma(a[j], x, b[j]);
                     x2 = vfma(a[j], x2, b2[j]);
-                    const int o = lane * K + j;
-                    const int64_t pos = ts_mod + o;
-                    int64_t qq, rem;
-                    if (T > TE) {
-                        qq = pos >= T ? 1 : 0;
-                        rem = pos - (qq ? T : 0);
-                    } else {
-                        const int pi = static_cast<int>(pos), ti = static_cast<int>(T);
-                        qq = pi / ti;
-                        rem = pi - static_cast<int>(qq) * ti;
-                    }
-                    const bool last = REV ? (rem == 0) : (rem == T - 1);
-                    if (last && o < nvalid) {
-                        const int64_t row = row_ts + qq;
+                    bool is_start, is_end;
+                    int64_t row;
+                    classify(j, is_start, is_end, row);
+                    const bool last = REV ? is_start : is_end;
+                    if (last && j < jv) {
                         cout[2 * row] = x2;
                         cout[2 * row + 1] = x;
                     }
@@ -621,13 +701,20 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
         }
         if (failed) break;
 
-        // ---------------- item epilogue: publish the outgoing state, move to the next item
+        // ---------------- item epilogue: hand the outgoing state on, move to the next item
         if (split && cur.s_log + 1 < p.segs_per_row) {
             if (lane == 0) {
                 unsigned char *rec = p.records + cur.row0 * CARRY_RECORD_BYTES;
                 const uint32_t tag = epoch | static_cast<uint32_t>(cur.s_log + 1);
                 publish_tagged(rec, 0, x_carry, tag);
                 if (REDUCE) publish_tagged(rec, 1, x2_carry, tag);
+            }
+        } else if (REDUCE && !INTERIOR) {
+            // the item closes its row: the running state is the row's carry
+            if (lane == 0) {
+                V *cout = static_cast<V *>(p.carry_out);
+                cout[2 * cur.row0] = x2_carry;
+                cout[2 * cur.row0 + 1] = x_carry;
             }
         }
         need_next();

@@ -68,8 +68,11 @@ typedef struct {
     int32_t dynamic;           /* 1 = items drawn from a ticket counter in the workspace   */
     int64_t rows_per_item;     /* rows grouped into one item when rows are not split       */
     int64_t row_groups;        /* ceil(rows / rows_per_item)                               */
-    int64_t seg_elems;         /* steps per segment when rows are split                    */
-    int64_t segs_per_row;      /* 1 = rows are not split                                   */
+    int64_t seg_elems;         /* steps per coarse segment when rows are split             */
+    int64_t fine_elems;        /* steps per fine segment (the part of a row processed last) */
+    int64_t coarse_segs;       /* coarse segments per row                                  */
+    int64_t fine_segs;         /* fine segments per row                                    */
+    int64_t segs_per_row;      /* coarse_segs + fine_segs; 1 = rows are not split          */
     int64_t items;             /* row_groups * segs_per_row                                */
     uint64_t smem_bytes;       /* dynamic shared memory per CTA                            */
     uint64_t workspace_bytes;  /* scratch the plan uses (0 = none)                         */
@@ -145,7 +148,8 @@ size_t ascan_workspace_bytes(int64_t rows, int64_t seqlen, int dtype, int kind);
 
 /*
  * The plan the library would use.  flags: bit 0 = every pointer is 16-byte
- * aligned, bit 1 = a workspace of ascan_workspace_bytes() is supplied;
+ * aligned, bit 1 = a workspace of ascan_workspace_bytes() is supplied, bit 2 =
+ * forward kind with reverse != 0;
  * sm_count <= 0 queries the current device.  Host only.
  */
 int ascan_plan_describe(int64_t rows, int64_t seqlen, int dtype, int kind,

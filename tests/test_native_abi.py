@@ -60,12 +60,20 @@ def test_planner_invariants(T, dtype, kind):
         assert pl["tile_elems"] == 32 * pl["chunks_per_lane"] * (16 // esize)
         assert pl["items"] == pl["row_groups"] * pl["segs_per_row"]
         assert pl["row_groups"] * pl["rows_per_item"] >= rows
-        assert pl["segs_per_row"] * pl["seg_elems"] >= T
+        assert pl["segs_per_row"] == pl["coarse_segs"] + pl["fine_segs"]
+        assert pl["coarse_segs"] * pl["seg_elems"] + pl["fine_segs"] * pl["fine_elems"] >= T
         assert pl["dynamic"] == 1 and pl["workspace_bytes"] == 256 + 32 * rows
         if pl["segs_per_row"] > 1:
             # split rows: one row per item, segments are whole tiles
             assert pl["rows_per_item"] == 1 and pl["seg_elems"] % pl["tile_elems"] == 0
-            assert (pl["segs_per_row"] - 1) * pl["seg_elems"] < T
+            assert pl["fine_elems"] % pl["tile_elems"] == 0 and pl["segs_per_row"] < 32768
+            # only the last piece of a row (in memory order) may be short, none is empty
+            if kind in (1, 3):
+                assert pl["fine_segs"] * pl["fine_elems"] + (pl["coarse_segs"] - 1) * pl["seg_elems"] < T or pl["coarse_segs"] == 0
+                assert pl["coarse_segs"] > 0 or (pl["fine_segs"] - 1) * pl["fine_elems"] < T
+            else:
+                assert pl["coarse_segs"] * pl["seg_elems"] + (pl["fine_segs"] - 1) * pl["fine_elems"] < T
+                assert pl["coarse_segs"] * pl["seg_elems"] <= T
         if pl["loader"] == 0:
             # bulk copies: every item starts on a 16-byte boundary and the matrix ends on one
             assert (pl["rows_per_item"] * T * esize) % 16 == 0
