@@ -1,0 +1,187 @@
+"""Multi-GPU sharding of the scan (one process per GPU, `torch.distributed`).
+
+The reference has no multi-device path.  Two ways to shard exist:
+
+* rows (batch x channel): rows are independent, so every rank runs the single-GPU
+  scan on its own rows and nothing is exchanged (`shard_rows` only slices).
+* time: every rank owns a contiguous time slice of every row.  The scan is the
+  classic three-step block scan over ranks:
+      1. each rank reduces its slice to a carry per row, (P, S) = (product of the
+         gates, last state from a zero start)                 -- `ascan_reduce_forward`
+      2. ONE all_gather of the carries (plus the first gate of each slice, which the
+         backward needs as its right halo): 3 values per row per rank
+      3. each rank folds the carries of the ranks before it into its incoming state
+         and runs the scan seeded with it                     -- `ascan_forward(carry_in)`
+  The backward mirrors it with the ranks after it: `ascan_reduce_backward`, one
+  all_gather of (P', S'), a suffix fold, and the seeded fused backward
+  (`carry_in`, `halo_gate_right`, `halo_state_left`).
+
+The fold helpers are plain tensor arithmetic and run on any device; the local steps
+default to the CUDA kernels (`NativeOps`) and fail on CPU tensors.  Tests inject other
+local steps to exercise the exchange logic on CPU ranks (gloo).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from . import _native
+
+
+def shard_rows(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    """The rows of a (B, C, T) tensor that `rank` owns when B*C rows are dealt in
+    contiguous blocks: returns a (1, rows_local, T) view-copy-free slice."""
+    B, C, T = t.shape
+    rows = B * C
+    lo = rows * rank // world
+    hi = rows * (rank + 1) // world
+    return t.reshape(1, rows, T)[:, lo:hi]
+
+
+def shard_time(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    """The time slice of a (B, C, T) tensor that `rank` owns (contiguous copy)."""
+    T = t.shape[-1]
+    lo = T * rank // world
+    hi = T * (rank + 1) // world
+    return t[..., lo:hi].contiguous()
+
+
+def compute_dtype(dtype: torch.dtype) -> torch.dtype:
+    """Carries travel in the arithmetic type of the kernels."""
+    return torch.complex64 if dtype == torch.complex64 else torch.float32
+
+
+def fold_prefix(prod: torch.Tensor, state: torch.Tensor, rank: int) -> torch.Tensor:
+    """Incoming state of `rank`: the composition of the carries of ranks 0..rank-1.
+    prod, state: (world, rows).  x -> P*x + S applied in rank order from zero."""
+    x = torch.zeros_like(state[0])
+    for j in range(rank):
+        x = prod[j] * x + state[j]
+    return x
+
+
+def fold_suffix(prod: torch.Tensor, state: torch.Tensor, rank: int) -> torch.Tensor:
+    """Incoming adjoint of `rank` (g just after its last step): the composition of the
+    backward carries of ranks world-1 down to rank+1."""
+    world = prod.shape[0]
+    g = torch.zeros_like(state[0])
+    for j in range(world - 1, rank, -1):
+        g = prod[j] * g + state[j]
+    return g
+
+
+class NativeOps:
+    """The local steps on the CUDA kernels (C ABI)."""
+
+    @staticmethod
+    def reduce_forward(gates, tokens):
+        rows = gates.numel() // gates.shape[-1]
+        carry = torch.empty(rows, 2, dtype=compute_dtype(gates.dtype), device=gates.device)
+        _native.reduce_forward(gates, tokens, carry)
+        return carry[:, 0], carry[:, 1]
+
+    @staticmethod
+    def forward(gates, tokens, carry_in):
+        out = torch.empty_like(tokens)
+        _native.forward(gates, tokens, out, carry_in=carry_in)
+        return out
+
+    @staticmethod
+    def reduce_backward(gates, grad_out, halo_gate_right):
+        rows = gates.numel() // gates.shape[-1]
+        carry = torch.empty(rows, 2, dtype=compute_dtype(gates.dtype), device=gates.device)
+        _native.reduce_backward(gates, grad_out, halo_gate_right, carry)
+        return carry[:, 0], carry[:, 1]
+
+    @staticmethod
+    def backward(gates, states, grad_out, carry_in, halo_gate_right, halo_state_left):
+        d_gates = torch.empty_like(gates)
+        d_tokens = torch.empty_like(gates)
+        _native.backward(gates, states, grad_out, d_gates, d_tokens, carry_in=carry_in,
+                         halo_gate_right=halo_gate_right, halo_state_left=halo_state_left)
+        return d_gates, d_tokens
+
+
+def _all_gather(x: torch.Tensor, group) -> torch.Tensor:
+    world = dist.get_world_size(group)
+    x = x.contiguous()
+    out = torch.empty((world * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    dist.all_gather_into_tensor(out, x, group=group)       # concatenated along dim 0 (gloo and nccl)
+    return out.view((world,) + tuple(x.shape))
+
+
+def time_sharded_forward(gates, tokens, group=None, ops=NativeOps):
+    """Forward of the time-sharded scan on this rank's slice.  Returns
+    (states, carry_in, halo_gate_right); the last two are what the backward needs."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    cdt = compute_dtype(gates.dtype)
+    rows = gates.numel() // gates.shape[-1]
+    if world == 1:
+        return ops.forward(gates, tokens, None), None, None
+    prod, state = ops.reduce_forward(gates, tokens)
+    first_gate = gates.reshape(rows, -1)[:, 0].to(cdt)
+    payload = torch.stack([prod.to(cdt), state.to(cdt), first_gate], dim=0)           # (3, rows)
+    gathered = _all_gather(payload, group)                                              # (world, 3, rows)
+    carry_in = fold_prefix(gathered[:, 0], gathered[:, 1], rank).contiguous()
+    halo_gate_right = (gathered[rank + 1, 2] if rank + 1 < world else torch.ones_like(first_gate)).contiguous()
+    states = ops.forward(gates, tokens, carry_in if rank > 0 else None)
+    return states, carry_in, halo_gate_right
+
+
+def time_sharded_backward(gates, states, grad_out, carry_in, halo_gate_right, group=None, ops=NativeOps):
+    """Backward of the time-sharded scan on this rank's slice: (d_gates, d_tokens)."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    if world == 1:
+        return ops.backward(gates, states, grad_out, None, None, None)
+    cdt = compute_dtype(gates.dtype)
+    prod, state = ops.reduce_backward(gates, grad_out, halo_gate_right)
+    payload = torch.stack([prod.to(cdt), state.to(cdt)], dim=0)
+    gathered = _all_gather(payload, group)                                              # (world, 2, rows)
+    g_in = fold_suffix(gathered[:, 0], gathered[:, 1], rank).contiguous()
+    return ops.backward(gates, states, grad_out, g_in, halo_gate_right, carry_in)
+
+
+class TimeShardedScan(torch.autograd.Function):
+    """Autograd wrapper of the time-sharded scan (same contract as warp.Scan /
+    complex.Scan on the local slice; `group` is the process group of the ranks that
+    hold the slices of one sequence, in time order)."""
+
+    @staticmethod
+    def forward(ctx, gates, tokens, group):
+        B, C, T = gates.shape
+        assert tokens.shape == (B, C, T)
+        assert gates.is_contiguous()
+        assert tokens.is_contiguous()
+        if gates.dtype != tokens.dtype:
+            raise RuntimeError("gates and tokens must have the same dtype")
+        states, carry_in, halo_gate_right = time_sharded_forward(gates, tokens, group)
+        ctx.group = group
+        ctx.save_for_backward(gates, states, carry_in, halo_gate_right)
+        return states
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        gates, states, carry_in, halo_gate_right = ctx.saved_tensors
+        grad_output = grad_output.contiguous()
+        d_gates, d_tokens = time_sharded_backward(gates, states, grad_output, carry_in, halo_gate_right, ctx.group)
+        return d_gates, d_tokens, None
+
+
+def sharded_scan(gates, tokens, group=None, dim: str = "time"):
+    """Scan over tensors that are sharded across the ranks of `group`.
+
+    dim="rows": the local tensors hold different rows; this is the plain single-GPU scan.
+    dim="time": the local tensors hold consecutive time slices of the same rows
+                (rank order = time order); one small all_gather per direction.
+    """
+    if dim == "rows":
+        if gates.dtype == torch.complex64:
+            from . import complex as _complex
+            return _complex.scan(gates, tokens)
+        from . import warp as _warp
+        return _warp.scan(gates, tokens)
+    if dim != "time":
+        raise ValueError("dim must be 'rows' or 'time'")
+    return TimeShardedScan.apply(gates, tokens, group)

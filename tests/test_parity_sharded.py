@@ -1,0 +1,141 @@
+"""Seeded and carry-only kernels (the local steps of the time-sharded scan) on the GPU.
+
+On one GPU the ranks are emulated one after the other: reduce every slice, fold the
+carries on the host side of the API, run the seeded scans, and compare the
+concatenation with the CPU oracle on the unsharded sequence.  With two or more GPUs
+the real NCCL path runs as child processes."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import complex_inputs, real_inputs, rel_err, to_np
+from oracle import scan_oracle
+
+pytestmark = pytest.mark.gpu
+
+REL = {torch.float32: 1e-5, torch.complex64: 1e-5, torch.bfloat16: 2.0 ** -8}
+
+
+def _emulate(gates, tokens, grad_out, world, dev):
+    from accelerated_scan import sharded
+
+    ops = sharded.NativeOps
+    T = gates.shape[-1]
+    cuts = [T * r // world for r in range(world + 1)]
+    sl = lambda t, r: t[..., cuts[r]:cuts[r + 1]].contiguous().to(dev)
+    g = [sl(gates, r) for r in range(world)]
+    x = [sl(tokens, r) for r in range(world)]
+    go = [sl(grad_out, r) for r in range(world)]
+    rows = gates.shape[0] * gates.shape[1]
+    cdt = sharded.compute_dtype(gates.dtype)
+    # forward: reduce -> fold -> seeded scan
+    carries = [ops.reduce_forward(g[r], x[r]) for r in range(world)]
+    P = torch.stack([c[0] for c in carries]).to(cdt)
+    S = torch.stack([c[1] for c in carries]).to(cdt)
+    first = torch.stack([g[r].reshape(rows, -1)[:, 0].to(cdt) for r in range(world)])
+    cin = [sharded.fold_prefix(P, S, r).contiguous() for r in range(world)]
+    states = [ops.forward(g[r], x[r], cin[r] if r > 0 else None) for r in range(world)]
+    # backward: reduce -> fold -> seeded fused backward
+    halo = [first[r + 1].contiguous() if r + 1 < world else torch.ones_like(first[0]) for r in range(world)]
+    bc = [ops.reduce_backward(g[r], go[r], halo[r]) for r in range(world)]
+    Pb = torch.stack([c[0] for c in bc]).to(cdt)
+    Sb = torch.stack([c[1] for c in bc]).to(cdt)
+    gin = [sharded.fold_suffix(Pb, Sb, r).contiguous() for r in range(world)]
+    grads = [ops.backward(g[r], states[r], go[r], gin[r], halo[r], cin[r]) for r in range(world)]
+    cat = lambda parts: torch.cat(parts, dim=-1)
+    return cat(states), cat([d[0] for d in grads]), cat([d[1] for d in grads]), (P, S)
+
+
+@pytest.mark.parametrize("world", [2, 3, 8])
+@pytest.mark.parametrize("seqlen", [96, 1000, 24576, 100000])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.complex64, torch.bfloat16])
+def test_emulated_time_shards(cuda_device, world, seqlen, dtype):
+    shape = (2, 5, seqlen)
+    if dtype == torch.complex64:
+        gates, tokens, grad_out = complex_inputs(9, shape, law="cfg4")
+    else:
+        gates, tokens, grad_out = real_inputs(9, shape, law="near_one", dtype=dtype)
+    up = (lambda t: t.numpy()) if dtype != torch.bfloat16 else (lambda t: t.float().numpy())
+    want = scan_oracle.scan(up(gates), up(tokens))
+    states, d_gates, d_tokens, (P, S) = _emulate(gates, tokens, grad_out, world, cuda_device)
+    tol = REL[dtype]
+    assert rel_err(to_np(states), want) <= tol
+    saved = to_np(states) if dtype == torch.bfloat16 else want
+    want_dg, want_dx = scan_oracle.scan_backward(up(gates), saved, up(grad_out))
+    assert rel_err(to_np(d_tokens), want_dx) <= tol
+    assert rel_err(to_np(d_gates), want_dg) <= tol
+    # the carries themselves: the product of the gates and the zero-start end state of slice 0
+    cut = seqlen // world
+    first = scan_oracle.scan(up(gates)[..., :cut], up(tokens)[..., :cut])[..., -1].reshape(-1)
+    assert rel_err(to_np(S[0]), first) <= 1e-5
+    prod = np.prod(up(gates)[..., :cut].astype(np.complex128 if dtype == torch.complex64 else np.float64), axis=-1).reshape(-1)
+    np.testing.assert_allclose(to_np(P[0]).astype(prod.dtype), prod, rtol=2e-4, atol=1e-30)
+
+
+@pytest.mark.parametrize("seqlen", [7, 100, 3000, 70000])
+def test_carry_in_is_initial_state(cuda_device, seqlen):
+    """ascan_forward with carry_in continues a scan: scanning [first | second] equals
+    scanning `second` from the last state of `first` (streaming / resume use)."""
+    from accelerated_scan import _native
+
+    gates, tokens, _ = real_inputs(3, (1, 9, 2 * seqlen), grad=False)
+    g, x = gates.to(cuda_device), tokens.to(cuda_device)
+    full = torch.empty_like(x)
+    _native.forward(g, x, full)
+    g2, x2 = g[..., seqlen:].contiguous(), x[..., seqlen:].contiguous()
+    cont = torch.empty_like(x2)
+    _native.forward(g2, x2, cont, carry_in=full[0, :, seqlen - 1].float().contiguous())
+    assert rel_err(to_np(cont), to_np(full[..., seqlen:])) <= 1e-5
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _nccl_worker(rank, world, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    import datetime
+    import torch.distributed as dist
+    from accelerated_scan import sharded
+
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=60))
+    try:
+        gates, tokens, grad_out = real_inputs(17, (2, 8, 49152), law="near_one")
+        g = sharded.shard_time(gates, rank, world).to(dev).requires_grad_(True)
+        x = sharded.shard_time(tokens, rank, world).to(dev).requires_grad_(True)
+        go = sharded.shard_time(grad_out, rank, world).to(dev)
+        out = sharded.sharded_scan(g, x, None, dim="time")
+        out.backward(go)
+        torch.cuda.synchronize()
+        np.savez(os.path.join(out_dir, f"rank{rank}.npz"), states=to_np(out), d_gates=to_np(g.grad),
+                 d_tokens=to_np(x.grad))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_time_sharded_nccl(cuda_device, tmp_path):
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    import torch.multiprocessing as mp
+
+    mp.spawn(_nccl_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    gates, tokens, grad_out = real_inputs(17, (2, 8, 49152), law="near_one")
+    want = scan_oracle.scan(gates.numpy(), tokens.numpy())
+    want_dg, want_dx = scan_oracle.scan_backward(gates.numpy(), want, grad_out.numpy())
+    parts = [np.load(tmp_path / f"rank{r}.npz") for r in range(world)]
+    cat = lambda k: np.concatenate([p[k] for p in parts], axis=-1)
+    assert rel_err(cat("states"), want) <= 1e-5
+    assert rel_err(cat("d_tokens"), want_dx) <= 1e-5
+    assert rel_err(cat("d_gates"), want_dg) <= 1e-5
