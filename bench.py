@@ -47,6 +47,8 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    ap.add_argument("--no-time-sharded", action="store_true")
+    ap.add_argument("--time-sharded-steps", type=int, default=5)
     return ap.parse_args()
 
 
@@ -275,9 +277,18 @@ def run_b200(args):
     value = world * bytes_step / (ms_per_step * 1e-3) / 1e9
     _native.check_status(dev)
 
+    # ---- second multi-GPU mode: one long sequence sharded along time (carry all_gather)
+    time_sharded = None
+    if not args.no_time_sharded and args.seqlen == 65536:
+        del gates, tokens, grad_out, out, d_gates, d_tokens
+        torch.cuda.empty_cache()
+        time_sharded = run_time_sharded(args, torch, dist, dev, world, rank)
+
     # ---- end to end through the drop-in autograd API with pinned host buffers
     e2e = None
     launches = 2 * K
+    if time_sharded:
+        launches += (args.time_sharded_steps + 3) * time_sharded["launches_per_step"]
     if not args.no_e2e:
         e2e, e2e_launches = run_e2e(args, torch, dist, warp, dev, world, dtype, esize)
         launches += e2e_launches
@@ -285,7 +296,7 @@ def run_b200(args):
     if world > 1:
         dist.barrier()
     if rank != 0:
-        if world > 1:
+        if dist.is_initialized():
             dist.destroy_process_group()
         return
 
@@ -298,29 +309,78 @@ def run_b200(args):
         "dtype": "f32", "data": "synthetic", "config": config_dict(args, world),
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
         "roofline": {
-            "kernel": "rowstream_kernel<backward>", "bound": "hbm", "achieved": round(bwd_gbs, 1), "peak": peak,
+            "kernel": "stream_kernel<K_BWD>", "bound": "hbm", "achieved": round(bwd_gbs, 1), "peak": peak,
             "unit": UNIT, "frac": round(bwd_gbs / peak, 4), "peak_kind": f"of {peak_kind}",
             "algorithmic_bytes_per_launch": 5 * esize * N, "ms_per_launch": round(bwd_ms, 5),
             "traffic": TRAFFIC_BWD_BYTES_PER_ELEM * N if TRAFFIC_BWD_BYTES_PER_ELEM and args.dtype == "bf16" else None,
         },
         "roofline_forward": {
-            "kernel": "rowstream_kernel<forward>", "bound": "hbm", "achieved": round(fwd_gbs, 1), "peak": peak,
+            "kernel": "stream_kernel<K_SCAN>", "bound": "hbm", "achieved": round(fwd_gbs, 1), "peak": peak,
             "unit": UNIT, "frac": round(fwd_gbs / peak, 4), "algorithmic_bytes_per_launch": 3 * esize * N,
             "ms_per_launch": round(fwd_ms, 5),
         },
         "pct_of_nominal_8TBs": round(100 * value / world / 8000.0, 2),
+        "time_sharded": time_sharded,
     }
     if not args.no_cpu_baseline and world == 1:
         cb, _, _ = cpu_baseline(args, esize)
         line["cpu_baseline"] = cb
     print(json.dumps(line), flush=True)
-    if world > 1:
+    if dist.is_initialized():
         dist.destroy_process_group()
 
 
 # DRAM bytes per element of the backward kernel from the ncu capture summarised under
 # profiles/ (dram__bytes_read.sum + dram__bytes_write.sum, scaled per element); None until captured.
 TRAFFIC_BWD_BYTES_PER_ELEM = None
+
+
+def run_time_sharded(args, torch, dist, dev, world, rank):
+    """(2, 512, 1048576) fp32 forward+backward with the sequence sharded along time over
+    the ranks: local carry reduce, one all_gather of the carries per direction, seeded
+    scan.  Strong scaling: the tensor is fixed, every rank holds 1/world of the steps."""
+    from accelerated_scan import sharded
+
+    Bt, Ct, Tt = 2, 512, 1048576
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29577")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+    Tl = Tt // world
+    gen = torch.Generator(device=dev).manual_seed(77 + rank)
+    g = 0.999 + 0.001 * torch.rand(Bt, Ct, Tl, device=dev, generator=gen)
+    x = torch.rand(Bt, Ct, Tl, device=dev, generator=gen)
+    go = torch.randn(Bt, Ct, Tl, device=dev, generator=gen)
+
+    def step():
+        states, cin, halo = sharded.time_sharded_forward(g, x, None)
+        sharded.time_sharded_backward(g, states, go, cin, halo, None)
+
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    K = args.time_sharded_steps
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(K):
+        step()
+    b.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    ms = a.elapsed_time(b) / K
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    n = Bt * Ct * Tt
+    gbs = 8 * 4 * n / (ms * 1e-3) / 1e9
+    # kernels per step and rank: scan + backward, plus the two carry reductions when sharded
+    return {"workload": f"({Bt},{Ct},{Tt}) fp32 fwd+bwd, time-sharded over {world} GPU(s)", "scaling": "strong",
+            "value": round(gbs, 1), "unit": UNIT, "ms_per_step": round(ms, 4), "steps": K,
+            "collective": "none" if world == 1 else "all_gather of 3 (forward) + 2 (backward) fp32 per row per rank",
+            "launches_per_step": 2 if world == 1 else 4,
+            "pct_of_measured_peak_per_gpu": round(100 * gbs / world / measured_peak()[0], 2)}
 
 
 def run_e2e(args, torch, dist, warp, dev, world, dtype, esize):
