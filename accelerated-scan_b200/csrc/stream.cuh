@@ -547,15 +547,40 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
             }
 
             // ---- pass 1: lane aggregate in processing order
+            // Real types without interior boundaries run the lane's elements as two half-length
+            // chains side by side in packed fp32x2 instructions (half the instructions, half the
+            // dependent latency); (A0h, B0h) is the aggregate of the first half.
+            constexpr bool PACKED = !INTERIOR && sizeof(V) == 4 && (K % 2 == 0);
+            constexpr int H = K / 2;
             constexpr int JF = REV ? K - 1 : 0;
-            V A = a[JF], B = b[JF];
-            V B2 = (REDUCE && INTERIOR) ? b2[JF] : vzero(V());
+            V A, B, A0h = vone(V()), B0h = vzero(V());
+            V B2 = vzero(V());
+            if constexpr (PACKED) {
+                auto J = [](int q) { return REV ? K - 1 - q : q; };
+                float2 Av = make_float2(a[J(0)], a[J(H)]);
+                float2 Bv = make_float2(b[J(0)], b[J(H)]);
 #pragma unroll
-            for (int q = 1; q < K; ++q) {
-                const int j = REV ? K - 1 - q : q;
-                B = vfma(a[j], B, b[j]);
-                if (REDUCE && INTERIOR) B2 = vfma(a[j], B2, b2[j]);
-                A = vmul(A, a[j]);
+                for (int q = 1; q < H; ++q) {
+                    const float2 av = make_float2(a[J(q)], a[J(H + q)]);
+                    const float2 bv = make_float2(b[J(q)], b[J(H + q)]);
+                    Bv = __ffma2_rn(av, Bv, bv);
+                    Av = __fmul2_rn(Av, av);
+                }
+                A0h = Av.x;
+                B0h = Bv.x;
+                A = Av.x * Av.y;
+                B = fmaf(Av.y, Bv.x, Bv.y);
+            } else {
+                A = a[JF];
+                B = b[JF];
+                if (REDUCE && INTERIOR) B2 = b2[JF];
+#pragma unroll
+                for (int q = 1; q < K; ++q) {
+                    const int j = REV ? K - 1 - q : q;
+                    B = vfma(a[j], B, b[j]);
+                    if (REDUCE && INTERIOR) B2 = vfma(a[j], B2, b2[j]);
+                    A = vmul(A, a[j]);
+                }
             }
             // the warp's incoming state enters through the first lane in processing order
             const int ll = REV ? 31 - lane : lane;
@@ -589,11 +614,24 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
 
             if (!REDUCE) {
                 // ---- pass 2: the recurrence itself from the lane's incoming state
+                if constexpr (PACKED) {
+                    auto J = [](int q) { return REV ? K - 1 - q : q; };
+                    float2 Xv = make_float2(x, fmaf(A0h, x, B0h));   // states entering the two halves
 #pragma unroll
-                for (int q = 0; q < K; ++q) {
-                    const int j = REV ? K - 1 - q : q;
-                    x = vfma(a[j], x, b[j]);
-                    b[j] = x;
+                    for (int q = 0; q < H; ++q) {
+                        const float2 av = make_float2(a[J(q)], a[J(H + q)]);
+                        const float2 bv = make_float2(b[J(q)], b[J(H + q)]);
+                        Xv = __ffma2_rn(av, Xv, bv);
+                        b[J(q)] = Xv.x;
+                        b[J(H + q)] = Xv.y;
+                    }
+                } else {
+#pragma unroll
+                    for (int q = 0; q < K; ++q) {
+                        const int j = REV ? K - 1 - q : q;
+                        x = vfma(a[j], x, b[j]);
+                        b[j] = x;
+                    }
                 }
                 if (KIND == K_BWD) {
                     // d_gates[t] = conj(x[t-1]) * g[t]: the previous state comes from the
