@@ -36,7 +36,8 @@ static int warp_smem(int nch, int stages, int kind, bool bulk) {
     const int tb = 32 * nch * 16;
     const int nstg = bulk ? stages : 1;
     const int outbufs = bulk ? 2 : 1;
-    return nstg * nin_of(kind) * tb + outbufs * nout_of(kind) * tb + 128;
+    const int stage = nin_of(kind) * tb + (kind == ASCAN_KIND_BACKWARD ? 128 : 0);   // + halo slot
+    return nstg * stage + outbufs * nout_of(kind) * tb + 128;
 }
 
 int make_plan(const PlanInput &in, ascan_plan *plan) {

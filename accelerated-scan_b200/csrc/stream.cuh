@@ -82,11 +82,17 @@ struct StreamParams {
 
 __host__ __device__ constexpr int stream_nin(int kind) { return kind == K_BWD ? 3 : 2; }
 __host__ __device__ constexpr int stream_nout(int kind) { return kind == K_SCAN ? 1 : (kind == K_BWD ? 2 : 0); }
+// Bytes of one ring stage: the tiles of the input streams and, for the fused backward, a
+// 128-byte slot whose first 16 bytes receive the chunk of saved states just below the tile
+// (its last element is the state before the tile's first step).
+__host__ __device__ constexpr int stream_stage_bytes(int nch, int kind) {
+    return stream_nin(kind) * 32 * nch * 16 + (kind == K_BWD ? 128 : 0);
+}
 __host__ __device__ constexpr int stream_warp_smem(int nch, int stages, int kind, bool bulk) {
     const int tb = 32 * nch * 16;
     const int nstg = bulk ? stages : 1;
     const int outbufs = bulk ? 2 : 1;
-    return nstg * stream_nin(kind) * tb + outbufs * stream_nout(kind) * tb + 128;
+    return nstg * stream_stage_bytes(nch, kind) + outbufs * stream_nout(kind) * tb + 128;
 }
 
 constexpr uint32_t LOAD_WAIT_POLLS = 1u << 22;
@@ -125,7 +131,8 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
     const int wpc = blockDim.x >> 5;
     unsigned char *wsm = smem_raw + static_cast<size_t>(wib) * WARP_SMEM;
     unsigned char *stage_base = wsm;
-    unsigned char *out_base = wsm + NSTG * NIN * TB;
+    constexpr int STAGE_BYTES = stream_stage_bytes(NCH, KIND);
+    unsigned char *out_base = wsm + NSTG * STAGE_BYTES;
     uint64_t *bars = reinterpret_cast<uint64_t *>(out_base + OUTBUFS * NOUT * TB);
 
     const int64_t w = static_cast<int64_t>(blockIdx.x) * wpc + wib;
@@ -220,14 +227,19 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
     auto issue = [&](const ItemDesc &d, int t, int s) {
         const uint32_t bytes = static_cast<uint32_t>(tile_valid(d, t)) * TR::ESIZE;
         const int64_t goff = (d.e_begin + static_cast<int64_t>(t) * TE) * TR::ESIZE;
-        mbar_expect_tx(&bars[s], bytes * NIN);
+        // fused backward: also the 16 bytes of saved states just below the tile (tiles start
+        // 16-byte aligned, so that chunk is aligned too); skipped at the start of the matrix
+        const bool halo = (KIND == K_BWD) && goff > 0;
+        mbar_expect_tx(&bars[s], bytes * NIN + (halo ? 16u : 0u));
+        unsigned char *dst = stage_base + s * STAGE_BYTES;
 #pragma unroll
         for (int k = 0; k < NIN; ++k) {
             if (ld_hint)
-                bulk_g2s_hint(stage_base + (s * NIN + k) * TB, gbase[k] + goff, bytes, &bars[s], ld_pol);
+                bulk_g2s_hint(dst + k * TB, gbase[k] + goff, bytes, &bars[s], ld_pol);
             else
-                bulk_g2s(stage_base + (s * NIN + k) * TB, gbase[k] + goff, bytes, &bars[s]);
+                bulk_g2s(dst + k * TB, gbase[k] + goff, bytes, &bars[s]);
         }
+        if (halo) bulk_g2s(dst + NIN * TB, gbase[2] + goff - 16, 16, &bars[s]);
     };
 
     if (BULK) {
@@ -375,15 +387,16 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
             const int t = tile_of_step(cur, i);
             const int64_t toff = static_cast<int64_t>(t) * TE;
             const int nvalid = tile_valid(cur, t);
-            const unsigned char *stg = stage_base + cs * NIN * TB;
+            const unsigned char *stg = stage_base + cs * STAGE_BYTES;
 
             // backward: the state just below the tile, needed by lane 0 for d_gates
             Raw x_halo_raw = 0;
             V x_halo_row = vzero(V());
             const bool halo_in_row = (ts_mod != 0);
             if (KIND == K_BWD) {
-                if (halo_in_row) x_halo_raw = TR::load_raw(p.in2, cur.e_begin + toff - 1);
-                else if (!INTERIOR && hstate) x_halo_row = hstate[row_ts];
+                // (the bulk loader brings this state with the tile, see issue())
+                if (halo_in_row && !BULK) x_halo_raw = TR::load_raw(p.in2, cur.e_begin + toff - 1);
+                else if (!halo_in_row && !INTERIOR && hstate) x_halo_row = hstate[row_ts];
             }
             // last tile of the item: fetch the header of the next one now
             ItemHeader head_next = head;
@@ -422,11 +435,17 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
                 TR::unpack(qb, &b[c * EPC]);
             }
             V xp[KIND == K_BWD ? K : 1];
+            V x_below = vzero(V());   // state just below the tile, from the halo chunk
             if (KIND == K_BWD) {
 #pragma unroll
                 for (int c = 0; c < NCH; ++c) {
                     const uint4 qx = *reinterpret_cast<const uint4 *>(stg + 2 * TB + (lane * NCH + c) * 16);
                     TR::unpack(qx, &xp[c * EPC]);
+                }
+                if (BULK && halo_in_row) {
+                    V hv[EPC];
+                    TR::unpack(*reinterpret_cast<const uint4 *>(stg + NIN * TB), hv);
+                    x_below = hv[EPC - 1];
                 }
             }
             if (BULK) {
@@ -637,7 +656,7 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
                     // d_gates[t] = conj(x[t-1]) * g[t]: the previous state comes from the
                     // element below (neighbouring lane by shuffle, tile halo for lane 0)
                     V dn = shfl_up(xp[K - 1], 1);
-                    if (lane == 0) dn = halo_in_row ? TR::decode(x_halo_raw) : x_halo_row;
+                    if (lane == 0) dn = halo_in_row ? (BULK ? x_below : TR::decode(x_halo_raw)) : x_halo_row;
 #pragma unroll
                     for (int j = 1; j < K; ++j) a[j] = vmul(vconj(xp[j - 1]), b[j]);
                     a[0] = vmul(vconj(dn), b[0]);
