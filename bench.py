@@ -312,7 +312,8 @@ def run_b200(args):
             "kernel": "stream_kernel<K_BWD>", "bound": "hbm", "achieved": round(bwd_gbs, 1), "peak": peak,
             "unit": UNIT, "frac": round(bwd_gbs / peak, 4), "peak_kind": f"of {peak_kind}",
             "algorithmic_bytes_per_launch": 5 * esize * N, "ms_per_launch": round(bwd_ms, 5),
-            "traffic": TRAFFIC_BWD_BYTES_PER_ELEM * N if TRAFFIC_BWD_BYTES_PER_ELEM and args.dtype == "bf16" else None,
+            "traffic": int(TRAFFIC_BWD_BYTES_PER_ELEM * N) if TRAFFIC_BWD_BYTES_PER_ELEM and args.dtype == "bf16" else None,
+            "traffic_note": "ncu dram bytes per element on (8,1536,16384), scaled to this launch by rows*T",
         },
         "roofline_forward": {
             "kernel": "stream_kernel<K_SCAN>", "bound": "hbm", "achieved": round(fwd_gbs, 1), "peak": peak,
@@ -331,8 +332,8 @@ def run_b200(args):
 
 
 # DRAM bytes per element of the backward kernel from the ncu capture summarised under
-# profiles/ (dram__bytes_read.sum + dram__bytes_write.sum, scaled per element); None until captured.
-TRAFFIC_BWD_BYTES_PER_ELEM = None
+# profiles/stream_kernel_bf16_8x1536x16384_full_set.md (dram__bytes_read.sum + dram__bytes_write.sum per element).
+TRAFFIC_BWD_BYTES_PER_ELEM = 9.80
 
 
 def run_time_sharded(args, torch, dist, dev, world, rank):
