@@ -115,12 +115,12 @@ def _require_cuda(*tensors):
 _workspaces = {}
 
 
-def workspace(device: torch.device, rows: int = 0) -> torch.Tensor:
+def workspace(device: torch.device, rows: int = 0, seqlen: int = 1, dtype: int = 0, kind: int = 0) -> torch.Tensor:
     """Scratch per (device, stream), owned by torch's allocator and zero-filled once
     when it is created (the kernels rearm it themselves).  It holds the status word,
     the work ticket and one carry record per row; launches on different streams get
     different workspaces because they may overlap."""
-    nbytes = int(lib.ascan_workspace_bytes(int(rows), 1, 0, 0))
+    nbytes = int(lib.ascan_workspace_bytes(int(rows), int(seqlen), int(dtype), int(kind)))
     stream = torch.cuda.current_stream(device).cuda_stream
     key = (device.index, stream)
     ws = _workspaces.get(key)
@@ -131,9 +131,9 @@ def workspace(device: torch.device, rows: int = 0) -> torch.Tensor:
 
 
 def plan(rows: int, seqlen: int, dtype: int, kind: int, aligned: bool = True, workspace: bool = True,
-         sm_count: int = 148) -> dict:
+         sm_count: int = 148, reverse: bool = False, lookback: bool = True) -> dict:
     pl = Plan()
-    flags = int(bool(aligned)) | (int(bool(workspace)) << 1)
+    flags = int(bool(aligned)) | (int(bool(workspace)) << 1) | (int(bool(reverse)) << 2) | (int(not lookback) << 3)
     check(lib.ascan_plan_describe(rows, seqlen, dtype, kind, flags, sm_count, ctypes.byref(pl)),
           "ascan_plan_describe")
     return pl.as_dict()
@@ -144,7 +144,7 @@ def forward(gates, tokens, out, reverse=False, carry_in=None):
     rows = gates.numel() // gates.shape[-1] if gates.shape[-1] else 0
     T = gates.shape[-1]
     with torch.cuda.device(gates.device):
-        ws = workspace(gates.device, rows)
+        ws = workspace(gates.device, rows, T, dtype_code(gates), KIND_FORWARD)
         rc = lib.ascan_forward(_ptr(gates), _ptr(tokens), _ptr(out), rows, T, dtype_code(gates), int(bool(reverse)),
                                _ptr(carry_in), _ptr(ws), ws.numel(), _stream(gates))
     check(rc, "ascan_forward")
@@ -155,7 +155,7 @@ def backward(gates, states, grad_out, d_gates, d_tokens, carry_in=None, halo_gat
     rows = gates.numel() // gates.shape[-1] if gates.shape[-1] else 0
     T = gates.shape[-1]
     with torch.cuda.device(gates.device):
-        ws = workspace(gates.device, rows)
+        ws = workspace(gates.device, rows, T, dtype_code(gates), KIND_BACKWARD)
         rc = lib.ascan_backward(_ptr(gates), _ptr(states), _ptr(grad_out), _ptr(d_gates), _ptr(d_tokens), rows, T,
                                 dtype_code(gates), _ptr(carry_in), _ptr(halo_gate_right), _ptr(halo_state_left),
                                 _ptr(ws), ws.numel(), _stream(gates))

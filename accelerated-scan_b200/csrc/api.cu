@@ -48,9 +48,9 @@ static int ensure_smem(const void *fn, size_t bytes) {
     return ASCAN_OK;
 }
 
-template <class TR, int NCH, int KIND, bool REVERSE, bool BULK, bool INTERIOR>
+template <class TR, int NCH, int KIND, bool REVERSE, bool BULK, bool INTERIOR, bool LOOKBACK = false>
 static int launch_one(const StreamParams &p, const ascan_plan &pl, cudaStream_t stream) {
-    auto kfn = stream_kernel<TR, NCH, KIND, REVERSE, BULK, INTERIOR>;
+    auto kfn = stream_kernel<TR, NCH, KIND, REVERSE, BULK, INTERIOR, LOOKBACK>;
     int rc = ensure_smem(reinterpret_cast<const void *>(kfn), pl.smem_bytes);
     if (rc != ASCAN_OK) return rc;
     kfn<<<pl.grid, pl.warps_per_cta * 32, pl.smem_bytes, stream>>>(p);
@@ -60,6 +60,11 @@ static int launch_one(const StreamParams &p, const ascan_plan &pl, cudaStream_t 
 // INTERIOR: items that group several rows have row boundaries inside their tiles.
 template <class TR, int NCH, int KIND, bool REVERSE, bool BULK>
 static int launch_interior(const StreamParams &p, const ascan_plan &pl, cudaStream_t stream) {
+    // look-back plans exist for the bulk loader and the two scan kinds only
+    if constexpr (BULK && (KIND == K_SCAN || KIND == K_BWD)) {
+        if (pl.kernel == 1) return launch_one<TR, NCH, KIND, REVERSE, BULK, false, true>(p, pl, stream);
+    }
+    if (pl.kernel == 1) return ASCAN_ERR_UNSUPPORTED;
     return pl.rows_per_item > 1 ? launch_one<TR, NCH, KIND, REVERSE, BULK, true>(p, pl, stream)
                                 : launch_one<TR, NCH, KIND, REVERSE, BULK, false>(p, pl, stream);
 }
@@ -96,10 +101,6 @@ static int l2_hints_env() {
 
 static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-static bool workspace_usable(const void *ws, size_t ws_bytes, int64_t rows) {
-    return ws && (reinterpret_cast<uintptr_t>(ws) & 255u) == 0 && ws_bytes >= workspace_bytes(rows);
-}
-
 static int plan_for(int64_t rows, int64_t seqlen, int dtype, int kind, bool aligned, const void *ws, size_t ws_bytes,
                     ascan_plan *pl, bool reverse = false) {
     PlanInput in;
@@ -109,10 +110,20 @@ static int plan_for(int64_t rows, int64_t seqlen, int dtype, int kind, bool alig
     in.dtype = dtype;
     in.kind = kind;
     in.aligned = aligned;
-    in.workspace = workspace_usable(ws, ws_bytes, rows);
+    in.workspace = ws && (reinterpret_cast<uintptr_t>(ws) & 255u) == 0;
     int rc = cached_sm_count(&in.sm_count);
     if (rc != ASCAN_OK) return rc;
-    return make_plan(in, pl);
+    // prefer the plan that wants the most scratch; step down while the caller's is too small
+    rc = make_plan(in, pl);
+    if (rc == ASCAN_OK && pl->workspace_bytes > ws_bytes && in.workspace) {
+        in.allow_lookback = false;
+        rc = make_plan(in, pl);
+        if (rc == ASCAN_OK && pl->workspace_bytes > ws_bytes) {
+            in.workspace = false;
+            rc = make_plan(in, pl);
+        }
+    }
+    return rc;
 }
 
 // Copies the plan's decomposition and the workspace pointers into the kernel parameters.
@@ -236,10 +247,21 @@ int ascan_reduce_backward(const void *gates, const void *grad_out, const void *h
 }
 
 size_t ascan_workspace_bytes(int64_t rows, int64_t seqlen, int dtype, int kind) {
-    (void)seqlen;
-    (void)dtype;
-    (void)kind;
-    return static_cast<size_t>(workspace_bytes(rows));
+    PlanInput in;
+    in.rows = rows;
+    in.seqlen = seqlen < 1 ? 1 : seqlen;
+    in.dtype = dtype;
+    in.kind = kind;
+    in.aligned = true;
+    in.workspace = true;
+    in.reverse = false;
+    if (cached_sm_count(&in.sm_count) != ASCAN_OK) {
+        cudaGetLastError();
+        in.sm_count = 148;          // no device to ask: size for a full B200
+    }
+    ascan_plan pl;
+    if (make_plan(in, &pl) != ASCAN_OK) return static_cast<size_t>(workspace_bytes(rows));
+    return static_cast<size_t>(pl.workspace_bytes);
 }
 
 int ascan_plan_describe(int64_t rows, int64_t seqlen, int dtype, int kind, int flags, int sm_count,
@@ -253,6 +275,7 @@ int ascan_plan_describe(int64_t rows, int64_t seqlen, int dtype, int kind, int f
     in.workspace = (flags & 2) != 0;
     in.reverse = (flags & 4) != 0;
     in.sm_count = sm_count;
+    in.allow_lookback = (flags & 8) == 0;
     if (sm_count <= 0) {
         int rc = cached_sm_count(&in.sm_count);
         if (rc != ASCAN_OK) return rc;

@@ -47,7 +47,6 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     if (in.rows < 0 || in.seqlen < 1 || in.sm_count < 1) return ASCAN_ERR_INVALID_ARG;
 
     ascan_plan pl = {};
-    pl.kernel = 0;
     const int nch = 3;
     const int64_t te = 32 * nch * (16 / esize);
     // tickets and split-row item numbers are 32-bit
@@ -85,7 +84,21 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     const int64_t tiles_row = (in.seqlen + te - 1) / te;
     const bool reverse_order = in.kind == ASCAN_KIND_BACKWARD || in.kind == ASCAN_KIND_REDUCE_BACKWARD || in.reverse;
     const bool can_split = use_ws && (!bulk || align_rows == 1) && env_int("ASCAN_NO_SPLIT", 0) == 0;
-    const int64_t split_min = env_int("ASCAN_SPLIT_MIN_TILES", 32);   // shorter rows stay whole: an item switch costs about a tile
+    // Far fewer rows than warps: chained segments would leave most warps idle, so the
+    // look-back plan lets many warps scan segments of one row at once.  Every segment but a
+    // row's first is streamed twice (aggregate pass, scan pass; the second read finds the data
+    // in L2), which caps this plan near 4 TB/s; measured against the chained plan it wins
+    // below about 0.44 times as many rows as warps.
+    const bool scan_kind = in.kind == ASCAN_KIND_FORWARD || in.kind == ASCAN_KIND_BACKWARD;
+    int lb_tiles = env_int("ASCAN_LOOKBACK_TILES", 8);
+    if (lb_tiles < 1) lb_tiles = 1;
+    const bool lookback = can_split && bulk && scan_kind && in.allow_lookback && 9 * in.rows < 4 * max_warps &&
+                          tiles_row >= 2 * lb_tiles && env_int("ASCAN_NO_LOOKBACK", 0) == 0;
+    if (lookback) {
+        seg_tiles = lb_tiles;
+        fine_tiles = lb_tiles;
+    }
+    const int64_t split_min = lookback ? 2 * lb_tiles : env_int("ASCAN_SPLIT_MIN_TILES", 32);
     if (can_split && tiles_row >= split_min && tiles_row >= 2 * fine_tiles) {
         int64_t fine_region = (static_cast<int64_t>(seg_tiles) * max_warps + in.rows - 1) / (in.rows > 0 ? in.rows : 1);
         fine_region = (fine_region + fine_tiles - 1) / fine_tiles * fine_tiles;      // tiles, multiple of a fine item
@@ -163,7 +176,11 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     pl.warps_per_cta = wpc;
     pl.grid = static_cast<int32_t>(grid);
     pl.smem_bytes = static_cast<uint64_t>(wpc) * wsm;
-    pl.workspace_bytes = use_ws ? workspace_bytes(in.rows) : 0;
+    pl.kernel = (lookback && pl.segs_per_row > 1) ? 1 : 0;
+    pl.workspace_bytes = !use_ws ? 0
+                         : (pl.kernel == 1 ? static_cast<uint64_t>(kCtrlBytes) + static_cast<uint64_t>(in.rows) *
+                                                 pl.segs_per_row * kLookbackRecordBytes
+                                           : workspace_bytes(in.rows));
     *plan = pl;
     return ASCAN_OK;
 }

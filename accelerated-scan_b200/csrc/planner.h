@@ -22,13 +22,16 @@ struct PlanInput {
     int kind;         // ascan_kind
     bool reverse;     // forward kind processed from the row end
     bool aligned;     // every pointer 16-byte aligned
-    bool workspace;   // a workspace of workspace_bytes() is available
+    bool workspace;   // a workspace of the plan's workspace_bytes is available
+    bool allow_lookback = true;   // false: never choose the look-back plan (smaller workspace)
     int sm_count;
 };
 
 int dtype_size(int dtype);   // bytes per element, 0 if unknown
 
-// Workspace a launch over `rows` rows wants: control block + one carry record per row.
+constexpr int kLookbackRecordBytes = 64;     // per (row, segment) record of the look-back plan
+
+// Workspace of the chained plans: control block + one carry record per row.
 uint64_t workspace_bytes(int64_t rows);
 
 // Fills `plan`; returns an ascan_status.

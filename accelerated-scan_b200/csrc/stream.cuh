@@ -38,6 +38,17 @@
 //     rows (INTERIOR = true) row starts fall inside tiles; the gate of a row's first
 //     processed element is forced to zero there, which resets the running state.
 //
+// Look-back mode (LOOKBACK = true), for matrices with fewer rows than warps
+//   Chaining the segments of a row lets only one warp work on a row at a time.  In this
+//   mode every segment but the first of a row is streamed twice by its warp: a first pass
+//   computes only the segment's aggregate (A, B) and publishes it; the warp then looks
+//   back over the records of the preceding segments -- 32 at a time, one per lane --
+//   composing aggregates until it meets a segment whose outgoing state is already known,
+//   publishes its own outgoing state A*x_in + B at once, and only then streams the
+//   segment again (the second read hits L2) to write the scan.  Segments of one row are
+//   thus scanned concurrently by many warps and CTAs; nothing waits for a whole segment
+//   scan.  Records are per (row, segment); every wait is bounded.
+//
 // Kinds: forward scan (optionally reversed), fused backward (reverse scan over the
 // gates shifted by one step plus the d_gates epilogue; shifted operands come from
 // neighbouring lanes by shuffle, tile halos from one scalar load), and the two
@@ -54,6 +65,7 @@ enum : int { K_SCAN = 0, K_BWD = 1, K_REDUCE = 2, K_REDUCE_BWD = 3 };
 enum : int { CTRL_STATUS = 0, CTRL_TICKET = 1, CTRL_DONE = 2, CTRL_EPOCH = 3 };
 constexpr int CTRL_BYTES = 256;        // control block, then one carry record per row
 constexpr int CARRY_RECORD_BYTES = 32;
+constexpr int LOOKBACK_RECORD_BYTES = 64;   // per (row, segment): aggregate A, aggregate B, outgoing state
 
 struct StreamParams {
     const void *in0;         // gates
@@ -105,10 +117,11 @@ struct ItemDesc {
     int64_t n;         // elements in the item
     int32_t s_log;     // segment index in processing order
     int32_t nt;        // tiles in the item
+    int32_t phase;     // look-back mode: 0 = aggregate pass, 1 = scan pass (always 1 otherwise)
     bool valid;
 };
 
-template <class TR, int NCH, int KIND, bool REVERSE, bool BULK, bool INTERIOR>
+template <class TR, int NCH, int KIND, bool REVERSE, bool BULK, bool INTERIOR, bool LOOKBACK>
 __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
     using V = typename TR::V;
     using Raw = typename TR::Raw;
@@ -178,7 +191,7 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
     auto describe = [&](int64_t q) -> ItemDesc {
         ItemDesc d;
         d.valid = q < p.items;
-        d.e_begin = 0; d.row0 = 0; d.pos0 = 0; d.s_log = 0; d.n = 0; d.nt = 0;
+        d.e_begin = 0; d.row0 = 0; d.pos0 = 0; d.s_log = 0; d.n = 0; d.nt = 0; d.phase = 1;
         if (!d.valid) return d;
         if (!split) {
             const int64_t r0 = q * p.rows_per_item;
@@ -211,6 +224,7 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
             d.n = left < len ? left : len;
         }
         d.nt = static_cast<int32_t>((d.n + TE - 1) / TE);
+        if (LOOKBACK && d.s_log > 0) d.phase = 0;
         return d;
     };
 
@@ -256,7 +270,12 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
     ItemDesc nxt = cur;
     auto need_next = [&]() {
         if (!nxt_ready) {
-            nxt = describe(cur.valid ? resolve(raw_next) : p.items);
+            if (LOOKBACK && cur.valid && cur.phase == 0) {
+                nxt = cur;             // the same segment again, this time to write the scan
+                nxt.phase = 1;
+            } else {
+                nxt = describe(cur.valid ? resolve(raw_next) : p.items);
+            }
             nxt_ready = true;
         }
     };
@@ -323,7 +342,7 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
         h.gate_kind = 0;
         h.halo = vone(V());
         if (!d.valid) return h;
-        if (split && d.s_log > 0) {
+        if (!LOOKBACK && split && d.s_log > 0) {
             const unsigned char *rec = p.records + d.row0 * CARRY_RECORD_BYTES;
             h.x = fetch_tagged(rec, 0, TWO_WORDS);
             if (REDUCE) h.x2 = fetch_tagged(rec, 1, TWO_WORDS);
@@ -340,6 +359,7 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
         return h;
     };
     ItemHeader head = fetch_header(cur);
+    V lookback_x_in = vzero(V());   // look-back mode: incoming state of the segment being processed
 
     while (cur.valid && !failed) {
         // ---------------- item prologue: incoming state, halo gate, running position
@@ -348,7 +368,14 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
         // backward kinds: gate of the first element above the tile
         const V item_end_gate = head.gate_kind == 1 ? TR::decode(head.gate) : (head.gate_kind == 2 ? head.halo : vone(V()));
         V next_gate = item_end_gate;
-        if (split && cur.s_log > 0) {
+        const bool agg_pass = LOOKBACK && cur.phase == 0;   // stream for the aggregate only
+        if (LOOKBACK && cur.s_log > 0) {
+            if (agg_pass) {
+                x2_carry = vone(V());          // zero state and unit response: (B, A) of the segment
+            } else {
+                x_carry = lookback_x_in;       // found by the look-back after the aggregate pass
+            }
+        } else if (split && cur.s_log > 0) {
             // state published by the warp that processed the previous segment of this row
             const unsigned char *rec = p.records + cur.row0 * CARRY_RECORD_BYTES;
             const uint32_t want = epoch | static_cast<uint32_t>(cur.s_log);
@@ -603,9 +630,10 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
             }
             // the warp's incoming state enters through the first lane in processing order
             const int ll = REV ? 31 - lane : lane;
+            const bool unit_channel = REDUCE || agg_pass;   // also carry the response to a unit state
             if (ll == 0) {
                 B = vfma(A, x_carry, B);
-                if (REDUCE) B2 = vfma(A, x2_carry, B2);
+                if (unit_channel) B2 = vfma(A, x2_carry, B2);
             }
             // ---- Kogge-Stone inclusive combine across lanes
 #pragma unroll
@@ -613,10 +641,10 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
                 const V Ap = REV ? shfl_down(A, d) : shfl_up(A, d);
                 const V Bp = REV ? shfl_down(B, d) : shfl_up(B, d);
                 V B2p = vzero(V());
-                if (REDUCE) B2p = REV ? shfl_down(B2, d) : shfl_up(B2, d);
+                if (unit_channel) B2p = REV ? shfl_down(B2, d) : shfl_up(B2, d);
                 if (ll >= d) {
                     B = vfma(A, Bp, B);
-                    if (REDUCE) B2 = vfma(A, B2p, B2);
+                    if (unit_channel) B2 = vfma(A, B2p, B2);
                     if (d < 16) A = vmul(A, Ap);
                 }
             }
@@ -629,9 +657,9 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
                 if (ll == 0) x2 = x2_carry;
             }
             x_carry = shfl_idx(B, REV ? 0 : 31);
-            if (REDUCE) x2_carry = shfl_idx(B2, REV ? 0 : 31);
+            if (unit_channel) x2_carry = shfl_idx(B2, REV ? 0 : 31);
 
-            if (!REDUCE) {
+            if (!REDUCE && !agg_pass) {
                 // ---- pass 2: the recurrence itself from the lane's incoming state
                 if constexpr (PACKED) {
                     auto J = [](int q) { return REV ? K - 1 - q : q; };
@@ -759,7 +787,74 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
         if (failed) break;
 
         // ---------------- item epilogue: hand the outgoing state on, move to the next item
-        if (split && cur.s_log + 1 < p.segs_per_row) {
+        if (LOOKBACK) {
+            unsigned char *rec = p.records + (cur.row0 * p.segs_per_row + cur.s_log) * LOOKBACK_RECORD_BYTES;
+            const uint32_t tag = epoch | static_cast<uint32_t>(cur.s_log + 1);
+            if (agg_pass) {
+                // ---- publish the aggregate, look back for the incoming state, publish the outgoing state
+                const V segA = x2_carry, segB = x_carry;
+                if (lane == 0) {
+                    publish_tagged(rec, 0, segA, tag);
+                    publish_tagged(rec, 1, segB, tag);
+                }
+                V accA = vone(V()), accB = vzero(V());      // composition of the segments walked so far
+                int k = cur.s_log - 1;                       // nearest preceding segment
+                bool found = false;
+                uint32_t polls = 0;
+                while (!found) {
+                    // lane i examines segment k - i; segment -1 stands for the row's initial state
+                    const int kk = k - lane;
+                    int state = 0;                           // 0 nothing yet, 1 aggregate, 2 outgoing state
+                    V rA = vone(V()), rB = vzero(V()), rX = vzero(V());
+                    if (kk < 0) {
+                        state = 2;
+                        if (kk == -1 && cin) rX = cin[cur.row0];
+                    } else {
+                        const unsigned char *pr =
+                            p.records + (cur.row0 * p.segs_per_row + kk) * LOOKBACK_RECORD_BYTES;
+                        const uint32_t want = epoch | static_cast<uint32_t>(kk + 1);
+                        if (read_tagged(pr, 2, want, rX)) {
+                            state = 2;
+                        } else {
+                            const bool okA = read_tagged(pr, 0, want, rA);
+                            const bool okB = read_tagged(pr, 1, want, rB);
+                            if (okA && okB) state = 1;
+                        }
+                    }
+                    const uint32_t has_x = __ballot_sync(0xffffffffu, state == 2);
+                    const uint32_t has_any = __ballot_sync(0xffffffffu, state != 0);
+                    const int px = has_x ? __ffs(has_x) - 1 : 32;        // nearest known outgoing state
+                    const uint32_t need = px >= 32 ? 0xffffffffu : ((1u << px) - 1u);
+                    if ((has_any & need) != need) {
+                        // a nearer segment has published nothing yet: poll again, with a bound
+                        if (++polls > CARRY_WAIT_POLLS) {
+                            status_bits |= STATUS_LOOKBACK_TIMEOUT;
+                            break;
+                        }
+                        __nanosleep(100);
+                        continue;
+                    }
+                    // compose the aggregates of lanes 0 .. px-1 (lane 0 is applied last)
+                    for (int i = 0; i < px && i < 32; ++i) {
+                        const V Ai = shfl_idx(rA, i), Bi = shfl_idx(rB, i);
+                        accB = vfma(accA, Bi, accB);
+                        accA = vmul(accA, Ai);
+                    }
+                    if (px < 32) {
+                        const V xs = shfl_idx(rX, px);
+                        lookback_x_in = vfma(accA, xs, accB);
+                        found = true;
+                    } else {
+                        k -= 32;
+                    }
+                }
+                if (!found) lookback_x_in = vzero(V());
+                if (lane == 0) publish_tagged(rec, 2, vfma(segA, lookback_x_in, segB), tag);
+            } else if (cur.s_log == 0 && p.segs_per_row > 1) {
+                // the first segment of a row is scanned straight away; its end state is known now
+                if (lane == 0) publish_tagged(rec, 2, x_carry, tag);
+            }
+        } else if (split && cur.s_log + 1 < p.segs_per_row) {
             if (lane == 0) {
                 unsigned char *rec = p.records + cur.row0 * CARRY_RECORD_BYTES;
                 const uint32_t tag = epoch | static_cast<uint32_t>(cur.s_log + 1);
@@ -775,8 +870,9 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
             }
         }
         need_next();
+        const bool same_ticket = LOOKBACK && cur.phase == 0;   // the scan pass of the same segment follows
         cur = nxt;
-        raw_next = cur.valid ? draw() : 0u;
+        if (!same_ticket) raw_next = cur.valid ? draw() : 0u;
         nxt_ready = false;
         if (prod_in_next) {
             prod_in_next = false;      // the producer's item is now the current one

@@ -58,7 +58,7 @@ typedef enum {
  * of warp.cuh:282-380.  Pure host arithmetic, usable without a GPU when
  * sm_count > 0 is passed. */
 typedef struct {
-    int32_t kernel;            /* 0 = warp-stream kernel                                   */
+    int32_t kernel;            /* 0 = segments of a row chained, 1 = look-back (few rows: segments of a row scanned concurrently) */
     int32_t loader;            /* 0 = bulk-async copies into shared-memory stages, 1 = plain element loads (unaligned data) */
     int32_t chunks_per_lane;   /* 16-byte chunks each lane owns per tile                  */
     int32_t stages;            /* shared-memory stages per warp                            */
@@ -139,17 +139,18 @@ int ascan_reduce_backward(const void *gates, const void *grad_out,
 
 /*
  * Scratch bytes a call of `kind` with these sizes can use: a control block
- * (status word, work ticket) plus one carry record per row.  With at least that
- * much scratch the kernels balance work over the SMs dynamically and split long
- * rows across warps; with less (or NULL) they fall back to a static deal of whole
- * rows, which is correct but slower.
+ * (status word, work ticket) plus one carry record per row, or per (row, segment)
+ * when the look-back plan applies (fewer rows than warps).  With that much scratch
+ * the kernels balance work over the SMs dynamically and split long rows across
+ * warps and CTAs; with less they step down to the chained plan (256 + 32*rows
+ * bytes), and with none (NULL) to a static deal of whole rows: correct, slower.
  */
 size_t ascan_workspace_bytes(int64_t rows, int64_t seqlen, int dtype, int kind);
 
 /*
  * The plan the library would use.  flags: bit 0 = every pointer is 16-byte
  * aligned, bit 1 = a workspace of ascan_workspace_bytes() is supplied, bit 2 =
- * forward kind with reverse != 0;
+ * forward kind with reverse != 0, bit 3 = never choose the look-back plan;
  * sm_count <= 0 queries the current device.  Host only.
  */
 int ascan_plan_describe(int64_t rows, int64_t seqlen, int dtype, int kind,

@@ -62,7 +62,16 @@ def test_planner_invariants(T, dtype, kind):
         assert pl["row_groups"] * pl["rows_per_item"] >= rows
         assert pl["segs_per_row"] == pl["coarse_segs"] + pl["fine_segs"]
         assert pl["coarse_segs"] * pl["seg_elems"] + pl["fine_segs"] * pl["fine_elems"] >= T
-        assert pl["dynamic"] == 1 and pl["workspace_bytes"] == 256 + 32 * rows
+        assert pl["dynamic"] == 1
+        if pl["kernel"] == 1:
+            # look-back plan: fewer rows than warps, per-(row, segment) records, equal small segments
+            assert 9 * rows < 4 * 148 * 12 and kind in (0, 1) and pl["segs_per_row"] > 1
+            assert pl["workspace_bytes"] == 256 + 64 * rows * pl["segs_per_row"]
+            assert pl["seg_elems"] == pl["fine_elems"]
+            chained = _native.plan(rows, T, dtype, kind, sm_count=148, lookback=False)
+            assert chained["kernel"] == 0 and chained["workspace_bytes"] == 256 + 32 * rows
+        else:
+            assert pl["workspace_bytes"] == 256 + 32 * rows
         if pl["segs_per_row"] > 1:
             # split rows: one row per item, segments are whole tiles
             assert pl["rows_per_item"] == 1 and pl["seg_elems"] % pl["tile_elems"] == 0

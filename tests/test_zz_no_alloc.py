@@ -30,7 +30,7 @@ def test_no_alloc_matches_workspace_entry_point(cuda_device, shape, dtype):
     rows, T = shape[0] * shape[1], shape[2]
     code = _native.DTYPE_CODE[dtype]
     # long rows: both entry points split them into segments and pass carries through scratch
-    assert _native.plan(rows, T, code, _native.KIND_FORWARD)["segs_per_row"] > 1
+    assert _native.plan(rows, T, code, _native.KIND_FORWARD, lookback=False)["segs_per_row"] > 1
     stream = ctypes.c_void_p(torch.cuda.current_stream(cuda_device).cuda_stream)
     for call, seed in enumerate((21, 22)):
         gates, tokens, _ = real_inputs(seed, shape, law="near_one", dtype=dtype, grad=False)
@@ -42,8 +42,10 @@ def test_no_alloc_matches_workspace_entry_point(cuda_device, shape, dtype):
             rc = lib.ascan_forward_no_alloc(_ptr(g), _ptr(x), _ptr(got), rows, T, code, reverse, stream)
             assert rc == 0, _native.strerror(rc)
             torch.cuda.synchronize(cuda_device)
-            assert rel_err(to_np(got), to_np(want)) <= FP32_REL, (call, reverse)
-            assert torch.equal(got, want), (call, reverse)
+            # (the two may plan differently -- the built-in scratch is too small for per-segment
+            # look-back records -- so the results agree to rounding, not bit for bit)
+            tol = FP32_REL if dtype == torch.float32 else 2.0 ** -7
+            assert rel_err(to_np(got), to_np(want)) <= tol, (call, reverse)
 
 
 def test_no_alloc_rejects_too_many_rows(cuda_device):
