@@ -32,6 +32,7 @@ class Plan(ctypes.Structure):
         ("kernel", ctypes.c_int32), ("loader", ctypes.c_int32), ("chunks_per_lane", ctypes.c_int32),
         ("stages", ctypes.c_int32), ("warps_per_cta", ctypes.c_int32), ("grid", ctypes.c_int32),
         ("tile_elems", ctypes.c_int32), ("dynamic", ctypes.c_int32),
+        ("team_size", ctypes.c_int32), ("reserved", ctypes.c_int32),
         ("rows_per_item", ctypes.c_int64), ("row_groups", ctypes.c_int64), ("seg_elems", ctypes.c_int64),
         ("fine_elems", ctypes.c_int64), ("coarse_segs", ctypes.c_int64), ("fine_segs", ctypes.c_int64),
         ("segs_per_row", ctypes.c_int64), ("items", ctypes.c_int64),
@@ -131,9 +132,10 @@ def workspace(device: torch.device, rows: int = 0, seqlen: int = 1, dtype: int =
 
 
 def plan(rows: int, seqlen: int, dtype: int, kind: int, aligned: bool = True, workspace: bool = True,
-         sm_count: int = 148, reverse: bool = False, lookback: bool = True) -> dict:
+         sm_count: int = 148, reverse: bool = False, lookback: bool = True, team: bool = True) -> dict:
     pl = Plan()
-    flags = int(bool(aligned)) | (int(bool(workspace)) << 1) | (int(bool(reverse)) << 2) | (int(not lookback) << 3)
+    flags = (int(bool(aligned)) | (int(bool(workspace)) << 1) | (int(bool(reverse)) << 2) | (int(not lookback) << 3)
+             | (int(not team) << 4))
     check(lib.ascan_plan_describe(rows, seqlen, dtype, kind, flags, sm_count, ctypes.byref(pl)),
           "ascan_plan_describe")
     return pl.as_dict()

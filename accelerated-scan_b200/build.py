@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "accelerated_scan", "libascan_b200.so")
 SOURCES = ["api.cu", "planner.cpp"]
-HEADERS = ["common.cuh", "stream.cuh", "planner.h", os.path.join("..", "..", "include", "ascan_b200.h")]
+HEADERS = ["common.cuh", "stream.cuh", "team.cuh", "planner.h", os.path.join("..", "..", "include", "ascan_b200.h")]
 
 
 def _nvcc() -> str:

@@ -11,6 +11,7 @@
 #include "../../include/ascan_b200.h"
 #include "planner.h"
 #include "stream.cuh"
+#include "team.cuh"
 
 namespace ascan {
 
@@ -60,11 +61,18 @@ static int launch_one(const StreamParams &p, const ascan_plan &pl, cudaStream_t 
 // INTERIOR: items that group several rows have row boundaries inside their tiles.
 template <class TR, int NCH, int KIND, bool REVERSE, bool BULK>
 static int launch_interior(const StreamParams &p, const ascan_plan &pl, cudaStream_t stream) {
-    // look-back plans exist for the bulk loader and the two scan kinds only
+    // look-back and team plans exist for the bulk loader and the two scan kinds only
     if constexpr (BULK && (KIND == K_SCAN || KIND == K_BWD)) {
         if (pl.kernel == 1) return launch_one<TR, NCH, KIND, REVERSE, BULK, false, true>(p, pl, stream);
+        if (pl.kernel == 2) {
+            auto kfn = team_kernel<TR, NCH, KIND, REVERSE>;
+            int rc = ensure_smem(reinterpret_cast<const void *>(kfn), pl.smem_bytes);
+            if (rc != ASCAN_OK) return rc;
+            kfn<<<pl.grid, pl.warps_per_cta * 32, pl.smem_bytes, stream>>>(p);
+            return cudaGetLastError() == cudaSuccess ? ASCAN_OK : ASCAN_ERR_LAUNCH;
+        }
     }
-    if (pl.kernel == 1) return ASCAN_ERR_UNSUPPORTED;
+    if (pl.kernel != 0) return ASCAN_ERR_UNSUPPORTED;
     return pl.rows_per_item > 1 ? launch_one<TR, NCH, KIND, REVERSE, BULK, true>(p, pl, stream)
                                 : launch_one<TR, NCH, KIND, REVERSE, BULK, false>(p, pl, stream);
 }
@@ -142,6 +150,7 @@ static void fill_common(StreamParams &p, const ascan_plan &pl, int64_t rows, int
     p.records = pl.dynamic ? static_cast<unsigned char *>(ws) + CTRL_BYTES : nullptr;
     p.stages = pl.stages;
     p.l2_hints = l2_hints_env();
+    p.team_size = pl.team_size;
 }
 
 }  // namespace ascan
@@ -276,6 +285,7 @@ int ascan_plan_describe(int64_t rows, int64_t seqlen, int dtype, int kind, int f
     in.reverse = (flags & 4) != 0;
     in.sm_count = sm_count;
     in.allow_lookback = (flags & 8) == 0;
+    in.allow_team = (flags & 16) == 0;
     if (sm_count <= 0) {
         int rc = cached_sm_count(&in.sm_count);
         if (rc != ASCAN_OK) return rc;

@@ -2,6 +2,8 @@
 
 #include <stdlib.h>
 
+#include <initializer_list>
+
 namespace ascan {
 
 int dtype_size(int dtype) {
@@ -84,23 +86,44 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     const int64_t tiles_row = (in.seqlen + te - 1) / te;
     const bool reverse_order = in.kind == ASCAN_KIND_BACKWARD || in.kind == ASCAN_KIND_REDUCE_BACKWARD || in.reverse;
     const bool can_split = use_ws && (!bulk || align_rows == 1) && env_int("ASCAN_NO_SPLIT", 0) == 0;
-    // Far fewer rows than warps: chained segments would leave most warps idle, so the
-    // look-back plan lets many warps scan segments of one row at once.  Every segment but a
-    // row's first is streamed twice (aggregate pass, scan pass; the second read finds the data
-    // in L2), which caps this plan near 4 TB/s; measured against the chained plan it wins
-    // below about 0.44 times as many rows as warps.
+    // Fewer rows than SMs: even a whole CTA per row (the team plan below) would leave SMs
+    // idle, so the look-back plan lets warps of many CTAs scan segments of one row at once.
+    // Every segment but a row's first is streamed twice (aggregate pass, scan pass; the second
+    // read finds the data in L2), which caps this plan near 4 TB/s.
     const bool scan_kind = in.kind == ASCAN_KIND_FORWARD || in.kind == ASCAN_KIND_BACKWARD;
     int lb_tiles = env_int("ASCAN_LOOKBACK_TILES", 8);
+    const int64_t lookback_rows = env_int("ASCAN_LOOKBACK_ROWS", in.sm_count);   // below one row per SM
     if (lb_tiles < 1) lb_tiles = 1;
-    const bool lookback = can_split && bulk && scan_kind && in.allow_lookback && 9 * in.rows < 4 * max_warps &&
+    const bool lookback = can_split && bulk && scan_kind && in.allow_lookback && in.rows < lookback_rows &&
                           tiles_row >= 2 * lb_tiles && env_int("ASCAN_NO_LOOKBACK", 0) == 0;
     if (lookback) {
         seg_tiles = lb_tiles;
         fine_tiles = lb_tiles;
     }
-    const int64_t split_min = lookback ? 2 * lb_tiles : env_int("ASCAN_SPLIT_MIN_TILES", 32);
+    // Fewer rows than warps, but too many for look-back to pay: teams of G warps share an
+    // item, so that all warps work although only rows/G... teams can be busy at once.  G is
+    // the smallest divisor of the warps per CTA with (warps / G) <= rows.
+    int team = 1;
+    if (!lookback && can_split && bulk && scan_kind && in.allow_team && in.rows > 0 && in.rows < max_warps &&
+        env_int("ASCAN_NO_TEAM", 0) == 0) {
+        const int64_t want = (max_warps + in.rows - 1) / in.rows;
+        for (int cand : {2, 3, 4, 6, 12}) {
+            if (cand >= want) {
+                team = cand;
+                break;
+            }
+        }
+        if (team == 1) team = 12;
+        const int team_env = env_int("ASCAN_TEAM", 0);
+        if (team_env == 2 || team_env == 3 || team_env == 4 || team_env == 6 || team_env == 12) team = team_env;
+        if (seg_tiles < 4 * team) seg_tiles = 4 * team;
+        if (fine_tiles < 2 * team) fine_tiles = 2 * team;
+        if (tiles_row < 2 * team) team = 1;           // rows too short to share
+    }
+    const int64_t workers = max_warps / team;
+    const int64_t split_min = lookback ? 2 * lb_tiles : (team > 1 ? 2 * fine_tiles : env_int("ASCAN_SPLIT_MIN_TILES", 32));
     if (can_split && tiles_row >= split_min && tiles_row >= 2 * fine_tiles) {
-        int64_t fine_region = (static_cast<int64_t>(seg_tiles) * max_warps + in.rows - 1) / (in.rows > 0 ? in.rows : 1);
+        int64_t fine_region = (static_cast<int64_t>(seg_tiles) * workers + in.rows - 1) / (in.rows > 0 ? in.rows : 1);
         fine_region = (fine_region + fine_tiles - 1) / fine_tiles * fine_tiles;      // tiles, multiple of a fine item
         if (fine_region > tiles_row) fine_region = tiles_row;
         int64_t coarse_tiles = tiles_row - fine_region;                               // may be 0
@@ -155,8 +178,9 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     if (stages > 8) stages = 8;
     pl.stages = bulk ? stages : 1;
 
+    // (the team kernel's backward stage has the same 128-byte halo slot, so the sizes agree)
     const int wsm = warp_smem(nch, pl.stages, in.kind, bulk);
-    int wpc = kMaxSmemPerCta / wsm;
+    int wpc = (kMaxSmemPerCta - (team > 1 ? kMaxWarpsPerCta / team * 256 : 0)) / wsm;
     if (wpc > kMaxWarpsPerCta) wpc = kMaxWarpsPerCta;
     const int wpc_env = env_int("ASCAN_WPC", 0);
     if (wpc_env > 0 && wpc_env < wpc) wpc = wpc_env;
@@ -173,10 +197,17 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
         grid = (pl.items + wpc - 1) / wpc;
         if (grid < 1) grid = 1;
     }
+    if (team > 1) {
+        // whole teams only, one persistent CTA per SM
+        wpc = kMaxWarpsPerCta;
+        grid = in.sm_count;
+        if (pl.rows_per_item != 1 || static_cast<int64_t>(wpc) * wsm + wpc / team * 256 > kMaxSmemPerCta) team = 1;
+    }
+    pl.team_size = team;
     pl.warps_per_cta = wpc;
     pl.grid = static_cast<int32_t>(grid);
-    pl.smem_bytes = static_cast<uint64_t>(wpc) * wsm;
-    pl.kernel = (lookback && pl.segs_per_row > 1) ? 1 : 0;
+    pl.smem_bytes = static_cast<uint64_t>(wpc) * wsm + (team > 1 ? static_cast<uint64_t>(wpc / team) * 256 : 0);
+    pl.kernel = (lookback && pl.segs_per_row > 1) ? 1 : (team > 1 ? 2 : 0);
     pl.workspace_bytes = !use_ws ? 0
                          : (pl.kernel == 1 ? static_cast<uint64_t>(kCtrlBytes) + static_cast<uint64_t>(in.rows) *
                                                  pl.segs_per_row * kLookbackRecordBytes

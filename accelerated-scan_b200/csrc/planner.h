@@ -24,6 +24,7 @@ struct PlanInput {
     bool aligned;     // every pointer 16-byte aligned
     bool workspace;   // a workspace of the plan's workspace_bytes is available
     bool allow_lookback = true;   // false: never choose the look-back plan (smaller workspace)
+    bool allow_team = true;       // false: never choose the team plan
     int sm_count;
 };
 

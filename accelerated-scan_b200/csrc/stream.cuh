@@ -90,6 +90,7 @@ struct StreamParams {
     unsigned char *records;  // per-row carry records (segs_per_row > 1)
     int32_t stages;          // shared-memory stages per warp (bulk loader)
     int32_t l2_hints;        // bits 0-1: loads (0 none, 1 evict_first, 2 evict_last); bits 2-3: stores
+    int32_t team_size;       // warps per team (team kernel only)
 };
 
 __host__ __device__ constexpr int stream_nin(int kind) { return kind == K_BWD ? 3 : 2; }

@@ -58,7 +58,7 @@ typedef enum {
  * of warp.cuh:282-380.  Pure host arithmetic, usable without a GPU when
  * sm_count > 0 is passed. */
 typedef struct {
-    int32_t kernel;            /* 0 = segments of a row chained, 1 = look-back (few rows: segments of a row scanned concurrently) */
+    int32_t kernel;            /* 0 = stream: one warp per item, segments of a row chained; 1 = look-back (very few rows: segments of a row scanned concurrently); 2 = team (fewer rows than warps: several warps share an item) */
     int32_t loader;            /* 0 = bulk-async copies into shared-memory stages, 1 = plain element loads (unaligned data) */
     int32_t chunks_per_lane;   /* 16-byte chunks each lane owns per tile                  */
     int32_t stages;            /* shared-memory stages per warp                            */
@@ -66,6 +66,8 @@ typedef struct {
     int32_t grid;              /* persistent CTAs                                          */
     int32_t tile_elems;        /* elements per warp tile                                   */
     int32_t dynamic;           /* 1 = items drawn from a ticket counter in the workspace   */
+    int32_t team_size;         /* warps that share an item (1 unless kernel == 2)          */
+    int32_t reserved;
     int64_t rows_per_item;     /* rows grouped into one item when rows are not split       */
     int64_t row_groups;        /* ceil(rows / rows_per_item)                               */
     int64_t seg_elems;         /* steps per coarse segment when rows are split             */
@@ -150,7 +152,8 @@ size_t ascan_workspace_bytes(int64_t rows, int64_t seqlen, int dtype, int kind);
 /*
  * The plan the library would use.  flags: bit 0 = every pointer is 16-byte
  * aligned, bit 1 = a workspace of ascan_workspace_bytes() is supplied, bit 2 =
- * forward kind with reverse != 0, bit 3 = never choose the look-back plan;
+ * forward kind with reverse != 0, bit 3 = never choose the look-back plan, bit 4 = never
+ * choose the team plan;
  * sm_count <= 0 queries the current device.  Host only.
  */
 int ascan_plan_describe(int64_t rows, int64_t seqlen, int dtype, int kind,

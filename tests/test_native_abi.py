@@ -65,13 +65,21 @@ def test_planner_invariants(T, dtype, kind):
         assert pl["dynamic"] == 1
         if pl["kernel"] == 1:
             # look-back plan: fewer rows than warps, per-(row, segment) records, equal small segments
-            assert 9 * rows < 4 * 148 * 12 and kind in (0, 1) and pl["segs_per_row"] > 1
+            assert rows < 148 and kind in (0, 1) and pl["segs_per_row"] > 1
             assert pl["workspace_bytes"] == 256 + 64 * rows * pl["segs_per_row"]
             assert pl["seg_elems"] == pl["fine_elems"]
-            chained = _native.plan(rows, T, dtype, kind, sm_count=148, lookback=False)
+            chained = _native.plan(rows, T, dtype, kind, sm_count=148, lookback=False, team=False)
             assert chained["kernel"] == 0 and chained["workspace_bytes"] == 256 + 32 * rows
         else:
             assert pl["workspace_bytes"] == 256 + 32 * rows
+        if pl["kernel"] == 2:
+            # team plan: fewer rows than warps, whole teams per CTA, rows never grouped
+            assert rows < 148 * 12 and kind in (0, 1) and pl["loader"] == 0
+            assert pl["team_size"] in (2, 3, 4, 6, 12) and pl["warps_per_cta"] % pl["team_size"] == 0
+            assert pl["rows_per_item"] == 1 and pl["grid"] == 148
+            assert (148 * 12) // pl["team_size"] <= max(rows, 148) or pl["team_size"] == 12
+        else:
+            assert pl["team_size"] == 1
         if pl["segs_per_row"] > 1:
             # split rows: one row per item, segments are whole tiles
             assert pl["rows_per_item"] == 1 and pl["seg_elems"] % pl["tile_elems"] == 0
