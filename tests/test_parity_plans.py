@@ -1,0 +1,128 @@
+"""Every launch plan of the planner against the CPU oracle: the stream kernel with
+chained segments, the look-back plan (fewer rows than SMs) and the team plan (fewer rows
+than warps, 2..12 warps per item), for all kinds, dtypes and the seeded forms.  The plan
+a shape gets is asserted, so a planner change cannot silently drop the coverage."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import complex_inputs, real_inputs, rel_err, to_np
+from oracle import scan_oracle
+
+pytestmark = pytest.mark.gpu
+
+TOL = {torch.float32: 1e-5, torch.complex64: 1e-5, torch.bfloat16: 2.0 ** -8, torch.float16: 2.0 ** -10}
+
+
+def _inputs(dtype, shape, seed=13):
+    if dtype == torch.complex64:
+        return complex_inputs(seed, shape, law="cfg4")
+    law = "uniform" if dtype == torch.float16 else "near_one"
+    return real_inputs(seed, shape, law=law, dtype=dtype)
+
+
+def _up(t):
+    return t.numpy() if t.dtype in (torch.float32, torch.complex64) else t.float().numpy()
+
+
+# rows, seqlen, expected plan kernel (0 stream, 1 look-back, 2 team), expected team size (0 = any)
+CASES = [
+    (2000, 8192, 0, 1),       # more rows than warps: chained stream kernel
+    (1024, 16384, 2, 2),      # config-5-like: two warps per item
+    (700, 9000, 2, 3),
+    (450, 12288, 2, 4),
+    (300, 20000, 2, 6),
+    (160, 33000, 2, 12),
+    (100, 50000, 1, 1),       # fewer rows than SMs: look-back
+    (3, 400000, 1, 1),
+]
+
+
+@pytest.mark.parametrize("rows,seqlen,kernel,team", CASES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.complex64])
+def test_plan_parity(cuda_device, rows, seqlen, kernel, team, dtype):
+    from accelerated_scan import _native
+
+    if dtype == torch.complex64:
+        seqlen = seqlen // 2          # same bytes per row
+    code = _native.DTYPE_CODE[dtype]
+    for kind in (_native.KIND_FORWARD, _native.KIND_BACKWARD):
+        pl = _native.plan(rows, seqlen, code, kind)
+        assert pl["kernel"] == kernel, pl
+        assert pl["team_size"] == team, pl
+    shape = (1, rows, seqlen)
+    gates, tokens, grad_out = _inputs(dtype, shape)
+    want = scan_oracle.scan(_up(gates), _up(tokens))
+    want_rev = scan_oracle.scan(_up(gates), _up(tokens), reverse=True)
+    g, x, go = gates.to(cuda_device), tokens.to(cuda_device), grad_out.to(cuda_device)
+    out, rev = torch.empty_like(x), torch.empty_like(x)
+    _native.forward(g, x, out)
+    _native.forward(g, x, rev, reverse=True)
+    tol = TOL[dtype]
+    assert rel_err(to_np(out), want) <= tol
+    assert rel_err(to_np(rev), want_rev) <= tol
+    states = to_np(out) if dtype == torch.bfloat16 else want
+    want_dg, want_dx = scan_oracle.scan_backward(_up(gates), states, _up(grad_out))
+    dg, dx = torch.empty_like(x), torch.empty_like(x)
+    _native.backward(g, out, go, dg, dx)
+    assert rel_err(to_np(dx), want_dx) <= tol
+    assert rel_err(to_np(dg), want_dg) <= tol
+    _native.check_status(cuda_device)
+
+
+@pytest.mark.parametrize("rows,seqlen", [(1024, 12000), (300, 20000), (100, 30000), (2000, 6000)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.complex64])
+def test_plan_seeded_forms(cuda_device, rows, seqlen, dtype):
+    """carry_in, halo_gate_right and halo_state_left under every plan: scanning the second
+    half of a sequence seeded with the first half's state equals the unsharded result."""
+    from accelerated_scan import _native, sharded
+
+    shape = (1, rows, 2 * seqlen)
+    gates, tokens, grad_out = _inputs(dtype, shape, seed=29)
+    want = scan_oracle.scan(_up(gates), _up(tokens))
+    want_dg, want_dx = scan_oracle.scan_backward(_up(gates), want, _up(grad_out))
+    cdt = sharded.compute_dtype(dtype)
+    half = lambda t, h: t[..., h * seqlen:(h + 1) * seqlen].contiguous().to(cuda_device)
+    g0, g1, x0, x1, go0, go1 = half(gates, 0), half(gates, 1), half(tokens, 0), half(tokens, 1), half(grad_out, 0), half(grad_out, 1)
+    s0 = torch.empty_like(x0)
+    _native.forward(g0, x0, s0)
+    carry = s0[0, :, -1].to(cdt).contiguous()
+    s1 = torch.empty_like(x1)
+    _native.forward(g1, x1, s1, carry_in=carry)
+    got = torch.cat([s0, s1], dim=-1)
+    assert rel_err(to_np(got), want) <= 1e-5
+    # backward of the second half needs the state before it; the first half needs the adjoint after it
+    dg1, dx1 = torch.empty_like(x1), torch.empty_like(x1)
+    _native.backward(g1, s1, go1, dg1, dx1, halo_state_left=carry)
+    g_in = dx1[0, :, 0].to(cdt).contiguous()
+    first_gate = g1[0, :, 0].to(cdt).contiguous()
+    dg0, dx0 = torch.empty_like(x0), torch.empty_like(x0)
+    _native.backward(g0, s0, go0, dg0, dx0, carry_in=g_in, halo_gate_right=first_gate)
+    assert rel_err(to_np(torch.cat([dx0, dx1], dim=-1)), want_dx) <= 1e-5
+    assert rel_err(to_np(torch.cat([dg0, dg1], dim=-1)), want_dg) <= 1e-5
+    _native.check_status(cuda_device)
+
+
+def test_small_workspace_steps_down_to_chained(cuda_device):
+    """A caller-supplied workspace that only fits the chained plan (256 + 32*rows bytes)
+    still gives the right answer for a shape whose preferred plan is look-back."""
+    import ctypes
+    from accelerated_scan import _native
+
+    rows, T = 16, 120000
+    gates, tokens, _ = real_inputs(31, (1, rows, T), grad=False)
+    want = scan_oracle.scan(gates.numpy(), tokens.numpy())
+    g, x = gates.to(cuda_device), tokens.to(cuda_device)
+    out = torch.empty_like(x)
+    ws = torch.zeros(256 + 32 * rows, dtype=torch.uint8, device=cuda_device)
+    assert _native.lib.ascan_workspace_bytes(rows, T, _native.F32, 0) > ws.numel()
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    rc = _native.lib.ascan_forward(p(g), p(x), p(out), rows, T, _native.F32, 0, None, p(ws), ws.numel(),
+                                   ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    assert rel_err(to_np(out), want) <= 1e-5
+    out2 = torch.empty_like(x)
+    rc = _native.lib.ascan_forward(p(g), p(x), p(out2), rows, T, _native.F32, 0, None, None, 0,
+                                   ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    assert rel_err(to_np(out2), want) <= 1e-5
