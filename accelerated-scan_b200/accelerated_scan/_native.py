@@ -67,6 +67,8 @@ def _load():
     lib.ascan_plan_describe.argtypes = [i64, i64, i32, i32, i32, i32, ctypes.POINTER(Plan)]
     lib.ascan_check.restype = i32
     lib.ascan_check.argtypes = [vp, vp]
+    lib.ascan_fold_carries.restype = i32
+    lib.ascan_fold_carries.argtypes = [vp, i64, i32, i32, i32, i32, i32, vp, vp, vp]
     lib.ascan_forward_no_alloc.restype = i32
     lib.ascan_forward_no_alloc.argtypes = [vp, vp, vp, i64, i64, i32, i32, vp]
     return lib
@@ -77,7 +79,7 @@ lib = _load()
 EXPORTS = (
     "ascan_version", "ascan_strerror", "ascan_forward", "ascan_backward", "ascan_reduce_forward",
     "ascan_reduce_backward", "ascan_workspace_bytes", "ascan_plan_describe", "ascan_check",
-    "ascan_forward_no_alloc",
+    "ascan_forward_no_alloc", "ascan_fold_carries",
 )
 
 
@@ -182,6 +184,21 @@ def reduce_backward(gates, grad_out, halo_gate_right, carry_out):
         rc = lib.ascan_reduce_backward(_ptr(gates), _ptr(grad_out), _ptr(halo_gate_right), _ptr(carry_out), rows,
                                        gates.shape[-1], dtype_code(gates), _ptr(ws), ws.numel(), _stream(gates))
     check(rc, "ascan_reduce_backward")
+
+
+def fold_carries(gathered, rank: int, suffix: bool, want_halo: bool = False):
+    """gathered: (world, rows, stride) tensor of float32 or complex64 on the GPU.  Returns
+    (state, halo_or_None), each of `rows` values."""
+    _require_cuda(gathered)
+    world, rows, stride = gathered.shape
+    state = torch.empty(rows, dtype=gathered.dtype, device=gathered.device)
+    halo = torch.empty(rows, dtype=gathered.dtype, device=gathered.device) if want_halo else None
+    code = C64 if gathered.dtype == torch.complex64 else F32
+    with torch.cuda.device(gathered.device):
+        rc = lib.ascan_fold_carries(_ptr(gathered), rows, world, int(rank), stride, code, int(bool(suffix)),
+                                    _ptr(state), _ptr(halo), _stream(gathered))
+    check(rc, "ascan_fold_carries")
+    return state, halo
 
 
 def check_status(device=None) -> None:

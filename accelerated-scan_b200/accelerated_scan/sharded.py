@@ -11,7 +11,7 @@ The reference has no multi-device path.  Two ways to shard exist:
       2. ONE all_gather of the carries (plus the first gate of each slice, which the
          backward needs as its right halo): 3 values per row per rank
       3. each rank folds the carries of the ranks before it into its incoming state
-         and runs the scan seeded with it                     -- `ascan_forward(carry_in)`
+         (`ascan_fold_carries`) and runs the scan seeded with it -- `ascan_forward(carry_in)`
   The backward mirrors it with the ranks after it: `ascan_reduce_backward`, one
   all_gather of (P', S'), a suffix fold, and the seeded fused backward
   (`carry_in`, `halo_gate_right`, `halo_state_left`).
@@ -74,11 +74,12 @@ class NativeOps:
     """The local steps on the CUDA kernels (C ABI)."""
 
     @staticmethod
-    def reduce_forward(gates, tokens):
+    def reduce_forward(gates, tokens, payload):
+        """Writes (P, S) of every row into payload[:, 0:2] (payload: (rows, >=2), compute dtype)."""
         rows = gates.numel() // gates.shape[-1]
-        carry = torch.empty(rows, 2, dtype=compute_dtype(gates.dtype), device=gates.device)
+        carry = torch.empty(rows, 2, dtype=payload.dtype, device=gates.device)
         _native.reduce_forward(gates, tokens, carry)
-        return carry[:, 0], carry[:, 1]
+        payload[:, 0:2] = carry
 
     @staticmethod
     def forward(gates, tokens, carry_in):
@@ -87,11 +88,11 @@ class NativeOps:
         return out
 
     @staticmethod
-    def reduce_backward(gates, grad_out, halo_gate_right):
+    def reduce_backward(gates, grad_out, halo_gate_right, payload):
         rows = gates.numel() // gates.shape[-1]
-        carry = torch.empty(rows, 2, dtype=compute_dtype(gates.dtype), device=gates.device)
+        carry = torch.empty(rows, 2, dtype=payload.dtype, device=gates.device)
         _native.reduce_backward(gates, grad_out, halo_gate_right, carry)
-        return carry[:, 0], carry[:, 1]
+        payload[:, 0:2] = carry
 
     @staticmethod
     def backward(gates, states, grad_out, carry_in, halo_gate_right, halo_state_left):
@@ -100,6 +101,22 @@ class NativeOps:
         _native.backward(gates, states, grad_out, d_gates, d_tokens, carry_in=carry_in,
                          halo_gate_right=halo_gate_right, halo_state_left=halo_state_left)
         return d_gates, d_tokens
+
+    @staticmethod
+    def fold(gathered, rank, suffix, want_halo):
+        """One small kernel instead of a chain of tensor ops (ascan_fold_carries)."""
+        return _native.fold_carries(gathered, rank, suffix, want_halo)
+
+
+def fold_with_tensor_ops(gathered, rank, suffix, want_halo):
+    """The same fold with plain tensor arithmetic (any device); gathered: (world, rows, stride)."""
+    prod, state = gathered[:, :, 0], gathered[:, :, 1]
+    x = fold_suffix(prod, state, rank) if suffix else fold_prefix(prod, state, rank)
+    halo = None
+    if want_halo:
+        world = gathered.shape[0]
+        halo = gathered[rank + 1, :, 2].clone() if rank + 1 < world else torch.ones_like(x)
+    return x.contiguous(), halo
 
 
 def _all_gather(x: torch.Tensor, group) -> torch.Tensor:
@@ -119,12 +136,11 @@ def time_sharded_forward(gates, tokens, group=None, ops=NativeOps):
     rows = gates.numel() // gates.shape[-1]
     if world == 1:
         return ops.forward(gates, tokens, None), None, None
-    prod, state = ops.reduce_forward(gates, tokens)
-    first_gate = gates.reshape(rows, -1)[:, 0].to(cdt)
-    payload = torch.stack([prod.to(cdt), state.to(cdt), first_gate], dim=0)           # (3, rows)
-    gathered = _all_gather(payload, group)                                              # (world, 3, rows)
-    carry_in = fold_prefix(gathered[:, 0], gathered[:, 1], rank).contiguous()
-    halo_gate_right = (gathered[rank + 1, 2] if rank + 1 < world else torch.ones_like(first_gate)).contiguous()
+    payload = torch.empty(rows, 3, dtype=cdt, device=gates.device)          # (P, S, first gate) per row
+    ops.reduce_forward(gates, tokens, payload)
+    payload[:, 2] = gates.reshape(rows, -1)[:, 0]
+    gathered = _all_gather(payload, group)                                   # (world, rows, 3)
+    carry_in, halo_gate_right = ops.fold(gathered, rank, False, True)
     states = ops.forward(gates, tokens, carry_in if rank > 0 else None)
     return states, carry_in, halo_gate_right
 
@@ -136,10 +152,11 @@ def time_sharded_backward(gates, states, grad_out, carry_in, halo_gate_right, gr
     if world == 1:
         return ops.backward(gates, states, grad_out, None, None, None)
     cdt = compute_dtype(gates.dtype)
-    prod, state = ops.reduce_backward(gates, grad_out, halo_gate_right)
-    payload = torch.stack([prod.to(cdt), state.to(cdt)], dim=0)
-    gathered = _all_gather(payload, group)                                              # (world, 2, rows)
-    g_in = fold_suffix(gathered[:, 0], gathered[:, 1], rank).contiguous()
+    rows = gates.numel() // gates.shape[-1]
+    payload = torch.empty(rows, 2, dtype=cdt, device=gates.device)          # (P', S') per row
+    ops.reduce_backward(gates, grad_out, halo_gate_right, payload)
+    gathered = _all_gather(payload, group)                                   # (world, rows, 2)
+    g_in, _ = ops.fold(gathered, rank, True, False)
     return ops.backward(gates, states, grad_out, g_in, halo_gate_right, carry_in)
 
 

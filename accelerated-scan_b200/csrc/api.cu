@@ -102,6 +102,35 @@ static int launch_dtype(int dtype, const StreamParams &p, const ascan_plan &pl, 
     }
 }
 
+// Folds the carries gathered from all ranks of a time-sharded scan into this rank's
+// incoming state: prefix = composition of ranks 0..rank-1 (forward), suffix = composition of
+// ranks world-1..rank+1 (backward).  gathered[j][r][0..stride): {P, S, (first gate)} of rank j.
+template <class V>
+__global__ void fold_carries_kernel(const V *gathered, int64_t rows, int world, int rank, int stride, int suffix,
+                                    V *state_out, V *halo_out) {
+    const int64_t r = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (r >= rows) return;
+    V x = vzero(V());
+    if (!suffix) {
+        for (int j = 0; j < rank; ++j) {
+            const V *c = gathered + (static_cast<int64_t>(j) * rows + r) * stride;
+            x = vfma(c[0], x, c[1]);
+        }
+    } else {
+        for (int j = world - 1; j > rank; --j) {
+            const V *c = gathered + (static_cast<int64_t>(j) * rows + r) * stride;
+            x = vfma(c[0], x, c[1]);
+        }
+    }
+    state_out[r] = x;
+    if (halo_out) {
+        // gate of the first step of the next rank, or one after the last rank
+        halo_out[r] = (rank + 1 < world && stride > 2)
+                          ? gathered[(static_cast<int64_t>(rank + 1) * rows + r) * stride + 2]
+                          : vone(V());
+    }
+}
+
 static int l2_hints_env() {
     const char *v = getenv("ASCAN_L2_HINTS");
     return (v && *v) ? atoi(v) : 0;
@@ -291,6 +320,27 @@ int ascan_plan_describe(int64_t rows, int64_t seqlen, int dtype, int kind, int f
         if (rc != ASCAN_OK) return rc;
     }
     return make_plan(in, plan);
+}
+
+int ascan_fold_carries(const void *gathered, int64_t rows, int world, int rank, int stride, int dtype, int suffix,
+                       void *state_out, void *halo_out, void *stream) {
+    if (rows < 0 || world < 1 || rank < 0 || rank >= world || stride < 2 || dtype_size(dtype) == 0)
+        return ASCAN_ERR_INVALID_ARG;
+    if (rows == 0) return ASCAN_OK;
+    if (!gathered || !state_out) return ASCAN_ERR_INVALID_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int threads = 256;
+    const unsigned blocks = static_cast<unsigned>((rows + threads - 1) / threads);
+    if (dtype == ASCAN_C64) {
+        fold_carries_kernel<float2><<<blocks, threads, 0, st>>>(static_cast<const float2 *>(gathered), rows, world, rank,
+                                                               stride, suffix, static_cast<float2 *>(state_out),
+                                                               static_cast<float2 *>(halo_out));
+    } else {
+        fold_carries_kernel<float><<<blocks, threads, 0, st>>>(static_cast<const float *>(gathered), rows, world, rank,
+                                                              stride, suffix, static_cast<float *>(state_out),
+                                                              static_cast<float *>(halo_out));
+    }
+    return cudaGetLastError() == cudaSuccess ? ASCAN_OK : ASCAN_ERR_LAUNCH;
 }
 
 int ascan_check(void *ws, void *stream) {

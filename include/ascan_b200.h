@@ -140,6 +140,19 @@ int ascan_reduce_backward(const void *gates, const void *grad_out,
                           void *ws, size_t ws_bytes, void *stream);
 
 /*
+ * Time-sharded scans: folds the carries gathered from all ranks into this rank's
+ * incoming state.  `gathered` holds world x rows x stride values of the compute
+ * type (float, or float2 for ASCAN_C64; other dtypes use float): {P, S, first gate}
+ * per rank and row (stride 3) or {P, S} (stride 2).  suffix == 0: state_out[r] =
+ * composition of ranks 0..rank-1 applied to zero (forward); suffix != 0: of ranks
+ * world-1..rank+1 (backward).  halo_out (nullable): first gate of rank+1, or one.
+ * No counterpart in the reference.
+ */
+int ascan_fold_carries(const void *gathered, int64_t rows, int world, int rank,
+                       int stride, int dtype, int suffix,
+                       void *state_out, void *halo_out, void *stream);
+
+/*
  * Scratch bytes a call of `kind` with these sizes can use: a control block
  * (status word, work ticket) plus one carry record per row, or per (row, segment)
  * when the look-back plan applies (fewer rows than warps).  With that much scratch

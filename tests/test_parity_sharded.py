@@ -32,19 +32,38 @@ def _emulate(gates, tokens, grad_out, world, dev):
     go = [sl(grad_out, r) for r in range(world)]
     rows = gates.shape[0] * gates.shape[1]
     cdt = sharded.compute_dtype(gates.dtype)
-    # forward: reduce -> fold -> seeded scan
-    carries = [ops.reduce_forward(g[r], x[r]) for r in range(world)]
-    P = torch.stack([c[0] for c in carries]).to(cdt)
-    S = torch.stack([c[1] for c in carries]).to(cdt)
-    first = torch.stack([g[r].reshape(rows, -1)[:, 0].to(cdt) for r in range(world)])
-    cin = [sharded.fold_prefix(P, S, r).contiguous() for r in range(world)]
+    # forward: reduce -> (gather) -> fold kernel -> seeded scan
+    fwd_payload = []
+    for r in range(world):
+        pay = torch.empty(rows, 3, dtype=cdt, device=dev)
+        ops.reduce_forward(g[r], x[r], pay)
+        pay[:, 2] = g[r].reshape(rows, -1)[:, 0]
+        fwd_payload.append(pay)
+    gathered = torch.stack(fwd_payload)                                   # what all_gather would return
+    P, S = gathered[:, :, 0], gathered[:, :, 1]
+    cin, halo = [], []
+    for r in range(world):
+        c, h = ops.fold(gathered, r, False, True)
+        # the fold kernel against the plain tensor arithmetic
+        c2, h2 = sharded.fold_with_tensor_ops(gathered, r, False, True)
+        torch.testing.assert_close(c, c2, rtol=1e-5, atol=1e-6)
+        torch.testing.assert_close(h, h2)
+        cin.append(c)
+        halo.append(h)
     states = [ops.forward(g[r], x[r], cin[r] if r > 0 else None) for r in range(world)]
-    # backward: reduce -> fold -> seeded fused backward
-    halo = [first[r + 1].contiguous() if r + 1 < world else torch.ones_like(first[0]) for r in range(world)]
-    bc = [ops.reduce_backward(g[r], go[r], halo[r]) for r in range(world)]
-    Pb = torch.stack([c[0] for c in bc]).to(cdt)
-    Sb = torch.stack([c[1] for c in bc]).to(cdt)
-    gin = [sharded.fold_suffix(Pb, Sb, r).contiguous() for r in range(world)]
+    # backward: reduce -> (gather) -> fold kernel -> seeded fused backward
+    bwd_payload = []
+    for r in range(world):
+        pay = torch.empty(rows, 2, dtype=cdt, device=dev)
+        ops.reduce_backward(g[r], go[r], halo[r], pay)
+        bwd_payload.append(pay)
+    gathered_b = torch.stack(bwd_payload)
+    gin = []
+    for r in range(world):
+        c, _ = ops.fold(gathered_b, r, True, False)
+        c2, _ = sharded.fold_with_tensor_ops(gathered_b, r, True, False)
+        torch.testing.assert_close(c, c2, rtol=1e-5, atol=1e-6)
+        gin.append(c)
     grads = [ops.backward(g[r], states[r], go[r], gin[r], halo[r], cin[r]) for r in range(world)]
     cat = lambda parts: torch.cat(parts, dim=-1)
     return cat(states), cat([d[0] for d in grads]), cat([d[1] for d in grads]), (P, S)

@@ -22,8 +22,10 @@ class LoopOps:
     def _rows(t):
         return t.reshape(-1, t.shape[-1])
 
+    fold = staticmethod(sharded.fold_with_tensor_ops)
+
     @staticmethod
-    def reduce_forward(gates, tokens):
+    def reduce_forward(gates, tokens, payload):
         a, b = LoopOps._rows(gates).to(torch.complex128), LoopOps._rows(tokens).to(torch.complex128)
         P = torch.ones(a.shape[0], dtype=a.dtype)
         S = torch.zeros(a.shape[0], dtype=a.dtype)
@@ -32,7 +34,8 @@ class LoopOps:
             P = P * a[:, t]
         cdt = sharded.compute_dtype(gates.dtype)
         conv = (lambda z: z.to(cdt)) if cdt.is_complex else (lambda z: z.real.to(cdt))
-        return conv(P), conv(S)
+        payload[:, 0] = conv(P)
+        payload[:, 1] = conv(S)
 
     @staticmethod
     def forward(gates, tokens, carry_in):
@@ -46,7 +49,7 @@ class LoopOps:
         return out.to(gates.dtype).reshape(gates.shape)
 
     @staticmethod
-    def reduce_backward(gates, grad_out, halo_gate_right):
+    def reduce_backward(gates, grad_out, halo_gate_right, payload):
         a, go = LoopOps._rows(gates).to(torch.complex128), LoopOps._rows(grad_out).to(torch.complex128)
         T = a.shape[1]
         nxt = torch.ones(a.shape[0], dtype=a.dtype) if halo_gate_right is None else halo_gate_right.to(torch.complex128)
@@ -58,7 +61,8 @@ class LoopOps:
             P = P * an
         cdt = sharded.compute_dtype(gates.dtype)
         conv = (lambda z: z.to(cdt)) if cdt.is_complex else (lambda z: z.real.to(cdt))
-        return conv(P), conv(g)
+        payload[:, 0] = conv(P)
+        payload[:, 1] = conv(g)
 
     @staticmethod
     def backward(gates, states, grad_out, carry_in, halo_gate_right, halo_state_left):
