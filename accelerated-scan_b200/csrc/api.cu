@@ -61,9 +61,12 @@ static int launch_one(const StreamParams &p, const ascan_plan &pl, cudaStream_t 
 // INTERIOR: items that group several rows have row boundaries inside their tiles.
 template <class TR, int NCH, int KIND, bool REVERSE, bool BULK>
 static int launch_interior(const StreamParams &p, const ascan_plan &pl, cudaStream_t stream) {
-    // look-back and team plans exist for the bulk loader and the two scan kinds only
+    // look-back plans exist for the bulk loader and the two scan kinds; team plans also for
+    // the carry-only kinds of the real dtypes
     if constexpr (BULK && (KIND == K_SCAN || KIND == K_BWD)) {
         if (pl.kernel == 1) return launch_one<TR, NCH, KIND, REVERSE, BULK, false, true>(p, pl, stream);
+    }
+    if constexpr (BULK && (KIND == K_SCAN || KIND == K_BWD || sizeof(typename TR::V) == 4)) {
         if (pl.kernel == 2) {
             auto kfn = team_kernel<TR, NCH, KIND, REVERSE>;
             int rc = ensure_smem(reinterpret_cast<const void *>(kfn), pl.smem_bytes);

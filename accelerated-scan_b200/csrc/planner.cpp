@@ -38,7 +38,8 @@ static int warp_smem(int nch, int stages, int kind, bool bulk) {
     const int tb = 32 * nch * 16;
     const int nstg = bulk ? stages : 1;
     const int outbufs = bulk ? 2 : 1;
-    const int stage = nin_of(kind) * tb + (kind == ASCAN_KIND_BACKWARD ? 128 : 0);   // + halo slot
+    // + halo slot (the stream kernel needs it for the fused backward only; sized for both)
+    const int stage = nin_of(kind) * tb + ((kind == ASCAN_KIND_BACKWARD || kind == ASCAN_KIND_REDUCE_BACKWARD) ? 128 : 0);
     return nstg * stage + outbufs * nout_of(kind) * tb + 128;
 }
 
@@ -104,7 +105,8 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     // item, so that all warps work although only rows/G... teams can be busy at once.  G is
     // the smallest divisor of the warps per CTA with (warps / G) <= rows.
     int team = 1;
-    if (!lookback && can_split && bulk && scan_kind && in.allow_team && in.rows > 0 && in.rows < max_warps &&
+    const bool team_kind = scan_kind || in.dtype != ASCAN_C64;     // carry-only kinds: real dtypes
+    if (!lookback && can_split && bulk && team_kind && in.allow_team && in.rows > 0 && in.rows < max_warps &&
         env_int("ASCAN_NO_TEAM", 0) == 0) {
         const int64_t want = (max_warps + in.rows - 1) / in.rows;
         for (int cand : {2, 3, 4, 6, 12}) {

@@ -99,7 +99,7 @@ __host__ __device__ constexpr int stream_nout(int kind) { return kind == K_SCAN 
 // 128-byte slot whose first 16 bytes receive the chunk of saved states just below the tile
 // (its last element is the state before the tile's first step).
 __host__ __device__ constexpr int stream_stage_bytes(int nch, int kind) {
-    return stream_nin(kind) * 32 * nch * 16 + (kind == K_BWD ? 128 : 0);
+    return stream_nin(kind) * 32 * nch * 16 + ((kind == K_BWD || kind == K_REDUCE_BWD) ? 128 : 0);
 }
 __host__ __device__ constexpr int stream_warp_smem(int nch, int stages, int kind, bool bulk) {
     const int tb = 32 * nch * 16;

@@ -30,7 +30,7 @@ constexpr int TEAM_SMEM_BYTES = 256;          // per team: 12 mailboxes, ticket 
 constexpr uint32_t MAIL_WAIT_POLLS = 1u << 24;
 
 __host__ __device__ constexpr int team_stage_bytes(int nch, int kind) {
-    return stream_nin(kind) * 32 * nch * 16 + (kind == K_BWD ? 128 : 0);
+    return stream_nin(kind) * 32 * nch * 16 + ((kind == K_BWD || kind == K_REDUCE_BWD) ? 128 : 0);
 }
 __host__ __device__ constexpr int team_warp_smem(int nch, int stages, int kind) {
     const int tb = 32 * nch * 16;
@@ -44,8 +44,11 @@ __global__ void __launch_bounds__(384, 1) team_kernel(const StreamParams p) {
     constexpr int K = NCH * EPC;
     constexpr int TE = 32 * K;
     constexpr int TB = 32 * NCH * 16;
-    constexpr bool BACK = (KIND == K_BWD);
+    constexpr bool BACK = (KIND == K_BWD || KIND == K_REDUCE_BWD);     // gates shifted by one step
+    constexpr bool FULL_BWD = (KIND == K_BWD);                          // ... and the d_gates epilogue
+    constexpr bool REDUCE = (KIND == K_REDUCE || KIND == K_REDUCE_BWD); // carry only (real dtypes)
     constexpr bool REV = REVERSE || BACK;
+    static_assert(!REDUCE || sizeof(typename TR::V) == 4, "team reductions carry two values in two 64-bit words");
     constexpr int NIN = stream_nin(KIND);
     constexpr int NOUT = stream_nout(KIND);
     constexpr int STAGE_BYTES = team_stage_bytes(NCH, KIND);
@@ -172,13 +175,13 @@ __global__ void __launch_bounds__(384, 1) team_kernel(const StreamParams p) {
         const int valid = tile_valid(d, t);
         const uint32_t bytes = static_cast<uint32_t>(valid) * TR::ESIZE;
         const int64_t goff = (d.e_begin + static_cast<int64_t>(t) * TE) * TR::ESIZE;
-        const bool below = BACK && goff > 0;
+        const bool below = FULL_BWD && goff > 0;
         const bool above = BACK && (d.pos0 + static_cast<int64_t>(t) * TE + valid < T);
         mbar_expect_tx(&bars[s], bytes * NIN + (below ? 16u : 0u) + (above ? 16u : 0u));
         unsigned char *dst = stage_base + s * STAGE_BYTES;
 #pragma unroll
         for (int k = 0; k < NIN; ++k) bulk_g2s(dst + k * TB, gbase[k] + goff, bytes, &bars[s]);
-        if (below) bulk_g2s(dst + NIN * TB, gbase[2] + goff - 16, 16, &bars[s]);
+        if (below) bulk_g2s(dst + NIN * TB, gbase[FULL_BWD ? 2 : 0] + goff - 16, 16, &bars[s]);
         if (above) bulk_g2s(dst + NIN * TB + 16, gbase[0] + goff + bytes, 16, &bars[s]);
     };
 
@@ -235,12 +238,20 @@ __global__ void __launch_bounds__(384, 1) team_kernel(const StreamParams p) {
 
     // what the first tile of an item needs from outside: the state published by the previous
     // segment of the row (fetched early, checked late, as in the stream kernel)
+    // (reduce kinds are real: slot 0 = state in w0, slot 1 = unit response in w1)
     auto fetch_state = [&](const ItemDesc &d) -> TaggedWords {
         TaggedWords wds;
         wds.w0 = 0;
         wds.w1 = 0;
-        if (d.valid && leader && split && d.s_log > 0)
-            wds = fetch_tagged(p.records + d.row0 * CARRY_RECORD_BYTES, 0, sizeof(V) > 4);
+        if (d.valid && leader && split && d.s_log > 0) {
+            const unsigned char *rec = p.records + d.row0 * CARRY_RECORD_BYTES;
+            if constexpr (REDUCE) {
+                wds.w0 = ld_relaxed_u64(rec);
+                wds.w1 = ld_relaxed_u64(rec + 16);
+            } else {
+                wds = fetch_tagged(rec, 0, sizeof(V) > 4);
+            }
+        }
         return wds;
     };
     TaggedWords head = fetch_state(cur);
@@ -248,18 +259,29 @@ __global__ void __launch_bounds__(384, 1) team_kernel(const StreamParams p) {
     while (cur.valid && !failed) {
         // ---------------- item prologue (only the leader's first tile uses the incoming state)
         V item_x_in = vzero(V());
+        V item_x2_in = vone(V());          // reduce kinds: unit response entering the item
         if (leader) {
             if (split && cur.s_log > 0) {
                 const unsigned char *rec = p.records + cur.row0 * CARRY_RECORD_BYTES;
                 const uint32_t want = epoch | static_cast<uint32_t>(cur.s_log);
-                bool got = decode_tagged(head, want, item_x_in);
+                bool got;
+                if constexpr (REDUCE) {
+                    TaggedWords t0, t1;
+                    t0.w0 = head.w0; t0.w1 = 0; t1.w0 = head.w1; t1.w1 = 0;
+                    got = decode_tagged(t0, want, item_x_in);
+                    got = decode_tagged(t1, want, item_x2_in) && got;
+                } else {
+                    got = decode_tagged(head, want, item_x_in);
+                }
                 for (uint32_t poll = 0; !got && poll < CARRY_WAIT_POLLS; ++poll) {
                     __nanosleep(64);
                     got = read_tagged(rec, 0, want, item_x_in);
+                    if (REDUCE) got = read_tagged(rec, 1, want, item_x2_in) && got;
                 }
                 if (!got) {
                     status_bits |= STATUS_LOOKBACK_TIMEOUT;
                     item_x_in = vzero(V());
+                    item_x2_in = vzero(V());
                 }
             } else if (cin) {
                 item_x_in = cin[cur.row0];
@@ -267,7 +289,7 @@ __global__ void __launch_bounds__(384, 1) team_kernel(const StreamParams p) {
         }
         // gate of the step after the row (backward): the caller's halo, or one
         const V row_end_gate = (BACK && hgate) ? hgate[cur.row0] : vone(V());
-        V item_x_out = vzero(V());
+        V item_x_out = vzero(V()), item_x2_out = vzero(V());
         bool fetched_next = false;
         TaggedWords head_next = head;
 
@@ -278,7 +300,7 @@ __global__ void __launch_bounds__(384, 1) team_kernel(const StreamParams p) {
             const int64_t pos = cur.pos0 + toff;                 // position of the tile in its row
             const unsigned char *stg = stage_base + cs * STAGE_BYTES;
             V x_row_start = vzero(V());
-            if (BACK && pos == 0 && hstate) x_row_start = hstate[cur.row0];
+            if (FULL_BWD && pos == 0 && hstate) x_row_start = hstate[cur.row0];
             if (i + G >= cur.nt) {
                 // this warp's last tile of the item: look at the next item now
                 need_next();
@@ -302,16 +324,18 @@ __global__ void __launch_bounds__(384, 1) team_kernel(const StreamParams p) {
                 TR::unpack(*reinterpret_cast<const uint4 *>(stg + 0 * TB + (lane * NCH + c) * 16), &a[c * EPC]);
                 TR::unpack(*reinterpret_cast<const uint4 *>(stg + 1 * TB + (lane * NCH + c) * 16), &b[c * EPC]);
             }
-            V xp[BACK ? K : 1];
+            V xp[FULL_BWD ? K : 1];
             V x_below = vzero(V()), gate_above = row_end_gate;
             if (BACK) {
-#pragma unroll
-                for (int c = 0; c < NCH; ++c)
-                    TR::unpack(*reinterpret_cast<const uint4 *>(stg + 2 * TB + (lane * NCH + c) * 16), &xp[c * EPC]);
                 V hv[EPC];
-                if (pos != 0) {
-                    TR::unpack(*reinterpret_cast<const uint4 *>(stg + NIN * TB), hv);
-                    x_below = hv[EPC - 1];
+                if (FULL_BWD) {
+#pragma unroll
+                    for (int c = 0; c < NCH; ++c)
+                        TR::unpack(*reinterpret_cast<const uint4 *>(stg + 2 * TB + (lane * NCH + c) * 16), &xp[c * EPC]);
+                    if (pos != 0) {
+                        TR::unpack(*reinterpret_cast<const uint4 *>(stg + NIN * TB), hv);
+                        x_below = hv[EPC - 1];
+                    }
                 }
                 if (pos + nvalid < T) {
                     TR::unpack(*reinterpret_cast<const uint4 *>(stg + NIN * TB + 16), hv);
@@ -404,6 +428,7 @@ __global__ void __launch_bounds__(384, 1) team_kernel(const StreamParams p) {
             // (a single store, a single load: nothing to order); a complex value is written
             // first, fenced, and then announced by the sequence number.
             V x_in = item_x_in;
+            V x2_in = item_x2_in;
             if (i > 0) {
                 const int from = (g + G - 1) % G;
                 const uint32_t want = step_base + static_cast<uint32_t>(i);
@@ -431,17 +456,26 @@ __global__ void __launch_bounds__(384, 1) team_kernel(const StreamParams p) {
                 }
                 if constexpr (sizeof(V) == 4) {
                     x_in = __uint_as_float(static_cast<uint32_t>(word));
+                    if constexpr (REDUCE) {
+                        // the second word was stored before the first: it is there once the first is
+                        x2_in = __uint_as_float(static_cast<uint32_t>(mail_word[from * 2 + 1]));
+                    }
                 } else {
                     x_in.x = mail_val[from * 4 + 2];
                     x_in.y = mail_val[from * 4 + 3];
                 }
             }
             const V x_out = vfma(At, x_in, Bt);
+            const V x2_out = REDUCE ? vmul(At, x2_in) : vzero(V());
             if (i + 1 < cur.nt) {
                 // forward it at once: the next warp only waits for this hop
                 if (lane == 0) {
                     const uint32_t seq = step_base + static_cast<uint32_t>(i) + 1u;
                     if constexpr (sizeof(V) == 4) {
+                        if constexpr (REDUCE) {
+                            mail_word[g * 2 + 1] = (static_cast<unsigned long long>(seq) << 32) | __float_as_uint(x2_out);
+                            __threadfence_block();
+                        }
                         mail_word[g * 2] = (static_cast<unsigned long long>(seq) << 32) | __float_as_uint(x_out);
                     } else {
                         mail_val[g * 4 + 2] = x_out.x;
@@ -452,6 +486,11 @@ __global__ void __launch_bounds__(384, 1) team_kernel(const StreamParams p) {
                 }
             } else {
                 item_x_out = x_out;
+                item_x2_out = x2_out;
+            }
+            if constexpr (REDUCE) {
+                ++step_count;
+                continue;          // carries only: nothing to write for this tile
             }
 
             // ---- pass 2: the recurrence from the lane's incoming state
@@ -475,7 +514,7 @@ __global__ void __launch_bounds__(384, 1) team_kernel(const StreamParams p) {
                     b[j] = x;
                 }
             }
-            if (BACK) {
+            if (FULL_BWD) {
                 // d_gates[t] = conj(x[t-1]) * g[t]
                 V dn = shfl_up(xp[K - 1], 1);
                 if (lane == 0) dn = (pos != 0) ? x_below : x_row_start;
@@ -507,9 +546,18 @@ __global__ void __launch_bounds__(384, 1) team_kernel(const StreamParams p) {
         // ---------------- item epilogue
         if (!failed) {
             // the warp that owned the last tile holds the state leaving the segment
-            if (split && cur.s_log + 1 < p.segs_per_row && (cur.nt - 1) % G == g && lane == 0) {
-                unsigned char *rec = p.records + cur.row0 * CARRY_RECORD_BYTES;
-                publish_tagged(rec, 0, item_x_out, epoch | static_cast<uint32_t>(cur.s_log + 1));
+            if ((cur.nt - 1) % G == g && lane == 0) {
+                if (split && cur.s_log + 1 < p.segs_per_row) {
+                    unsigned char *rec = p.records + cur.row0 * CARRY_RECORD_BYTES;
+                    const uint32_t tag = epoch | static_cast<uint32_t>(cur.s_log + 1);
+                    publish_tagged(rec, 0, item_x_out, tag);
+                    if (REDUCE) publish_tagged(rec, 1, item_x2_out, tag);
+                } else if (REDUCE) {
+                    // the item closes its row: the running state is the row's carry
+                    V *cout = static_cast<V *>(p.carry_out);
+                    cout[2 * cur.row0] = item_x2_out;
+                    cout[2 * cur.row0 + 1] = item_x_out;
+                }
             }
             if (!fetched_next) {
                 need_next();

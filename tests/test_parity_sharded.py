@@ -95,6 +95,32 @@ def test_emulated_time_shards(cuda_device, world, seqlen, dtype):
     np.testing.assert_allclose(to_np(P[0]).astype(prod.dtype), prod, rtol=2e-4, atol=1e-30)
 
 
+@pytest.mark.parametrize("rows,seqlen", [(300, 24576), (1024, 6000), (2000, 4608)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_emulated_time_shards_many_rows(cuda_device, rows, seqlen, dtype):
+    """The same with row counts that take the team plan (carry-only kinds included) and the
+    chained stream plan."""
+    from accelerated_scan import _native
+
+    world = 2
+    code = _native.DTYPE_CODE[dtype]
+    expect = 2 if rows < 148 * 12 else 0
+    assert _native.plan(rows, seqlen // world, code, _native.KIND_REDUCE_FORWARD)["kernel"] == expect
+    assert _native.plan(rows, seqlen // world, code, _native.KIND_REDUCE_BACKWARD)["kernel"] == expect
+    shape = (1, rows, seqlen)
+    gates, tokens, grad_out = real_inputs(19, shape, law="near_one", dtype=dtype)
+    up = (lambda t: t.numpy()) if dtype != torch.bfloat16 else (lambda t: t.float().numpy())
+    want = scan_oracle.scan(up(gates), up(tokens))
+    states, d_gates, d_tokens, _ = _emulate(gates, tokens, grad_out, world, cuda_device)
+    tol = REL[dtype]
+    assert rel_err(to_np(states), want) <= tol
+    saved = to_np(states) if dtype == torch.bfloat16 else want
+    want_dg, want_dx = scan_oracle.scan_backward(up(gates), saved, up(grad_out))
+    assert rel_err(to_np(d_tokens), want_dx) <= tol
+    assert rel_err(to_np(d_gates), want_dg) <= tol
+    _native.check_status(cuda_device)
+
+
 @pytest.mark.parametrize("seqlen", [7, 100, 3000, 70000])
 def test_carry_in_is_initial_state(cuda_device, seqlen):
     """ascan_forward with carry_in continues a scan: scanning [first | second] equals
