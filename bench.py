@@ -48,6 +48,7 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--no-time-sharded", action="store_true")
+    ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--time-sharded-steps", type=int, default=5)
     return ap.parse_args()
 
@@ -73,23 +74,31 @@ def config_dict(args, n_gpus):
 
 # ------------------------------------------------------------------ CPU oracle leg
 
-def cpu_oracle_run(seqlen, rows, repeats=1):
-    """fwd + bwd of the CPU oracle on `rows` rows; returns seconds per pass."""
+def cpu_oracle_inputs(seqlen, rows):
     import numpy as np
-    from oracle import scan_oracle
 
     rng = np.random.default_rng(0)
     g = (0.999 + 0.001 * rng.random((1, rows, seqlen), dtype=np.float32))
     x = rng.random((1, rows, seqlen), dtype=np.float32)
     go = rng.standard_normal((1, rows, seqlen), dtype=np.float32)
-    best = None
-    for _ in range(repeats):
-        t0 = time.perf_counter()
-        out = scan_oracle.scan(g, x)
-        scan_oracle.scan_backward(g, out, go)
-        dt = time.perf_counter() - t0
-        best = dt if best is None else min(best, dt)
-    return best
+    return g, x, go
+
+
+def cpu_oracle_pass(inputs):
+    """One fwd + bwd of the CPU oracle; returns the seconds it took (inputs are made outside)."""
+    from oracle import scan_oracle
+
+    g, x, go = inputs
+    t0 = time.perf_counter()
+    out = scan_oracle.scan(g, x)
+    scan_oracle.scan_backward(g, out, go)
+    return time.perf_counter() - t0
+
+
+def cpu_oracle_run(seqlen, rows, repeats=1):
+    """fwd + bwd of the CPU oracle on `rows` rows; returns the best seconds per pass."""
+    inputs = cpu_oracle_inputs(seqlen, rows)
+    return min(cpu_oracle_pass(inputs) for _ in range(repeats))
 
 
 def cpu_baseline(args, esize):
@@ -125,12 +134,10 @@ def run_reference(args):
     budget = 120.0 / max(1, args.steps + args.warmup)
     rows = int(min(B * C, max(probe_rows, probe_rows * min(budget, 10.0) / max(t_probe, 1e-6))))
     rows = max(cores, rows // cores * cores)
+    inputs = cpu_oracle_inputs(args.seqlen, rows)
     for _ in range(args.warmup):
-        cpu_oracle_run(args.seqlen, rows)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        cpu_oracle_run(args.seqlen, rows)
-    dt = (time.perf_counter() - t0) / max(1, args.steps)
+        cpu_oracle_pass(inputs)
+    dt = sum(cpu_oracle_pass(inputs) for _ in range(args.steps)) / max(1, args.steps)
     gbs = 8 * esize * rows * args.seqlen / dt / 1e9
     line = {
         "impl": "reference", "metric": METRIC, "value": round(gbs, 4), "unit": UNIT, "n_gpus": args.gpus,
@@ -277,6 +284,11 @@ def run_b200(args):
     value = world * bytes_step / (ms_per_step * 1e-3) / 1e9
     _native.check_status(dev)
 
+    # ---- sequence-length sweep (8, 1536, L), L = 128 .. 65536, same dtype (rank 0 only)
+    sweep = None
+    if not args.no_sweep and args.seqlen == 65536 and rank == 0:
+        sweep = run_sweep(args, torch, _native, dev, dtype, esize, gates, tokens, grad_out, out, d_gates, d_tokens)
+
     # ---- second multi-GPU mode: one long sequence sharded along time (carry all_gather)
     time_sharded = None
     if not args.no_time_sharded and args.seqlen == 65536:
@@ -289,6 +301,8 @@ def run_b200(args):
     launches = 2 * K
     if time_sharded:
         launches += (args.time_sharded_steps + 3) * time_sharded["launches_per_step"]
+    if sweep:
+        launches += 10 * 2 * 8
     if not args.no_e2e:
         e2e, e2e_launches = run_e2e(args, torch, dist, warp, dev, world, dtype, esize)
         launches += e2e_launches
@@ -322,6 +336,7 @@ def run_b200(args):
         },
         "pct_of_nominal_8TBs": round(100 * value / world / 8000.0, 2),
         "time_sharded": time_sharded,
+        "sweep": sweep,
     }
     if not args.no_cpu_baseline and world == 1:
         cb, _, _ = cpu_baseline(args, esize)
@@ -334,6 +349,41 @@ def run_b200(args):
 # DRAM bytes per element of the backward kernel from the ncu capture summarised under
 # profiles/stream_kernel_bf16_8x1536x16384_full_set.md (dram__bytes_read.sum + dram__bytes_write.sum per element).
 TRAFFIC_BWD_BYTES_PER_ELEM = 9.80
+
+
+def run_sweep(args, torch, _native, dev, dtype, esize, gates, tokens, grad_out, out, d_gates, d_tokens):
+    """Forward and backward time for (8, 1536, L), L = 128 ... 65536 (the reference's benchmark
+    sweep, tests/bench.py:15), on prefixes of the benchmark's buffers.  Short sequences fit
+    in L2, so a 256 MB buffer is rewritten before every timed launch to flush it."""
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    rows = B * C
+    points = []
+    for L in [2 ** i for i in range(7, 17)]:
+        n = rows * L
+        view = lambda t: t.reshape(-1)[:n].view(B, C, L)
+        g, x, go, o, dg, dx = (view(t) for t in (gates, tokens, grad_out, out, d_gates, d_tokens))
+
+        def timed(fn, reps=7):
+            fn()
+            ts = []
+            for _ in range(reps):
+                flush.zero_()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                fn()
+                b.record()
+                torch.cuda.synchronize()
+                ts.append(a.elapsed_time(b))
+            ts.sort()
+            return ts[len(ts) // 2]
+
+        tf = timed(lambda: _native.forward(g, x, o))
+        tb = timed(lambda: _native.backward(g, o, go, dg, dx))
+        points.append({"L": L, "fwd_ms": round(tf, 5), "bwd_ms": round(tb, 5),
+                       "fwd_GBps": round(3 * esize * n / tf / 1e6, 1), "bwd_GBps": round(5 * esize * n / tb / 1e6, 1)})
+    del flush
+    return {"shape": f"({B},{C},L) {args.dtype}", "l2": "256 MB flush buffer rewritten before every timed launch",
+            "timing": "median of 7 single launches, CUDA events", "points": points}
 
 
 def run_time_sharded(args, torch, dist, dev, world, rank):
