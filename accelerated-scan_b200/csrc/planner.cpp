@@ -205,12 +205,18 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
         grid = in.sm_count;
         if (pl.rows_per_item != 1 || static_cast<int64_t>(wpc) * wsm + wpc / team * 256 > kMaxSmemPerCta) team = 1;
     }
+    // A problem of at most two items per warp gains nothing from tickets: deal statically and
+    // save the ticket and exit-counter round trips (they are a fifth of a 15 us kernel).
+    if (pl.dynamic && team == 1 && pl.segs_per_row == 1 && pl.items <= 2 * grid * wpc &&
+        env_int("ASCAN_NO_SMALL_STATIC", 0) == 0) {
+        pl.dynamic = 0;
+    }
     pl.team_size = team;
     pl.warps_per_cta = wpc;
     pl.grid = static_cast<int32_t>(grid);
     pl.smem_bytes = static_cast<uint64_t>(wpc) * wsm + (team > 1 ? static_cast<uint64_t>(wpc / team) * 256 : 0);
     pl.kernel = (lookback && pl.segs_per_row > 1) ? 1 : (team > 1 ? 2 : 0);
-    pl.workspace_bytes = !use_ws ? 0
+    pl.workspace_bytes = (!use_ws || !pl.dynamic) ? 0
                          : (pl.kernel == 1 ? static_cast<uint64_t>(kCtrlBytes) + static_cast<uint64_t>(in.rows) *
                                                  pl.segs_per_row * kLookbackRecordBytes
                                            : workspace_bytes(in.rows));
