@@ -136,7 +136,11 @@ __global__ void fold_carries_kernel(const V *gathered, int64_t rows, int world, 
 
 static int l2_hints_env() {
     const char *v = getenv("ASCAN_L2_HINTS");
-    return (v && *v) ? atoi(v) : 0;
+    int bits = (v && *v) ? (atoi(v) & 15) : 0;
+    // test hook: one carry hand-over is dropped so that a bounded device-side wait expires
+    const char *d = getenv("ASCAN_TEST_DROP_CARRY");
+    if (d && *d == '1') bits |= 256;
+    return bits;
 }
 
 static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

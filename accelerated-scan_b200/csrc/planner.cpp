@@ -164,6 +164,8 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
         if (fit < seg_tiles) seg_tiles = static_cast<int>(fit);
         int64_t rpi = (seg_tiles * te) / in.seqlen;
         if (rpi < 1) rpi = 1;
+        const int rpi_env = env_int("ASCAN_RPI", 0);                     // sweep/test override
+        if (rpi_env > 0) rpi = rpi_env;
         if (bulk) rpi = (rpi + align_rows - 1) / align_rows * align_rows;
         pl.rows_per_item = rpi;
         pl.row_groups = (in.rows + rpi - 1) / rpi;

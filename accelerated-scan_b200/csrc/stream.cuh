@@ -89,7 +89,8 @@ struct StreamParams {
     uint32_t *ctrl;          // control words, or null (static dealing, no status)
     unsigned char *records;  // per-row carry records (segs_per_row > 1)
     int32_t stages;          // shared-memory stages per warp (bulk loader)
-    int32_t l2_hints;        // bits 0-1: loads (0 none, 1 evict_first, 2 evict_last); bits 2-3: stores
+    int32_t l2_hints;        // bits 0-1: loads (0 none, 1 evict_first, 2 evict_last); bits 2-3: stores;
+                             // bit 8: test hook, drop one carry hand-over (see the item epilogue)
     int32_t team_size;       // warps per team (team kernel only)
 };
 
@@ -856,7 +857,10 @@ __global__ void __launch_bounds__(384, 1) stream_kernel(const StreamParams p) {
                 if (lane == 0) publish_tagged(rec, 2, x_carry, tag);
             }
         } else if (split && cur.s_log + 1 < p.segs_per_row) {
-            if (lane == 0) {
+            // (fault injection for the tests: bit 8 of l2_hints drops the hand-over of row 0's
+            // first segment, so exactly one reader runs into its bound and reports it)
+            const bool drop = (p.l2_hints & 256) && cur.row0 == 0 && cur.s_log == 0;
+            if (lane == 0 && !drop) {
                 unsigned char *rec = p.records + cur.row0 * CARRY_RECORD_BYTES;
                 const uint32_t tag = epoch | static_cast<uint32_t>(cur.s_log + 1);
                 publish_tagged(rec, 0, x_carry, tag);
