@@ -185,10 +185,14 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     // (the team kernel's backward stage has the same 128-byte halo slot, so the sizes agree)
     const int wsm = warp_smem(nch, pl.stages, in.kind, bulk);
     int wpc = (kMaxSmemPerCta - (team > 1 ? kMaxWarpsPerCta / team * 256 : 0)) / wsm;
-    if (wpc > kMaxWarpsPerCta) wpc = kMaxWarpsPerCta;
+    // the stream kernels are compiled for 16 warps per CTA (14 for the fused backward, which
+    // needs more registers); 14 measured best (more warps hide more of a tile's dependent
+    // latency, 15-16 leave too few registers and shared memory per warp)
+    const int wpc_cap = team > 1 ? kMaxWarpsPerCta : (in.kind == ASCAN_KIND_BACKWARD ? 14 : 16);
+    if (wpc > wpc_cap) wpc = wpc_cap;
     const int wpc_env = env_int("ASCAN_WPC", 0);
     if (wpc_env > 0 && wpc_env < wpc) wpc = wpc_env;
-    else if (wpc > 12) wpc = 12;
+    else if (wpc > 14) wpc = 14;
     if (wpc < 1) return ASCAN_ERR_UNSUPPORTED;
 
     // One persistent CTA per SM.  With fewer items than warps, spread the items over

@@ -25,6 +25,10 @@ import sys
 import threading
 import time
 
+# keep stdout to the one JSON line: NCCL prints its version banner there at VERSION level
+if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+    os.environ["NCCL_DEBUG"] = "WARN"
+
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(ROOT, "accelerated-scan_b200"))
 sys.path.insert(0, ROOT)
@@ -393,10 +397,6 @@ def run_time_sharded(args, torch, dist, dev, world, rank):
     from accelerated_scan import sharded
 
     Bt, Ct, Tt = 2, 512, 1048576
-    if not dist.is_initialized():
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ.setdefault("MASTER_PORT", "29577")
-        dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
     Tl = Tt // world
     gen = torch.Generator(device=dev).manual_seed(77 + rank)
     g = 0.999 + 0.001 * torch.rand(Bt, Ct, Tl, device=dev, generator=gen)
@@ -404,26 +404,35 @@ def run_time_sharded(args, torch, dist, dev, world, rank):
     go = torch.randn(Bt, Ct, Tl, device=dev, generator=gen)
 
     def step():
-        states, cin, halo = sharded.time_sharded_forward(g, x, None)
-        sharded.time_sharded_backward(g, states, go, cin, halo, None)
+        if world == 1:
+            # one rank: the sharded scan is the plain kernels (no process group needed)
+            states = sharded.NativeOps.forward(g, x, None)
+            sharded.NativeOps.backward(g, states, go, None, None, None)
+        else:
+            states, cin, halo = sharded.time_sharded_forward(g, x, None)
+            sharded.time_sharded_backward(g, states, go, cin, halo, None)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
 
     for _ in range(3):
         step()
-    torch.cuda.synchronize()
-    dist.barrier()
-    torch.cuda.synchronize()
+    barrier()
     K = args.time_sharded_steps
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
     for _ in range(K):
         step()
     b.record()
-    torch.cuda.synchronize()
-    dist.barrier()
+    barrier()
     ms = a.elapsed_time(b) / K
-    t = torch.tensor([ms], device=dev, dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
     n = Bt * Ct * Tt
     gbs = 8 * 4 * n / (ms * 1e-3) / 1e9
     # kernels per step and rank: scan + backward, plus the two carry reductions when sharded
