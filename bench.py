@@ -53,6 +53,7 @@ def parse_args():
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--no-time-sharded", action="store_true")
     ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--no-also", action="store_true")
     ap.add_argument("--time-sharded-steps", type=int, default=5)
     return ap.parse_args()
 
@@ -293,10 +294,18 @@ def run_b200(args):
     if not args.no_sweep and args.seqlen == 65536 and rank == 0:
         sweep = run_sweep(args, torch, _native, dev, dtype, esize, gates, tokens, grad_out, out, d_gates, d_tokens)
 
+    # ---- the other dtypes of the metric on this GPU: fp32 at the same shape, complex64 (4,1024,16384)
+    also = None
+    if not args.no_also and args.seqlen == 65536 and args.dtype == "bf16" and rank == 0:
+        del gates, tokens, grad_out, out, d_gates, d_tokens
+        torch.cuda.empty_cache()
+        also = run_also(torch, _native, dev)
+        gates = tokens = grad_out = out = d_gates = d_tokens = None
+
     # ---- second multi-GPU mode: one long sequence sharded along time (carry all_gather)
     time_sharded = None
     if not args.no_time_sharded and args.seqlen == 65536:
-        del gates, tokens, grad_out, out, d_gates, d_tokens
+        gates = tokens = grad_out = out = d_gates = d_tokens = None
         torch.cuda.empty_cache()
         time_sharded = run_time_sharded(args, torch, dist, dev, world, rank)
 
@@ -307,6 +316,8 @@ def run_b200(args):
         launches += (args.time_sharded_steps + 3) * time_sharded["launches_per_step"]
     if sweep:
         launches += 10 * 2 * 8
+    if also:
+        launches += 2 * 2 * 13
     if not args.no_e2e:
         e2e, e2e_launches = run_e2e(args, torch, dist, warp, dev, world, dtype, esize)
         launches += e2e_launches
@@ -341,6 +352,7 @@ def run_b200(args):
         "pct_of_nominal_8TBs": round(100 * value / world / 8000.0, 2),
         "time_sharded": time_sharded,
         "sweep": sweep,
+        "also": also,
     }
     if not args.no_cpu_baseline and world == 1:
         cb, _, _ = cpu_baseline(args, esize)
@@ -353,6 +365,54 @@ def run_b200(args):
 # DRAM bytes per element of the backward kernel from the ncu capture summarised under
 # profiles/stream_kernel_bf16_8x1536x16384_full_set.md (dram__bytes_read.sum + dram__bytes_write.sum per element).
 TRAFFIC_BWD_BYTES_PER_ELEM = 9.82
+
+
+def run_also(torch, _native, dev):
+    """fwd+bwd of the same kernels for fp32 (8,1536,65536) and complex64 (4,1024,16384), inputs
+    resident, every tensor larger than L2, 10 timed steps after 3 warm-up steps."""
+    import math
+
+    peak, _ = measured_peak()
+    results = []
+    for name, shape, dt in (("fp32 (8,1536,65536)", (B, C, 65536), torch.float32),
+                            ("complex64 (4,1024,16384)", (4, 1024, 16384), torch.complex64)):
+        gen = torch.Generator(device=dev).manual_seed(4321)
+        if dt == torch.complex64:
+            r = 0.9 + 0.099 * torch.rand(*shape, device=dev, generator=gen)
+            th = (2 * torch.rand(*shape, device=dev, generator=gen) - 1) * math.pi
+            g = torch.polar(r, th)
+            x = torch.complex(torch.randn(*shape, device=dev, generator=gen), torch.randn(*shape, device=dev, generator=gen))
+            go = torch.complex(torch.randn(*shape, device=dev, generator=gen), torch.randn(*shape, device=dev, generator=gen))
+            del r, th
+        else:
+            g = 0.999 + 0.001 * torch.rand(*shape, device=dev, generator=gen)
+            x = torch.rand(*shape, device=dev, generator=gen)
+            go = torch.randn(*shape, device=dev, generator=gen)
+        o, dg, dx = torch.empty_like(x), torch.empty_like(x), torch.empty_like(x)
+        for _ in range(3):
+            _native.forward(g, x, o)
+            _native.backward(g, o, go, dg, dx)
+        torch.cuda.synchronize()
+        K = 10
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+        for k in range(K):
+            ev[k][0].record()
+            _native.forward(g, x, o)
+            ev[k][1].record()
+            _native.backward(g, o, go, dg, dx)
+            ev[k][2].record()
+        torch.cuda.synchronize()
+        fwd = sum(e[0].elapsed_time(e[1]) for e in ev) / K
+        bwd = sum(e[1].elapsed_time(e[2]) for e in ev) / K
+        n, es = x.numel(), x.element_size()
+        both = 8 * es * n / ((fwd + bwd) * 1e-3) / 1e9
+        results.append({"workload": name, "fwd_ms": round(fwd, 5), "bwd_ms": round(bwd, 5),
+                        "fwd_GBps": round(3 * es * n / fwd / 1e6, 1), "bwd_GBps": round(5 * es * n / bwd / 1e6, 1),
+                        "value": round(both, 1), "unit": UNIT, "frac_of_measured_peak": round(both / peak, 4),
+                        "pct_of_nominal_8TBs": round(100 * both / 8000.0, 2)})
+        del g, x, go, o, dg, dx
+        torch.cuda.empty_cache()
+    return results
 
 
 def run_sweep(args, torch, _native, dev, dtype, esize, gates, tokens, grad_out, out, d_gates, d_tokens):
