@@ -25,9 +25,6 @@ import sys
 import threading
 import time
 
-# keep stdout to the one JSON line: NCCL prints its version banner there at VERSION level
-if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-    os.environ["NCCL_DEBUG"] = "WARN"
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(ROOT, "accelerated-scan_b200"))
@@ -228,7 +225,20 @@ def run_b200(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        # stdout carries exactly one JSON line: the NCCL version banner that appears with the
+        # first communicator is sent to stderr (file descriptor level, it is printed natively)
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=dev)
+            warm = torch.zeros(1, device=dev)
+            dist.all_reduce(warm)
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved_stdout, 1)
+            os.close(saved_stdout)
 
     dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float32
     esize = 2 if args.dtype == "bf16" else 4
