@@ -2,7 +2,7 @@
 
 Run where the reference checkout is present:
 
-    python tests/golden/make_golden.py [path/to/reference]
+    python tests/golden/make_golden.py path/to/reference
 
 It loads the reference's oracle module accelerated_scan/ref.py by file path
 (pure torch, runs on CPU), draws the seeded inputs the reference's own tests
@@ -100,7 +100,9 @@ def complex_case(scan, name, seed, shape, *, mode, loss):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py path/to/reference   (the checkout that holds accelerated_scan/ref.py)")
+    root = sys.argv[1]
     scan = load_ref(root)
     torch.set_num_threads(1)
     # configuration "fp32 forward, (1, 16, 1024), gates 0.999+0.001*U, tokens U, seed 0"
