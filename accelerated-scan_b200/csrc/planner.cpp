@@ -194,6 +194,8 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     if (wpc_env > 0 && wpc_env < wpc) wpc = wpc_env;
     else if (wpc > 14) wpc = 14;
     if (wpc < 1) return ASCAN_ERR_UNSUPPORTED;
+    // kernels for items that group rows keep more state per thread: compiled for 12 warps
+    if (pl.rows_per_item > 1 && wpc > kMaxWarpsPerCta) wpc = kMaxWarpsPerCta;
 
     // One persistent CTA per SM.  With fewer items than warps, spread the items over
     // all SMs before filling the warps of a CTA.

@@ -124,7 +124,7 @@ struct ItemDesc {
 };
 
 template <class TR, int NCH, int KIND, bool REVERSE, bool BULK, bool INTERIOR, bool LOOKBACK>
-__global__ void __launch_bounds__(KIND == K_BWD ? 448 : 512, 1) stream_kernel(const StreamParams p) {
+__global__ void __launch_bounds__(INTERIOR ? 384 : (KIND == K_BWD ? 448 : 512), 1) stream_kernel(const StreamParams p) {
     using V = typename TR::V;
     using Raw = typename TR::Raw;
     constexpr int EPC = TR::EPC;
@@ -508,19 +508,18 @@ __global__ void __launch_bounds__(KIND == K_BWD ? 448 : 512, 1) stream_kernel(co
             const bool tiny = T < K;            // several rows inside one lane: per-element arithmetic
             int js = -1, je = -1, jwrap = K;    // row start, row end, first element of the next row
             int64_t rowq = row_ts;              // row of the lane's first element
+            // Row starts and row ends as bit masks over the lane's elements: testing a constant
+            // bit keeps a[] and b[] in registers (an equality test `j == js` invites the compiler
+            // to turn the chain into one indexed store, which moves the arrays to local memory).
+            uint32_t smask = 0, emask = 0;
+            auto row_of = [&](int j) -> int64_t {
+                if (!tiny) return rowq + (j >= jwrap ? 1 : 0);
+                return row_ts + (static_cast<int>(ts_mod) + lane * K + j) / static_cast<int>(T);
+            };
             auto classify = [&](int j, bool &is_start, bool &is_end, int64_t &row) {
-                if (!tiny) {
-                    is_start = (j == js);
-                    is_end = (j == je);
-                    row = rowq + (j >= jwrap ? 1 : 0);
-                } else {
-                    const int pi = static_cast<int>(ts_mod) + lane * K + j, ti = static_cast<int>(T);
-                    const int qi = pi / ti;
-                    const int rem = pi - qi * ti;
-                    is_start = (rem == 0);
-                    is_end = (rem == ti - 1);
-                    row = row_ts + qi;
-                }
+                is_start = (smask >> j) & 1u;
+                is_end = (emask >> j) & 1u;
+                row = row_of(j);
             };
 
             if (!INTERIOR) {
@@ -566,6 +565,17 @@ __global__ void __launch_bounds__(KIND == K_BWD ? 448 : 512, 1) stream_kernel(co
                     jwrap = tr < K ? static_cast<int>(tr) : K;
                     js = (r == 0) ? 0 : (tr < K ? static_cast<int>(tr) : -1);
                     je = (tr <= K) ? static_cast<int>(tr - 1) : -1;
+                    if (js >= 0) smask = 1u << js;
+                    if (je >= 0) emask = 1u << je;
+                }
+                if (slow && tiny) {
+#pragma unroll
+                    for (int j = 0; j < K; ++j) {
+                        const int pi = static_cast<int>(ts_mod) + lane * K + j, ti = static_cast<int>(T);
+                        const int rem = pi - (pi / ti) * ti;
+                        smask |= (rem == 0 ? 1u : 0u) << j;
+                        emask |= (rem == ti - 1 ? 1u : 0u) << j;
+                    }
                 }
                 if (slow) {
 #pragma unroll
