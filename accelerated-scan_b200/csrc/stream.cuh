@@ -124,7 +124,7 @@ struct ItemDesc {
 };
 
 template <class TR, int NCH, int KIND, bool REVERSE, bool BULK, bool INTERIOR, bool LOOKBACK>
-__global__ void __launch_bounds__(INTERIOR ? 384 : (KIND == K_BWD ? 448 : 512), 1) stream_kernel(const StreamParams p) {
+__global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ? 448 : 512), 1) stream_kernel(const StreamParams p) {
     using V = typename TR::V;
     using Raw = typename TR::Raw;
     constexpr int EPC = TR::EPC;
