@@ -51,6 +51,8 @@ def parse_args():
     ap.add_argument("--no-time-sharded", action="store_true")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-also", action="store_true")
+    ap.add_argument("--e2e-slabs", type=int, default=16)
+    ap.add_argument("--e2e-streams", type=int, default=4)
     ap.add_argument("--time-sharded-steps", type=int, default=5)
     return ap.parse_args()
 
@@ -518,7 +520,7 @@ def run_e2e(args, torch, dist, warp, dev, world, dtype, esize):
     copies gates, tokens and grad_out host->device and out, d_gates, d_tokens back.
     Rows are independent, so the step is pipelined in row slabs over three streams."""
     T = args.seqlen
-    slabs = 8
+    slabs = args.e2e_slabs
     rows_slab = B * C // slabs
     shape = (1, rows_slab, T)
     pin = lambda: [torch.empty(shape, dtype=dtype).pin_memory() for _ in range(slabs)]
@@ -529,7 +531,7 @@ def run_e2e(args, torch, dist, warp, dev, world, dtype, esize):
         h_g[i].copy_((0.999 + 0.001 * torch.rand(shape, generator=gen)).to(dtype))
         h_x[i].copy_(torch.rand(shape, generator=gen).to(dtype))
         h_go[i].copy_(torch.randn(shape, generator=gen).to(dtype))
-    streams = [torch.cuda.Stream(device=dev) for _ in range(3)]
+    streams = [torch.cuda.Stream(device=dev) for _ in range(args.e2e_streams)]
     bufs = [[torch.empty(shape, dtype=dtype, device=dev) for _ in range(3)] for _ in streams]
     launches = 0
 
@@ -571,7 +573,7 @@ def run_e2e(args, torch, dist, warp, dev, world, dtype, esize):
     gbs = world * 8 * esize * n_elems / dt / 1e9
     return ({"value": round(gbs, 2), "unit": UNIT, "h2d_bytes_per_step": 3 * esize * n_elems,
              "d2h_bytes_per_step": 3 * esize * n_elems, "ms_per_step": round(dt * 1e3, 3), "steps": args.e2e_steps,
-             "api": "accelerated_scan.warp.scan + autograd backward, 8 row slabs pipelined on 3 streams"}, launches)
+             "api": f"accelerated_scan.warp.scan + autograd backward, {slabs} row slabs pipelined on {len(streams)} streams"}, launches)
 
 
 def main():
