@@ -187,3 +187,29 @@ def test_deterministic(cuda_device):
 def test_status_word_clean(cuda_device):
     from accelerated_scan import _native
     _native.check_status(cuda_device)
+
+
+def test_more_than_2_31_elements(cuda_device):
+    """64-bit offsets: a matrix of 2.2e9 elements (the reference indexes with 32-bit ints,
+    warp.cuh:58-59).  Rows are independent, so a few rows spread over the matrix are checked
+    against the oracle; the inputs are drawn on the GPU and the checked rows copied back."""
+    warp = _warp()
+    rows, T = 2112, 1 << 20
+    assert rows * T > 2 ** 31
+    free, _ = torch.cuda.mem_get_info(cuda_device)
+    if free < 40 * 2 ** 30:
+        pytest.skip("needs about 27 GB of device memory")
+    gen = torch.Generator(device=cuda_device).manual_seed(5)
+    gates = (0.999 + 0.001 * torch.rand(1, rows, T, device=cuda_device, generator=gen)).to(torch.bfloat16)
+    tokens = torch.rand(1, rows, T, device=cuda_device, generator=gen).to(torch.bfloat16)
+    grad_out = torch.randn(1, rows, T, device=cuda_device, generator=gen).to(torch.bfloat16)
+    out = warp.scan_forward(gates, tokens)
+    d_gates, d_tokens = torch.empty_like(gates), torch.empty_like(gates)
+    warp.warpscan_backward(gates, out, grad_out, d_gates, d_tokens)
+    pick = [0, 1, rows // 2, rows - 2, rows - 1]
+    sel = lambda t: t[:, pick].float().cpu().numpy()
+    want = scan_oracle.scan(sel(gates), sel(tokens))
+    assert rel_err(sel(out), want) <= BF16_REL
+    want_dg, want_dx = scan_oracle.scan_backward(sel(gates), sel(out), sel(grad_out))
+    assert rel_err(sel(d_tokens), want_dx) <= BF16_REL
+    assert rel_err(sel(d_gates), want_dg) <= BF16_REL
