@@ -67,6 +67,8 @@ def _load():
     lib.ascan_plan_describe.argtypes = [i64, i64, i32, i32, i32, i32, ctypes.POINTER(Plan)]
     lib.ascan_check.restype = i32
     lib.ascan_check.argtypes = [vp, vp]
+    lib.ascan_forward_complex_real_tokens.restype = i32
+    lib.ascan_forward_complex_real_tokens.argtypes = [vp, vp, vp, i64, i64, i32, vp, sz, vp]
     lib.ascan_fold_carries.restype = i32
     lib.ascan_fold_carries.argtypes = [vp, i64, i32, i32, i32, i32, i32, vp, vp, vp]
     lib.ascan_forward_no_alloc.restype = i32
@@ -79,7 +81,7 @@ lib = _load()
 EXPORTS = (
     "ascan_version", "ascan_strerror", "ascan_forward", "ascan_backward", "ascan_reduce_forward",
     "ascan_reduce_backward", "ascan_workspace_bytes", "ascan_plan_describe", "ascan_check",
-    "ascan_forward_no_alloc", "ascan_fold_carries",
+    "ascan_forward_no_alloc", "ascan_fold_carries", "ascan_forward_complex_real_tokens",
 )
 
 
@@ -152,6 +154,26 @@ def forward(gates, tokens, out, reverse=False, carry_in=None):
         rc = lib.ascan_forward(_ptr(gates), _ptr(tokens), _ptr(out), rows, T, dtype_code(gates), int(bool(reverse)),
                                _ptr(carry_in), _ptr(ws), ws.numel(), _stream(gates))
     check(rc, "ascan_forward")
+
+
+UNSUPPORTED = 2
+
+
+def forward_complex_real_tokens(gates, tokens_real, out, reverse=False) -> bool:
+    """complex64 gates, float32 tokens (imaginary part zero), complex64 out.  Returns False
+    when the library has no fused kernel for this shape or alignment (the caller then promotes
+    the tokens to complex and calls `forward`)."""
+    _require_cuda(gates, tokens_real, out)
+    rows = gates.numel() // gates.shape[-1] if gates.shape[-1] else 0
+    T = gates.shape[-1]
+    with torch.cuda.device(gates.device):
+        ws = workspace(gates.device, rows, T, C64, KIND_FORWARD)
+        rc = lib.ascan_forward_complex_real_tokens(_ptr(gates), _ptr(tokens_real), _ptr(out), rows, T,
+                                                   int(bool(reverse)), _ptr(ws), ws.numel(), _stream(gates))
+    if rc == UNSUPPORTED:
+        return False
+    check(rc, "ascan_forward_complex_real_tokens")
+    return True
 
 
 def backward(gates, states, grad_out, d_gates, d_tokens, carry_in=None, halo_gate_right=None, halo_state_left=None):

@@ -55,14 +55,20 @@ class Scan(torch.autograd.Function):
         assert forget.is_contiguous()
         assert inputs.is_contiguous()
 
-        if real_inputs:
-            inputs = torch.complex(inputs.float(), torch.zeros_like(inputs, dtype=torch.float32))
-        elif inputs.dtype != torch.complex64:
+        if not real_inputs and inputs.dtype != torch.complex64:
             raise RuntimeError("inputs must be complex64 or real")
 
-        states = torch.empty_like(inputs)
-        if states.numel():
-            _native.forward(forget, inputs, states)
+        states = torch.empty_like(forget)
+        fused = False
+        if real_inputs and states.numel() and inputs.dtype == torch.float32:
+            # real tokens go straight into the kernel (no complex copy of the inputs) ...
+            fused = _native.forward_complex_real_tokens(forget, inputs, states)
+        if not fused:
+            # ... unless the shape has no fused kernel: promote as the reference does (complex.py:168-169)
+            if real_inputs:
+                inputs = torch.complex(inputs.float(), torch.zeros_like(inputs, dtype=torch.float32))
+            if states.numel():
+                _native.forward(forget, inputs, states)
         ctx.save_for_backward(forget, states)
         ctx.real_inputs = real_inputs
         return states

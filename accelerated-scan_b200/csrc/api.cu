@@ -329,6 +329,51 @@ int ascan_plan_describe(int64_t rows, int64_t seqlen, int dtype, int kind, int f
     return make_plan(in, plan);
 }
 
+int ascan_forward_complex_real_tokens(const void *gates, const void *tokens_real, void *out, int64_t rows,
+                                       int64_t seqlen, int reverse, void *ws, size_t ws_bytes, void *stream) {
+    if (rows < 0 || seqlen < 1) return ASCAN_ERR_INVALID_ARG;
+    if (rows == 0) return ASCAN_OK;
+    if (!gates || !tokens_real || !out) return ASCAN_ERR_INVALID_ARG;
+    // The fused form exists for the bulk loader with one row (or one segment) per item in the
+    // chained stream plan; the real rows must start 16-byte aligned as well (seqlen % 4 == 0).
+    const bool al = aligned16(gates) && aligned16(tokens_real) && aligned16(out);
+    if (!al || seqlen % 4 != 0) return ASCAN_ERR_UNSUPPORTED;
+    PlanInput in;
+    in.reverse = reverse != 0;
+    in.rows = rows;
+    in.seqlen = seqlen;
+    in.dtype = ASCAN_C64;
+    in.kind = ASCAN_KIND_FORWARD;
+    in.aligned = true;
+    in.workspace = ws && (reinterpret_cast<uintptr_t>(ws) & 255u) == 0;
+    in.allow_lookback = false;
+    in.allow_team = false;
+    int rc = cached_sm_count(&in.sm_count);
+    if (rc != ASCAN_OK) return rc;
+    ascan_plan pl;
+    rc = make_plan(in, &pl);
+    if (rc == ASCAN_OK && pl.workspace_bytes > ws_bytes && in.workspace) {
+        in.workspace = false;
+        rc = make_plan(in, &pl);
+    }
+    if (rc != ASCAN_OK) return rc;
+    if (pl.loader != 0 || pl.rows_per_item != 1 || pl.kernel != 0) return ASCAN_ERR_UNSUPPORTED;
+    StreamParams p = {};
+    p.in0 = gates;
+    p.in1 = tokens_real;
+    p.out0 = out;
+    fill_common(p, pl, rows, seqlen, ws);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    auto launch = [&](auto kfn) -> int {
+        int r2 = ensure_smem(reinterpret_cast<const void *>(kfn), pl.smem_bytes);
+        if (r2 != ASCAN_OK) return r2;
+        kfn<<<pl.grid, pl.warps_per_cta * 32, pl.smem_bytes, st>>>(p);
+        return cudaGetLastError() == cudaSuccess ? ASCAN_OK : ASCAN_ERR_LAUNCH;
+    };
+    return reverse ? launch(stream_kernel<TraitsC64, 3, K_SCAN, true, true, false, false, true>)
+                   : launch(stream_kernel<TraitsC64, 3, K_SCAN, false, true, false, false, true>);
+}
+
 int ascan_fold_carries(const void *gathered, int64_t rows, int world, int rank, int stride, int dtype, int suffix,
                        void *state_out, void *halo_out, void *stream) {
     if (rows < 0 || world < 1 || rank < 0 || rank >= world || stride < 2 || dtype_size(dtype) == 0)

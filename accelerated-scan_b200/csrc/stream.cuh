@@ -123,7 +123,10 @@ struct ItemDesc {
     bool valid;
 };
 
-template <class TR, int NCH, int KIND, bool REVERSE, bool BULK, bool INTERIOR, bool LOOKBACK>
+// TOKR (complex forward only): the token stream is real fp32 (half the bytes per tile); the
+// imaginary part is taken as zero, which fuses the reference's promotion
+// `torch.complex(inputs, zeros)` (complex.py:168-169) into the scan.
+template <class TR, int NCH, int KIND, bool REVERSE, bool BULK, bool INTERIOR, bool LOOKBACK, bool TOKR = false>
 __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ? 448 : 512), 1) stream_kernel(const StreamParams p) {
     using V = typename TR::V;
     using Raw = typename TR::Raw;
@@ -246,8 +249,15 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
         // fused backward: also the 16 bytes of saved states just below the tile (tiles start
         // 16-byte aligned, so that chunk is aligned too); skipped at the start of the matrix
         const bool halo = (KIND == K_BWD) && goff > 0;
-        mbar_expect_tx(&bars[s], bytes * NIN + (halo ? 16u : 0u));
         unsigned char *dst = stage_base + s * STAGE_BYTES;
+        if constexpr (TOKR) {
+            // complex gates, real tokens: the token tile has half the bytes
+            mbar_expect_tx(&bars[s], bytes + bytes / 2);
+            bulk_g2s(dst, gbase[0] + goff, bytes, &bars[s]);
+            bulk_g2s(dst + TB, gbase[1] + goff / 2, bytes / 2, &bars[s]);
+            return;
+        }
+        mbar_expect_tx(&bars[s], bytes * NIN + (halo ? 16u : 0u));
 #pragma unroll
         for (int k = 0; k < NIN; ++k) {
             if (ld_hint)
@@ -459,9 +469,16 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
 #pragma unroll
             for (int c = 0; c < NCH; ++c) {
                 const uint4 qa = *reinterpret_cast<const uint4 *>(stg + 0 * TB + (lane * NCH + c) * 16);
-                const uint4 qb = *reinterpret_cast<const uint4 *>(stg + 1 * TB + (lane * NCH + c) * 16);
                 TR::unpack(qa, &a[c * EPC]);
-                TR::unpack(qb, &b[c * EPC]);
+                if constexpr (TOKR) {
+                    // K real tokens of 4 bytes per lane, read as 8-byte pairs; imaginary part zero
+                    const float2 tk = *reinterpret_cast<const float2 *>(stg + TB + lane * (K * 4) + c * 8);
+                    b[2 * c] = make_float2(tk.x, 0.0f);
+                    b[2 * c + 1] = make_float2(tk.y, 0.0f);
+                } else {
+                    const uint4 qb = *reinterpret_cast<const uint4 *>(stg + 1 * TB + (lane * NCH + c) * 16);
+                    TR::unpack(qb, &b[c * EPC]);
+                }
             }
             V xp[KIND == K_BWD ? K : 1];
             V x_below = vzero(V());   // state just below the tile, from the halo chunk

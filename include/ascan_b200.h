@@ -140,6 +140,19 @@ int ascan_reduce_backward(const void *gates, const void *grad_out,
                           void *ws, size_t ws_bytes, void *stream);
 
 /*
+ * Complex forward scan with REAL tokens: gates and out are complex64, tokens_real
+ * is fp32 and its imaginary part is taken as zero.  Fuses the promotion
+ * torch.complex(inputs, zeros) of the reference's complex Scan.forward
+ * (complex.py:162,168-169), which otherwise writes and re-reads a whole complex
+ * tensor.  Needs 16-byte aligned pointers and seqlen % 4 == 0, and shapes the
+ * stream plan handles with one row or segment per item; otherwise it returns
+ * ASCAN_ERR_UNSUPPORTED and the caller promotes the tokens itself.
+ */
+int ascan_forward_complex_real_tokens(const void *gates, const void *tokens_real, void *out,
+                                      int64_t rows, int64_t seqlen, int reverse,
+                                      void *ws, size_t ws_bytes, void *stream);
+
+/*
  * Time-sharded scans: folds the carries gathered from all ranks into this rank's
  * incoming state.  `gathered` holds world x rows x stride values of the compute
  * type (float, or float2 for ASCAN_C64; other dtypes use float): {P, S, first gate}

@@ -144,3 +144,25 @@ def test_triton_style_launchers(cuda_device):
     want_df, want_dx = scan_oracle.scan_backward(forget.numpy(), want, grad_out.numpy())
     assert rel_err(to_np(d_x), want_dx) <= REL
     assert rel_err(to_np(d_f), want_df) <= REL
+
+
+@pytest.mark.parametrize("rows,seqlen,fused", [(2000, 4096, True), (8, 40000, True), (300, 20000, True),
+                                               (4, 16323, False), (6, 1002, False)])
+def test_real_tokens_fused_into_the_kernel(cuda_device, rows, seqlen, fused):
+    """Real inputs go into the complex kernel as fp32 (no complex copy) whenever the rows are
+    16-byte aligned in both streams (seqlen % 4 == 0); other shapes report "unsupported" and
+    complex.scan promotes the tokens as the reference does.  Both give the same answer."""
+    from accelerated_scan import _native
+
+    cplx = _cplx()
+    forget, inputs, _ = complex_inputs(21, (1, rows, seqlen), law="cfg4", real_tokens=True)
+    want = scan_oracle.scan(forget.numpy(), inputs.numpy())
+    f, x = forget.to(cuda_device), inputs.to(cuda_device)
+    out = torch.empty_like(f)
+    assert _native.forward_complex_real_tokens(f, x, out) == fused
+    if fused:
+        assert rel_err(to_np(out), want) <= REL
+        rev = torch.empty_like(f)
+        assert _native.forward_complex_real_tokens(f, x, rev, reverse=True)
+        assert rel_err(to_np(rev), scan_oracle.scan(forget.numpy(), inputs.numpy(), reverse=True)) <= REL
+    assert rel_err(to_np(cplx.scan(f, x)), want) <= REL
