@@ -90,6 +90,12 @@ template <class TR, int KIND, bool REVERSE>
 static int launch_nch(const StreamParams &p, const ascan_plan &pl, cudaStream_t stream) {
     switch (pl.chunks_per_lane) {
         case 3: return launch_loader<TR, 3, KIND, REVERSE>(p, pl, stream);
+        case 2:
+            // two chunks per lane: planned for the fused backward of the 16-bit dtypes only
+            if constexpr (KIND == K_BWD && TR::EPC == 8) {
+                if (pl.kernel == 0) return launch_loader<TR, 2, KIND, REVERSE>(p, pl, stream);
+            }
+            return ASCAN_ERR_UNSUPPORTED;
         default: return ASCAN_ERR_UNSUPPORTED;
     }
 }

@@ -50,17 +50,21 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     if (in.rows < 0 || in.seqlen < 1 || in.sm_count < 1) return ASCAN_ERR_INVALID_ARG;
 
     ascan_plan pl = {};
-    // (2 and 4 were measured: 4 loses 15 % to bank conflicts everywhere, 2 gains 2 % in the bf16
-    // backward and loses 14 % in the forward)
-    const int nch = 3;
+    // 16-byte chunks per lane.  3 everywhere (odd: the 16-byte shared accesses of a quarter-warp
+    // hit distinct bank groups; 4 loses 15 % to conflicts), except the fused backward of the
+    // 16-bit dtypes in the plain stream plan: 24 elements x 3 streams per lane leave too few
+    // registers, and 2 chunks (16 elements) measured 2-6 % faster there despite 2-way conflicts.
+    const int64_t stream_warps = static_cast<int64_t>(in.sm_count) * kMaxWarpsPerCta;
+    const int nch = (in.kind == ASCAN_KIND_BACKWARD && esize == 2 && in.rows >= stream_warps &&
+                     env_int("ASCAN_NCH3_ONLY", 0) == 0)
+                        ? 2
+                        : 3;
     const int64_t te = 32 * nch * (16 / esize);
     // tickets and split-row item numbers are 32-bit
     const bool use_ws = in.workspace && env_int("ASCAN_STATIC", 0) == 0 && in.rows < (1ll << 30) &&
                         in.rows * ((in.seqlen + te - 1) / te) < (1ll << 31);
     pl.dynamic = use_ws ? 1 : 0;
 
-    // 16-byte chunks per lane: odd, so that the 16-byte shared accesses of a
-    // quarter-warp hit distinct bank groups.
     pl.chunks_per_lane = nch;
     pl.tile_elems = static_cast<int32_t>(te);
 
