@@ -376,7 +376,7 @@ def run_b200(args):
 
 # DRAM bytes per element of the backward kernel from the ncu capture summarised under
 # profiles/stream_kernel_bf16_8x1536x16384_full_set.md (dram__bytes_read.sum + dram__bytes_write.sum per element).
-TRAFFIC_BWD_BYTES_PER_ELEM = 9.82
+TRAFFIC_BWD_BYTES_PER_ELEM = 9.86
 
 
 def run_also(torch, _native, dev):
