@@ -8,6 +8,10 @@ the autograd surface for it.  Works for the real dtypes and complex64.
 
     out = scan(gates, tokens, initial_state)          # (B, C, T)
     next_state = out[..., -1]                          # differentiable: it is a slice of `out`
+
+When only the last state is wanted (prefill of a streaming model), `final_state` runs the
+carry-only kernel (`ascan_reduce_forward`): it reads the two inputs and writes two values
+per row, a third less traffic than the scan and no (B, C, T) output tensor.
 """
 import torch
 
@@ -66,3 +70,31 @@ def scan(gates, tokens, initial_state=None):
         from . import warp as _warp
         return _warp.scan(gates, tokens)
     return ScanWithState.apply(gates, tokens, initial_state)
+
+
+def final_state(gates, tokens, initial_state=None):
+    """x[T-1] of the scan without materialising x: (B, C) in the accumulation dtype
+    (float32 for the real dtypes, complex64 for complex64).  Not differentiable (the
+    states that the gradient of the gates needs are never written); use `scan` to train.
+
+    The kernel returns, per row, the product P of the gates and the last state S from a
+    zero start; the state from `initial_state` is P * initial_state + S.
+    """
+    B, C, T = gates.shape
+    assert tokens.shape == (B, C, T)
+    assert gates.is_contiguous()
+    assert tokens.is_contiguous()
+    if gates.dtype != tokens.dtype:
+        raise RuntimeError("gates and tokens must have the same dtype")
+    cdt = compute_dtype(gates.dtype)
+    if initial_state is not None:
+        assert initial_state.shape == (B, C)
+    if T == 0:
+        return torch.zeros(B, C, dtype=cdt, device=gates.device) if initial_state is None else initial_state.to(cdt)
+    with torch.no_grad():
+        carry = torch.empty(B * C, 2, dtype=cdt, device=gates.device)
+        _native.reduce_forward(gates, tokens, carry)
+        prod, state = carry[:, 0].reshape(B, C), carry[:, 1].reshape(B, C)
+        if initial_state is not None:
+            state = prod * initial_state.to(cdt) + state
+    return state

@@ -71,3 +71,26 @@ def test_none_state_is_the_drop_in_scan(cuda_device):
     gates, tokens, _ = real_inputs(1, (1, 4, 512), grad=False)
     g, x = gates.to(cuda_device), tokens.to(cuda_device)
     assert torch.equal(stateful.scan(g, x), warp.scan(g, x))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.complex64])
+@pytest.mark.parametrize("shape", [(2, 3, 1), (1, 5, 777), (2, 160, 3000), (1, 2, 300000)])
+@pytest.mark.parametrize("with_state", [False, True])
+def test_final_state_is_the_last_column_of_the_scan(cuda_device, dtype, shape, with_state):
+    from accelerated_scan import stateful
+
+    if dtype == torch.complex64:
+        gates, tokens, _ = complex_inputs(9, shape, law="cfg4")
+        x0 = torch.complex(torch.randn(shape[:2]), torch.randn(shape[:2])) if with_state else None
+    else:
+        gates, tokens, _ = real_inputs(9, shape, law="near_one" if shape[-1] > 2000 else "uniform", dtype=dtype, grad=False)
+        x0 = torch.randn(shape[:2]) if with_state else None
+    g, x = gates.to(cuda_device), tokens.to(cuda_device)
+    s0 = x0.to(cuda_device) if with_state else None
+    # the scan writes its states in the storage dtype; the carry-only kernel keeps fp32
+    want = stateful.scan(g, x, s0)[..., -1]
+    got = stateful.final_state(g, x, s0)
+    assert got.shape == shape[:2]
+    assert got.dtype == (torch.complex64 if dtype == torch.complex64 else torch.float32)
+    tol = 2.0 ** -8 if dtype == torch.bfloat16 else 1e-5
+    assert rel_err(to_np(got), to_np(want.to(got.dtype))) <= tol
