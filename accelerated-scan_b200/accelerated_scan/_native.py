@@ -71,6 +71,10 @@ def _load():
     lib.ascan_forward_complex_real_tokens.argtypes = [vp, vp, vp, i64, i64, i32, vp, sz, vp]
     lib.ascan_fold_carries.restype = i32
     lib.ascan_fold_carries.argtypes = [vp, i64, i32, i32, i32, i32, i32, vp, vp, vp]
+    lib.ascan_forward_sigmoid_gates.restype = i32
+    lib.ascan_forward_sigmoid_gates.argtypes = [vp, vp, vp, i64, i64, i32, vp, sz, vp]
+    lib.ascan_backward_sigmoid_gates.restype = i32
+    lib.ascan_backward_sigmoid_gates.argtypes = [vp, vp, vp, vp, vp, i64, i64, i32, vp, sz, vp]
     lib.ascan_forward_no_alloc.restype = i32
     lib.ascan_forward_no_alloc.argtypes = [vp, vp, vp, i64, i64, i32, i32, vp]
     return lib
@@ -82,6 +86,7 @@ EXPORTS = (
     "ascan_version", "ascan_strerror", "ascan_forward", "ascan_backward", "ascan_reduce_forward",
     "ascan_reduce_backward", "ascan_workspace_bytes", "ascan_plan_describe", "ascan_check",
     "ascan_forward_no_alloc", "ascan_fold_carries", "ascan_forward_complex_real_tokens",
+    "ascan_forward_sigmoid_gates", "ascan_backward_sigmoid_gates",
 )
 
 
@@ -173,6 +178,38 @@ def forward_complex_real_tokens(gates, tokens_real, out, reverse=False) -> bool:
     if rc == UNSUPPORTED:
         return False
     check(rc, "ascan_forward_complex_real_tokens")
+    return True
+
+
+def forward_sigmoid_gates(gate_logits, tokens, out) -> bool:
+    """out[t] = sigmoid(gate_logits[t]) * out[t-1] + tokens[t].  Returns False when the library
+    has no fused kernel for this shape or alignment (the caller applies the sigmoid itself)."""
+    _require_cuda(gate_logits, tokens, out)
+    rows = gate_logits.numel() // gate_logits.shape[-1] if gate_logits.shape[-1] else 0
+    T = gate_logits.shape[-1]
+    with torch.cuda.device(gate_logits.device):
+        ws = workspace(gate_logits.device, rows, T, dtype_code(gate_logits), KIND_FORWARD)
+        rc = lib.ascan_forward_sigmoid_gates(_ptr(gate_logits), _ptr(tokens), _ptr(out), rows, T,
+                                             dtype_code(gate_logits), _ptr(ws), ws.numel(), _stream(gate_logits))
+    if rc == UNSUPPORTED:
+        return False
+    check(rc, "ascan_forward_sigmoid_gates")
+    return True
+
+
+def backward_sigmoid_gates(gate_logits, states, grad_out, d_logits, d_tokens) -> bool:
+    """Fused backward of `forward_sigmoid_gates`: d_logits and d_tokens.  False when unsupported."""
+    _require_cuda(gate_logits, states, grad_out, d_logits, d_tokens)
+    rows = gate_logits.numel() // gate_logits.shape[-1] if gate_logits.shape[-1] else 0
+    T = gate_logits.shape[-1]
+    with torch.cuda.device(gate_logits.device):
+        ws = workspace(gate_logits.device, rows, T, dtype_code(gate_logits), KIND_BACKWARD)
+        rc = lib.ascan_backward_sigmoid_gates(_ptr(gate_logits), _ptr(states), _ptr(grad_out), _ptr(d_logits),
+                                              _ptr(d_tokens), rows, T, dtype_code(gate_logits), _ptr(ws), ws.numel(),
+                                              _stream(gate_logits))
+    if rc == UNSUPPORTED:
+        return False
+    check(rc, "ascan_backward_sigmoid_gates")
     return True
 
 

@@ -195,6 +195,64 @@ static void fill_common(StreamParams &p, const ascan_plan &pl, int64_t rows, int
     p.team_size = pl.team_size;
 }
 
+// Plan for the fused variants, which exist only in the chained stream plan with the bulk
+// loader and one row or segment per item.
+static int plan_for_variant(int64_t rows, int64_t seqlen, int dtype, int kind, bool reverse, void *ws, size_t ws_bytes,
+                            ascan_plan *pl) {
+    PlanInput in;
+    in.reverse = reverse;
+    in.rows = rows;
+    in.seqlen = seqlen;
+    in.dtype = dtype;
+    in.kind = kind;
+    in.aligned = true;
+    in.workspace = ws && (reinterpret_cast<uintptr_t>(ws) & 255u) == 0;
+    in.allow_lookback = false;
+    in.allow_team = false;
+    int rc = cached_sm_count(&in.sm_count);
+    if (rc != ASCAN_OK) return rc;
+    rc = make_plan(in, pl);
+    if (rc == ASCAN_OK && pl->workspace_bytes > ws_bytes && in.workspace) {
+        in.workspace = false;
+        rc = make_plan(in, pl);
+    }
+    if (rc != ASCAN_OK) return rc;
+    if (pl->loader != 0 || pl->rows_per_item != 1 || pl->kernel != 0) return ASCAN_ERR_UNSUPPORTED;
+    return ASCAN_OK;
+}
+
+template <class KFN>
+static int launch_variant(KFN kfn, const StreamParams &p, const ascan_plan &pl, cudaStream_t st) {
+    int rc = ensure_smem(reinterpret_cast<const void *>(kfn), pl.smem_bytes);
+    if (rc != ASCAN_OK) return rc;
+    kfn<<<pl.grid, pl.warps_per_cta * 32, pl.smem_bytes, st>>>(p);
+    return cudaGetLastError() == cudaSuccess ? ASCAN_OK : ASCAN_ERR_LAUNCH;
+}
+
+template <class TR>
+static int launch_sigmoid(int kind, const StreamParams &p, const ascan_plan &pl, cudaStream_t st) {
+    if (kind == ASCAN_KIND_FORWARD) {
+        if (pl.chunks_per_lane != 3) return ASCAN_ERR_UNSUPPORTED;
+        return launch_variant(stream_kernel<TR, 3, K_SCAN, false, true, false, false, false, 1>, p, pl, st);
+    }
+    if (pl.chunks_per_lane == 3)
+        return launch_variant(stream_kernel<TR, 3, K_BWD, true, true, false, false, false, 1>, p, pl, st);
+    if constexpr (TR::EPC == 8) {
+        if (pl.chunks_per_lane == 2)
+            return launch_variant(stream_kernel<TR, 2, K_BWD, true, true, false, false, false, 1>, p, pl, st);
+    }
+    return ASCAN_ERR_UNSUPPORTED;
+}
+
+static int launch_sigmoid_dtype(int dtype, int kind, const StreamParams &p, const ascan_plan &pl, cudaStream_t st) {
+    switch (dtype) {
+        case ASCAN_F32: return launch_sigmoid<TraitsF32>(kind, p, pl, st);
+        case ASCAN_BF16: return launch_sigmoid<TraitsBF16>(kind, p, pl, st);
+        case ASCAN_F16: return launch_sigmoid<TraitsF16>(kind, p, pl, st);
+        default: return ASCAN_ERR_UNSUPPORTED;
+    }
+}
+
 }  // namespace ascan
 
 using namespace ascan;
@@ -378,6 +436,47 @@ int ascan_forward_complex_real_tokens(const void *gates, const void *tokens_real
     };
     return reverse ? launch(stream_kernel<TraitsC64, 3, K_SCAN, true, true, false, false, true>)
                    : launch(stream_kernel<TraitsC64, 3, K_SCAN, false, true, false, false, true>);
+}
+
+int ascan_forward_sigmoid_gates(const void *gate_logits, const void *tokens, void *out, int64_t rows, int64_t seqlen,
+                                int dtype, void *ws, size_t ws_bytes, void *stream) {
+    if (rows < 0 || seqlen < 1 || dtype_size(dtype) == 0) return ASCAN_ERR_INVALID_ARG;
+    if (dtype == ASCAN_C64) return ASCAN_ERR_UNSUPPORTED;
+    if (rows == 0) return ASCAN_OK;
+    if (!gate_logits || !tokens || !out) return ASCAN_ERR_INVALID_ARG;
+    if (!(aligned16(gate_logits) && aligned16(tokens) && aligned16(out))) return ASCAN_ERR_UNSUPPORTED;
+    ascan_plan pl;
+    int rc = plan_for_variant(rows, seqlen, dtype, ASCAN_KIND_FORWARD, false, ws, ws_bytes, &pl);
+    if (rc != ASCAN_OK) return rc;
+    StreamParams p = {};
+    p.in0 = gate_logits;
+    p.in1 = tokens;
+    p.out0 = out;
+    fill_common(p, pl, rows, seqlen, ws);
+    return launch_sigmoid_dtype(dtype, ASCAN_KIND_FORWARD, p, pl, static_cast<cudaStream_t>(stream));
+}
+
+int ascan_backward_sigmoid_gates(const void *gate_logits, const void *states, const void *grad_out, void *d_logits,
+                                 void *d_tokens, int64_t rows, int64_t seqlen, int dtype, void *ws, size_t ws_bytes,
+                                 void *stream) {
+    if (rows < 0 || seqlen < 1 || dtype_size(dtype) == 0) return ASCAN_ERR_INVALID_ARG;
+    if (dtype == ASCAN_C64) return ASCAN_ERR_UNSUPPORTED;
+    if (rows == 0) return ASCAN_OK;
+    if (!gate_logits || !states || !grad_out || !d_logits || !d_tokens) return ASCAN_ERR_INVALID_ARG;
+    if (!(aligned16(gate_logits) && aligned16(states) && aligned16(grad_out) && aligned16(d_logits) &&
+          aligned16(d_tokens)))
+        return ASCAN_ERR_UNSUPPORTED;
+    ascan_plan pl;
+    int rc = plan_for_variant(rows, seqlen, dtype, ASCAN_KIND_BACKWARD, false, ws, ws_bytes, &pl);
+    if (rc != ASCAN_OK) return rc;
+    StreamParams p = {};
+    p.in0 = gate_logits;
+    p.in1 = grad_out;
+    p.in2 = states;
+    p.out0 = d_tokens;
+    p.out1 = d_logits;
+    fill_common(p, pl, rows, seqlen, ws);
+    return launch_sigmoid_dtype(dtype, ASCAN_KIND_BACKWARD, p, pl, static_cast<cudaStream_t>(stream));
 }
 
 int ascan_fold_carries(const void *gathered, int64_t rows, int world, int rank, int stride, int dtype, int suffix,

@@ -112,6 +112,20 @@ __host__ __device__ constexpr int stream_warp_smem(int nch, int stages, int kind
 constexpr uint32_t LOAD_WAIT_POLLS = 1u << 22;
 constexpr uint32_t CARRY_WAIT_POLLS = 1u << 20;
 
+// sigmoid in fp32 from the approximate exp2 and reciprocal instructions.  REFINE adds one
+// Newton step to the reciprocal: the raw instruction is biased by up to an ulp, and a bias
+// in gates near one grows by 1 / (1 - gate) in the states (seen as 2e-5 at gates of 0.9995),
+// which fp32 storage shows and the 16-bit dtypes do not.
+template <bool REFINE>
+__device__ __forceinline__ float sigmoid_fast(float z) {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(z * -1.4426950408889634f));
+    const float d = 1.0f + e;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d));
+    if (REFINE && e < 1e30f) r = fmaf(r, fmaf(-d, r, 1.0f), r);
+    return r;
+}
+
 struct ItemDesc {
     int64_t e_begin;   // first element of the item in the flat matrix
     int64_t row0;      // row of that element
@@ -126,7 +140,13 @@ struct ItemDesc {
 // TOKR (complex forward only): the token stream is real fp32 (half the bytes per tile); the
 // imaginary part is taken as zero, which fuses the reference's promotion
 // `torch.complex(inputs, zeros)` (complex.py:168-169) into the scan.
-template <class TR, int NCH, int KIND, bool REVERSE, bool BULK, bool INTERIOR, bool LOOKBACK, bool TOKR = false>
+//
+// ACT = 1 (real dtypes, K_SCAN and K_BWD, one row or segment per item): the first input holds
+// gate pre-activations z and the gate is sigmoid(z), computed in fp32 as the tile is read.
+// The fused backward returns d_z[t] = x[t-1] * g[t] * s(1 - s) in place of d_gates, which
+// removes the caller's sigmoid pass and its backward pass over the (B, C, T) tensors.
+template <class TR, int NCH, int KIND, bool REVERSE, bool BULK, bool INTERIOR, bool LOOKBACK, bool TOKR = false,
+          int ACT = 0>
 __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ? 448 : 512), 1) stream_kernel(const StreamParams p) {
     using V = typename TR::V;
     using Raw = typename TR::Raw;
@@ -378,7 +398,10 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
         V x_carry = vzero(V());    // state entering the tile
         V x2_carry = vzero(V());   // reduce kinds: response to a unit incoming state
         // backward kinds: gate of the first element above the tile
-        const V item_end_gate = head.gate_kind == 1 ? TR::decode(head.gate) : (head.gate_kind == 2 ? head.halo : vone(V()));
+        V item_end_gate = head.gate_kind == 1 ? TR::decode(head.gate) : (head.gate_kind == 2 ? head.halo : vone(V()));
+        if constexpr (ACT == 1) {
+            if (head.gate_kind == 1) item_end_gate = sigmoid_fast<TR::ESIZE == 4>(item_end_gate);
+        }
         V next_gate = item_end_gate;
         const bool agg_pass = LOOKBACK && cur.phase == 0;   // stream for the aggregate only
         if (LOOKBACK && cur.s_log > 0) {
@@ -480,6 +503,10 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
                     TR::unpack(qb, &b[c * EPC]);
                 }
             }
+            if constexpr (ACT == 1) {
+#pragma unroll
+                for (int j = 0; j < K; ++j) a[j] = sigmoid_fast<TR::ESIZE == 4>(a[j]);
+            }
             V xp[KIND == K_BWD ? K : 1];
             V x_below = vzero(V());   // state just below the tile, from the halo chunk
             if (KIND == K_BWD) {
@@ -507,8 +534,10 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
             }
 
             // ---- backward kinds: shift the gates by one step inside registers
+            V gate_first = vone(V());   // gate of the lane's first element, before the shift
             if (BACK) {
                 const V g0 = a[0];
+                gate_first = g0;
                 V up = shfl_down(g0, 1);
                 if (lane == 31) up = next_gate;
 #pragma unroll
@@ -714,9 +743,21 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
                     // element below (neighbouring lane by shuffle, tile halo for lane 0)
                     V dn = shfl_up(xp[K - 1], 1);
                     if (lane == 0) dn = halo_in_row ? (BULK ? x_below : TR::decode(x_halo_raw)) : x_halo_row;
+                    if constexpr (ACT == 1) {
+                        // after the shift a[j-1] is the gate s of element j: chain rule through
+                        // the sigmoid, d_z = d_gate * s * (1 - s); downwards, so that each gate
+                        // is read before its slot receives a gradient
 #pragma unroll
-                    for (int j = 1; j < K; ++j) a[j] = vmul(vconj(xp[j - 1]), b[j]);
-                    a[0] = vmul(vconj(dn), b[0]);
+                        for (int j = K - 1; j >= 1; --j) {
+                            const V sg = a[j - 1];
+                            a[j] = vmul(vmul(xp[j - 1], b[j]), fmaf(-sg, sg, sg));
+                        }
+                        a[0] = vmul(vmul(dn, b[0]), fmaf(-gate_first, gate_first, gate_first));
+                    } else {
+#pragma unroll
+                        for (int j = 1; j < K; ++j) a[j] = vmul(vconj(xp[j - 1]), b[j]);
+                        a[0] = vmul(vconj(dn), b[0]);
+                    }
                     if (INTERIOR && (start_mask_lo | start_mask_hi)) {
 #pragma unroll
                         for (int j = 0; j < K; ++j) {

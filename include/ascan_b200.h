@@ -153,6 +153,25 @@ int ascan_forward_complex_real_tokens(const void *gates, const void *tokens_real
                                       void *ws, size_t ws_bytes, void *stream);
 
 /*
+ * Scan whose gates are sigmoid(gate_logits), the activation fused into the kernels
+ * (real dtypes only).  The reference takes ready-made gates (warp.py:68-83), so a
+ * caller with sigmoid gates runs an elementwise pass before the scan and another
+ * one in the backward; here the forward reads the logits and the backward returns
+ * d_logits[t] = x[t-1] * g[t] * s[t] * (1 - s[t]) directly.  The sigmoid is
+ * evaluated in fp32 and is never rounded to the storage dtype.  Needs 16-byte
+ * aligned pointers and a shape the stream plan handles with one row or segment per
+ * item; otherwise ASCAN_ERR_UNSUPPORTED is returned and the caller applies the
+ * activation itself.  No counterpart in the reference.
+ */
+int ascan_forward_sigmoid_gates(const void *gate_logits, const void *tokens, void *out,
+                                int64_t rows, int64_t seqlen, int dtype,
+                                void *ws, size_t ws_bytes, void *stream);
+int ascan_backward_sigmoid_gates(const void *gate_logits, const void *states, const void *grad_out,
+                                 void *d_logits, void *d_tokens,
+                                 int64_t rows, int64_t seqlen, int dtype,
+                                 void *ws, size_t ws_bytes, void *stream);
+
+/*
  * Time-sharded scans: folds the carries gathered from all ranks into this rank's
  * incoming state.  `gathered` holds world x rows x stride values of the compute
  * type (float, or float2 for ASCAN_C64; other dtypes use float): {P, S, first gate}
