@@ -71,6 +71,8 @@ def _load():
     lib.ascan_forward_complex_real_tokens.argtypes = [vp, vp, vp, i64, i64, i32, vp, sz, vp]
     lib.ascan_fold_carries.restype = i32
     lib.ascan_fold_carries.argtypes = [vp, i64, i32, i32, i32, i32, i32, vp, vp, vp]
+    lib.ascan_backward_complex_real_tokens.restype = i32
+    lib.ascan_backward_complex_real_tokens.argtypes = [vp, vp, vp, vp, vp, i64, i64, vp, sz, vp]
     lib.ascan_forward_sigmoid_gates.restype = i32
     lib.ascan_forward_sigmoid_gates.argtypes = [vp, vp, vp, i64, i64, i32, vp, sz, vp]
     lib.ascan_backward_sigmoid_gates.restype = i32
@@ -86,7 +88,7 @@ EXPORTS = (
     "ascan_version", "ascan_strerror", "ascan_forward", "ascan_backward", "ascan_reduce_forward",
     "ascan_reduce_backward", "ascan_workspace_bytes", "ascan_plan_describe", "ascan_check",
     "ascan_forward_no_alloc", "ascan_fold_carries", "ascan_forward_complex_real_tokens",
-    "ascan_forward_sigmoid_gates", "ascan_backward_sigmoid_gates",
+    "ascan_forward_sigmoid_gates", "ascan_backward_sigmoid_gates", "ascan_backward_complex_real_tokens",
 )
 
 
@@ -178,6 +180,22 @@ def forward_complex_real_tokens(gates, tokens_real, out, reverse=False) -> bool:
     if rc == UNSUPPORTED:
         return False
     check(rc, "ascan_forward_complex_real_tokens")
+    return True
+
+
+def backward_complex_real_tokens(gates, states, grad_out, d_gates, d_tokens_real) -> bool:
+    """Fused complex backward that writes only the real part of the token gradient (float32).
+    Returns False when the library has no fused kernel for this shape or alignment."""
+    _require_cuda(gates, states, grad_out, d_gates, d_tokens_real)
+    rows = gates.numel() // gates.shape[-1] if gates.shape[-1] else 0
+    T = gates.shape[-1]
+    with torch.cuda.device(gates.device):
+        ws = workspace(gates.device, rows, T, C64, KIND_BACKWARD)
+        rc = lib.ascan_backward_complex_real_tokens(_ptr(gates), _ptr(states), _ptr(grad_out), _ptr(d_gates),
+                                                    _ptr(d_tokens_real), rows, T, _ptr(ws), ws.numel(), _stream(gates))
+    if rc == UNSUPPORTED:
+        return False
+    check(rc, "ascan_backward_complex_real_tokens")
     return True
 
 

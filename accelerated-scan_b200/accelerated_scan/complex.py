@@ -50,6 +50,7 @@ class Scan(torch.autograd.Function):
         if forget.dtype != torch.complex64:
             raise RuntimeError("forget must be complex64")
         real_inputs = not torch.is_complex(inputs)
+        inputs_dtype = inputs.dtype
         B, C, T = forget.shape
         assert inputs.shape == (B, C, T)
         assert forget.is_contiguous()
@@ -71,6 +72,7 @@ class Scan(torch.autograd.Function):
                 _native.forward(forget, inputs, states)
         ctx.save_for_backward(forget, states)
         ctx.real_inputs = real_inputs
+        ctx.inputs_dtype = inputs_dtype
         return states
 
     # reverse scan over the conjugated gates shifted by one step (complex.py:188-219)
@@ -82,11 +84,16 @@ class Scan(torch.autograd.Function):
         assert states.is_contiguous()
 
         d_forget = torch.empty_like(forget)
+        if ctx.real_inputs and states.numel():
+            # real inputs: the kernel writes the real part of their gradient only (complex.py:217-218)
+            d_real = torch.empty(states.shape, dtype=torch.float32, device=states.device)
+            if _native.backward_complex_real_tokens(forget, states, d_output, d_forget, d_real):
+                return d_forget, d_real.to(ctx.inputs_dtype)
         d_inputs = torch.empty_like(states)
         if states.numel():
             _native.backward(forget, states, d_output, d_forget, d_inputs)
         if ctx.real_inputs:
-            d_inputs = d_inputs.real
+            d_inputs = d_inputs.real.to(ctx.inputs_dtype)
         return d_forget, d_inputs
 
 

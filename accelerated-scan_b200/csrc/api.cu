@@ -438,6 +438,30 @@ int ascan_forward_complex_real_tokens(const void *gates, const void *tokens_real
                    : launch(stream_kernel<TraitsC64, 3, K_SCAN, false, true, false, false, true>);
 }
 
+int ascan_backward_complex_real_tokens(const void *gates, const void *states, const void *grad_out, void *d_gates,
+                                       void *d_tokens_real, int64_t rows, int64_t seqlen, void *ws, size_t ws_bytes,
+                                       void *stream) {
+    if (rows < 0 || seqlen < 1) return ASCAN_ERR_INVALID_ARG;
+    if (rows == 0) return ASCAN_OK;
+    if (!gates || !states || !grad_out || !d_gates || !d_tokens_real) return ASCAN_ERR_INVALID_ARG;
+    const bool al = aligned16(gates) && aligned16(states) && aligned16(grad_out) && aligned16(d_gates) &&
+                    aligned16(d_tokens_real);
+    if (!al || seqlen % 4 != 0) return ASCAN_ERR_UNSUPPORTED;
+    ascan_plan pl;
+    int rc = plan_for_variant(rows, seqlen, ASCAN_C64, ASCAN_KIND_BACKWARD, false, ws, ws_bytes, &pl);
+    if (rc != ASCAN_OK) return rc;
+    if (pl.chunks_per_lane != 3) return ASCAN_ERR_UNSUPPORTED;
+    StreamParams p = {};
+    p.in0 = gates;
+    p.in1 = grad_out;
+    p.in2 = states;
+    p.out0 = d_tokens_real;
+    p.out1 = d_gates;
+    fill_common(p, pl, rows, seqlen, ws);
+    return launch_variant(stream_kernel<TraitsC64, 3, K_BWD, true, true, false, false, true>, p, pl,
+                          static_cast<cudaStream_t>(stream));
+}
+
 int ascan_forward_sigmoid_gates(const void *gate_logits, const void *tokens, void *out, int64_t rows, int64_t seqlen,
                                 int dtype, void *ws, size_t ws_bytes, void *stream) {
     if (rows < 0 || seqlen < 1 || dtype_size(dtype) == 0) return ASCAN_ERR_INVALID_ARG;

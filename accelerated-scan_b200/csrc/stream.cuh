@@ -137,9 +137,11 @@ struct ItemDesc {
     bool valid;
 };
 
-// TOKR (complex forward only): the token stream is real fp32 (half the bytes per tile); the
-// imaginary part is taken as zero, which fuses the reference's promotion
-// `torch.complex(inputs, zeros)` (complex.py:168-169) into the scan.
+// TOKR (complex64, K_SCAN and K_BWD): the tokens of the caller are real fp32.  Forward: the
+// token stream has half the bytes per tile and its imaginary part is taken as zero, which
+// fuses the reference's promotion `torch.complex(inputs, zeros)` (complex.py:168-169) into
+// the scan.  Backward: only the real part of d_tokens is written, as fp32, which is what the
+// reference returns for real inputs (`d_inputs.real`, complex.py:217-218).
 //
 // ACT = 1 (real dtypes, K_SCAN and K_BWD, one row or segment per item): the first input holds
 // gate pre-activations z and the gate is sigmoid(z), computed in fp32 as the tile is read.
@@ -160,6 +162,8 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
     constexpr int NIN = stream_nin(KIND);
     constexpr int NOUT = stream_nout(KIND);
     constexpr int OUTBUFS = BULK ? 2 : 1;
+    constexpr bool TOK_IN_REAL = TOKR && KIND == K_SCAN;
+    constexpr bool TOK_OUT_REAL = TOKR && KIND == K_BWD;
     const int NSTG = BULK ? p.stages : 1;
     const int WARP_SMEM = stream_warp_smem(NCH, p.stages, KIND, BULK);
 
@@ -270,7 +274,7 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
         // 16-byte aligned, so that chunk is aligned too); skipped at the start of the matrix
         const bool halo = (KIND == K_BWD) && goff > 0;
         unsigned char *dst = stage_base + s * STAGE_BYTES;
-        if constexpr (TOKR) {
+        if constexpr (TOK_IN_REAL) {
             // complex gates, real tokens: the token tile has half the bytes
             mbar_expect_tx(&bars[s], bytes + bytes / 2);
             bulk_g2s(dst, gbase[0] + goff, bytes, &bars[s]);
@@ -493,7 +497,7 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
             for (int c = 0; c < NCH; ++c) {
                 const uint4 qa = *reinterpret_cast<const uint4 *>(stg + 0 * TB + (lane * NCH + c) * 16);
                 TR::unpack(qa, &a[c * EPC]);
-                if constexpr (TOKR) {
+                if constexpr (TOK_IN_REAL) {
                     // K real tokens of 4 bytes per lane, read as 8-byte pairs; imaginary part zero
                     const float2 tk = *reinterpret_cast<const float2 *>(stg + TB + lane * (K * 4) + c * 8);
                     b[2 * c] = make_float2(tk.x, 0.0f);
@@ -780,7 +784,12 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
                 __syncwarp();
 #pragma unroll
                 for (int c = 0; c < NCH; ++c) {
-                    *reinterpret_cast<uint4 *>(ob + (lane * NCH + c) * 16) = TR::pack(&b[c * EPC]);
+                    if constexpr (TOK_OUT_REAL) {
+                        // real parts only: K values of 4 bytes per lane, written as 8-byte pairs
+                        *reinterpret_cast<float2 *>(ob + lane * (K * 4) + c * 8) = make_float2(b[2 * c].x, b[2 * c + 1].x);
+                    } else {
+                        *reinterpret_cast<uint4 *>(ob + (lane * NCH + c) * 16) = TR::pack(&b[c * EPC]);
+                    }
                     if (NOUT > 1) *reinterpret_cast<uint4 *>(ob + TB + (lane * NCH + c) * 16) = TR::pack(&a[c * EPC]);
                 }
                 if (BULK) {
@@ -791,7 +800,9 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
                         const int64_t goff = (cur.e_begin + toff) * TR::ESIZE;
 #pragma unroll
                         for (int k = 0; k < NOUT; ++k) {
-                            if (st_hint)
+                            if (TOK_OUT_REAL && k == 0)
+                                bulk_s2g(obase[0] + goff / 2, ob, bytes / 2);
+                            else if (st_hint)
                                 bulk_s2g_hint(obase[k] + goff, ob + k * TB, bytes, st_pol);
                             else
                                 bulk_s2g(obase[k] + goff, ob + k * TB, bytes);

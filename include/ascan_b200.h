@@ -153,6 +153,19 @@ int ascan_forward_complex_real_tokens(const void *gates, const void *tokens_real
                                       void *ws, size_t ws_bytes, void *stream);
 
 /*
+ * Fused complex backward for REAL tokens: as ascan_backward with dtype complex64,
+ * but d_tokens_real receives only the real part of the token gradient, as fp32
+ * (rows x seqlen floats).  This is what the reference's complex Scan.backward
+ * returns for real inputs (`d_inputs.real`, complex.py:217-218) without writing
+ * the complex gradient first.  Same conditions and fallback rule as
+ * ascan_forward_complex_real_tokens.
+ */
+int ascan_backward_complex_real_tokens(const void *gates, const void *states, const void *grad_out,
+                                       void *d_gates, void *d_tokens_real,
+                                       int64_t rows, int64_t seqlen,
+                                       void *ws, size_t ws_bytes, void *stream);
+
+/*
  * Scan whose gates are sigmoid(gate_logits), the activation fused into the kernels
  * (real dtypes only).  The reference takes ready-made gates (warp.py:68-83), so a
  * caller with sigmoid gates runs an elementwise pass before the scan and another

@@ -166,3 +166,14 @@ def test_real_tokens_fused_into_the_kernel(cuda_device, rows, seqlen, fused):
         assert _native.forward_complex_real_tokens(f, x, rev, reverse=True)
         assert rel_err(to_np(rev), scan_oracle.scan(forget.numpy(), inputs.numpy(), reverse=True)) <= REL
     assert rel_err(to_np(cplx.scan(f, x)), want) <= REL
+    # backward: only the real part of the token gradient is written, as fp32
+    g = torch.Generator().manual_seed(22)
+    grad_out = torch.complex(torch.randn(1, rows, seqlen, generator=g), torch.randn(1, rows, seqlen, generator=g))
+    want_df, want_dx = scan_oracle.scan_backward(forget.numpy(), want, grad_out.numpy())
+    states = torch.from_numpy(want).to(cuda_device)
+    d_f = torch.empty_like(f)
+    d_x = torch.full((1, rows, seqlen), float("nan"), dtype=torch.float32, device=cuda_device)
+    assert _native.backward_complex_real_tokens(f, states, grad_out.to(cuda_device), d_f, d_x) == fused
+    if fused:
+        assert rel_err(to_np(d_f), want_df) <= REL
+        assert rel_err(to_np(d_x), want_dx.real) <= REL
