@@ -430,8 +430,11 @@ def run_also(torch, _native, dev):
 def run_sweep(args, torch, _native, dev, dtype, esize, gates, tokens, grad_out, out, d_gates, d_tokens):
     """Forward and backward time for (8, 1536, L), L = 128 ... 65536 (the reference's benchmark
     sweep, tests/bench.py:15), on prefixes of the benchmark's buffers.  Short sequences fit
-    in L2, so a 256 MB buffer is rewritten before every timed launch to flush it."""
+    in L2, so a 256 MB buffer is rewritten before every timed launch to flush it; a second
+    256 MB buffer is then read, which pushes the flush's own dirty lines out to DRAM so that
+    the timed launch does not pay for writing them back (8-10 us at these sizes)."""
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    drain = torch.zeros(64 << 20, dtype=torch.float32, device=dev)
     rows = B * C
     points = []
     for L in [2 ** i for i in range(7, 17)]:
@@ -444,6 +447,7 @@ def run_sweep(args, torch, _native, dev, dtype, esize, gates, tokens, grad_out, 
             ts = []
             for _ in range(reps):
                 flush.zero_()
+                drain.sum()
                 a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 a.record()
                 fn()
@@ -457,8 +461,9 @@ def run_sweep(args, torch, _native, dev, dtype, esize, gates, tokens, grad_out, 
         tb = timed(lambda: _native.backward(g, o, go, dg, dx))
         points.append({"L": L, "fwd_ms": round(tf, 5), "bwd_ms": round(tb, 5),
                        "fwd_GBps": round(3 * esize * n / tf / 1e6, 1), "bwd_GBps": round(5 * esize * n / tb / 1e6, 1)})
-    del flush
-    return {"shape": f"({B},{C},L) {args.dtype}", "l2": "256 MB flush buffer rewritten before every timed launch",
+    del flush, drain
+    return {"shape": f"({B},{C},L) {args.dtype}",
+            "l2": "256 MB flush buffer rewritten, then another 256 MB read (drains the flush's dirty lines), before every timed launch",
             "timing": "median of 7 single launches, CUDA events", "points": points}
 
 
