@@ -380,8 +380,9 @@ TRAFFIC_BWD_BYTES_PER_ELEM = 9.86
 
 
 def run_also(torch, _native, dev):
-    """fwd+bwd of the same kernels for fp32 (8,1536,65536) and complex64 (4,1024,16384), inputs
-    resident, every tensor larger than L2, 10 timed steps after 3 warm-up steps."""
+    """fwd+bwd of the same kernels for fp32 (8,1536,65536) and complex64 (4,1024,16384), and of
+    the sigmoid-gate variant in bf16; inputs resident, every tensor larger than L2, 10 timed
+    steps after warm-up."""
     import math
 
     peak, _ = measured_peak()
@@ -424,6 +425,38 @@ def run_also(torch, _native, dev):
                         "pct_of_nominal_8TBs": round(100 * both / 8000.0, 2)})
         del g, x, go, o, dg, dx
         torch.cuda.empty_cache()
+    # sigmoid gates fused into the kernels (accelerated_scan.gated), bf16 at the headline shape
+    shape = (B, C, 65536)
+    gen = torch.Generator(device=dev).manual_seed(4322)
+    z = (6.0 + 3.0 * torch.rand(*shape, device=dev, generator=gen)).to(torch.bfloat16)
+    x = torch.rand(*shape, device=dev, generator=gen).to(torch.bfloat16)
+    go = torch.randn(*shape, device=dev, generator=gen).to(torch.bfloat16)
+    o, dz, dx = torch.empty_like(x), torch.empty_like(x), torch.empty_like(x)
+    if _native.forward_sigmoid_gates(z, x, o) and _native.backward_sigmoid_gates(z, o, go, dz, dx):
+        for _ in range(2):
+            _native.forward_sigmoid_gates(z, x, o)
+            _native.backward_sigmoid_gates(z, o, go, dz, dx)
+        torch.cuda.synchronize()
+        K = 10
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+        for k in range(K):
+            ev[k][0].record()
+            _native.forward_sigmoid_gates(z, x, o)
+            ev[k][1].record()
+            _native.backward_sigmoid_gates(z, o, go, dz, dx)
+            ev[k][2].record()
+        torch.cuda.synchronize()
+        fwd = sum(e[0].elapsed_time(e[1]) for e in ev) / K
+        bwd = sum(e[1].elapsed_time(e[2]) for e in ev) / K
+        n, es = x.numel(), x.element_size()
+        both = 8 * es * n / ((fwd + bwd) * 1e-3) / 1e9
+        results.append({"workload": "bf16 (8,1536,65536), gates = sigmoid(logits) evaluated in the kernels",
+                        "fwd_ms": round(fwd, 5), "bwd_ms": round(bwd, 5),
+                        "fwd_GBps": round(3 * es * n / fwd / 1e6, 1), "bwd_GBps": round(5 * es * n / bwd / 1e6, 1),
+                        "value": round(both, 1), "unit": UNIT, "frac_of_measured_peak": round(both / peak, 4),
+                        "pct_of_nominal_8TBs": round(100 * both / 8000.0, 2)})
+    del z, x, go, o, dz, dx
+    torch.cuda.empty_cache()
     return results
 
 
