@@ -137,3 +137,20 @@ def test_cpu_tensors_fail_loudly():
         cplx.scan(g, g.clone())
     with pytest.raises(AssertionError):
         warp.Scan.apply(g, torch.rand(1, 2, 16))
+
+
+def test_extensions_fail_loudly_on_cpu_tensors():
+    """The modules beyond the reference's surface have no CPU path either."""
+    import torch
+    from accelerated_scan import gated, stateful
+
+    g = torch.rand(1, 2, 64)
+    with pytest.raises(RuntimeError):
+        gated.scan(g, g.clone())
+    with pytest.raises(RuntimeError):
+        stateful.scan(g, g.clone(), torch.zeros(1, 2))
+    with pytest.raises(RuntimeError):
+        stateful.final_state(g, g.clone())
+    c = torch.complex(g, g)
+    with pytest.raises(RuntimeError):
+        gated.scan(c, c)
