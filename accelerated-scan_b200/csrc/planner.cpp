@@ -93,13 +93,15 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     const int64_t tiles_row = (in.seqlen + te - 1) / te;
     const bool reverse_order = in.kind == ASCAN_KIND_BACKWARD || in.kind == ASCAN_KIND_REDUCE_BACKWARD || in.reverse;
     const bool can_split = use_ws && (!bulk || align_rows == 1) && env_int("ASCAN_NO_SPLIT", 0) == 0;
-    // Fewer rows than SMs: even a whole CTA per row (the team plan below) would leave SMs
+    // Clearly fewer rows than SMs: a whole CTA per row (the team plan below) would leave SMs
     // idle, so the look-back plan lets warps of many CTAs scan segments of one row at once.
     // Every segment but a row's first is streamed twice (aggregate pass, scan pass; the second
     // read finds the data in L2), which caps this plan near 4 TB/s.
     const bool scan_kind = in.kind == ASCAN_KIND_FORWARD || in.kind == ASCAN_KIND_BACKWARD;
     int lb_tiles = env_int("ASCAN_LOOKBACK_TILES", 8);
-    const int64_t lookback_rows = env_int("ASCAN_LOOKBACK_ROWS", in.sm_count);   // below one row per SM
+    // below three rows per four SMs (measured on 148 SMs: at 96 rows look-back and teams of 12
+    // warps tie, at 128 rows the teams win by 10-20 %)
+    const int64_t lookback_rows = env_int("ASCAN_LOOKBACK_ROWS", in.sm_count * 3 / 4);
     if (lb_tiles < 1) lb_tiles = 1;
     const bool lookback = can_split && bulk && scan_kind && in.allow_lookback && in.rows < lookback_rows &&
                           tiles_row >= 2 * lb_tiles && env_int("ASCAN_NO_LOOKBACK", 0) == 0;
@@ -189,7 +191,9 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     pl.stages = bulk ? stages : 1;
 
     // (the team kernel's backward stage has the same 128-byte halo slot, so the sizes agree)
-    const int wsm = warp_smem(nch, pl.stages, in.kind, bulk);
+    // look-back kernels keep, per tile of a segment and lane, two values of the compute type
+    // (must match lookback_prefix_bytes in stream.cuh)
+    const int wsm = warp_smem(nch, pl.stages, in.kind, bulk) + (lookback ? 8 * 32 * 2 * (esize == 8 ? 8 : 4) : 0);
     int wpc = (kMaxSmemPerCta - (team > 1 ? kMaxWarpsPerCta / team * 256 : 0)) / wsm;
     // the stream kernels are compiled for 16 warps per CTA (14 for the fused backward, which
     // needs more registers); 14 measured best (more warps hide more of a tile's dependent

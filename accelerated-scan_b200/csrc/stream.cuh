@@ -109,6 +109,13 @@ __host__ __device__ constexpr int stream_warp_smem(int nch, int stages, int kind
     return nstg * stream_stage_bytes(nch, kind) + outbufs * stream_nout(kind) * tb + 128;
 }
 
+// Look-back plan: the aggregate pass leaves, per tile and lane, the affine map from the
+// segment's start to the lane's first element; the scan pass applies it to the segment's
+// incoming state and goes straight to the recurrence (no lane aggregates, no shuffle
+// combine a second time).  Segments of up to LB_PREFIX_TILES tiles use it.
+constexpr int LB_PREFIX_TILES = 8;
+__host__ __device__ constexpr int lookback_prefix_bytes(int vsize) { return LB_PREFIX_TILES * 32 * 2 * vsize; }
+
 constexpr uint32_t LOAD_WAIT_POLLS = 1u << 22;
 constexpr uint32_t CARRY_WAIT_POLLS = 1u << 20;
 
@@ -165,7 +172,7 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
     constexpr bool TOK_IN_REAL = TOKR && KIND == K_SCAN;
     constexpr bool TOK_OUT_REAL = TOKR && KIND == K_BWD;
     const int NSTG = BULK ? p.stages : 1;
-    const int WARP_SMEM = stream_warp_smem(NCH, p.stages, KIND, BULK);
+    const int WARP_SMEM = stream_warp_smem(NCH, p.stages, KIND, BULK) + (LOOKBACK ? lookback_prefix_bytes(sizeof(V)) : 0);
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31;
@@ -176,6 +183,7 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
     constexpr int STAGE_BYTES = stream_stage_bytes(NCH, KIND);
     unsigned char *out_base = wsm + NSTG * STAGE_BYTES;
     uint64_t *bars = reinterpret_cast<uint64_t *>(out_base + OUTBUFS * NOUT * TB);
+    V *lane_prefix = reinterpret_cast<V *>(reinterpret_cast<unsigned char *>(bars) + 128);   // LOOKBACK only
 
     const int64_t w = static_cast<int64_t>(blockIdx.x) * wpc + wib;
     const int64_t W = static_cast<int64_t>(gridDim.x) * wpc;
@@ -408,6 +416,9 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
         }
         V next_gate = item_end_gate;
         const bool agg_pass = LOOKBACK && cur.phase == 0;   // stream for the aggregate only
+        // the scan pass of a segment whose aggregate pass left the lanes' prefixes behind
+        const bool keep_prefix = LOOKBACK && cur.s_log > 0 && cur.nt <= LB_PREFIX_TILES;
+        const bool use_prefix = keep_prefix && !agg_pass;
         if (LOOKBACK && cur.s_log > 0) {
             if (agg_pass) {
                 x2_carry = vone(V());          // zero state and unit response: (B, A) of the segment
@@ -513,7 +524,7 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
             }
             V xp[KIND == K_BWD ? K : 1];
             V x_below = vzero(V());   // state just below the tile, from the halo chunk
-            if (KIND == K_BWD) {
+            if (KIND == K_BWD && !agg_pass) {
 #pragma unroll
                 for (int c = 0; c < NCH; ++c) {
                     const uint4 qx = *reinterpret_cast<const uint4 *>(stg + 2 * TB + (lane * NCH + c) * 16);
@@ -661,7 +672,14 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
             constexpr bool PACKED = !INTERIOR && sizeof(V) == 4 && (K % 2 == 0);
             constexpr int H = K / 2;
             constexpr int JF = REV ? K - 1 : 0;
-            V A, B, A0h = vone(V()), B0h = vzero(V());
+            V A0h = vone(V()), B0h = vzero(V());
+            V x = vzero(V());    // state entering this lane
+            V x2 = vzero(V());
+            if (use_prefix) {
+                const V pa = lane_prefix[(i * 32 + lane) * 2], pb = lane_prefix[(i * 32 + lane) * 2 + 1];
+                x = vfma(pa, lookback_x_in, pb);
+            } else {
+            V A, B;
             V B2 = vzero(V());
             if constexpr (PACKED) {
                 auto J = [](int q) { return REV ? K - 1 - q : q; };
@@ -711,19 +729,24 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
                 }
             }
             // state entering this lane = inclusive result of the previous lane
-            V x = REV ? shfl_down(B, 1) : shfl_up(B, 1);
+            x = REV ? shfl_down(B, 1) : shfl_up(B, 1);
             if (ll == 0) x = x_carry;
-            V x2 = vzero(V());
-            if (REDUCE && INTERIOR) {
+            if ((REDUCE && INTERIOR) || (agg_pass && keep_prefix)) {
                 x2 = REV ? shfl_down(B2, 1) : shfl_up(B2, 1);
                 if (ll == 0) x2 = x2_carry;
             }
+            if (agg_pass && keep_prefix) {
+                lane_prefix[(i * 32 + lane) * 2] = x2;
+                lane_prefix[(i * 32 + lane) * 2 + 1] = x;
+            }
             x_carry = shfl_idx(B, REV ? 0 : 31);
             if (unit_channel) x2_carry = shfl_idx(B2, REV ? 0 : 31);
+            }
 
             if (!REDUCE && !agg_pass) {
                 // ---- pass 2: the recurrence itself from the lane's incoming state
-                if constexpr (PACKED) {
+                if (PACKED && !use_prefix) {
+                  if constexpr (PACKED) {
                     auto J = [](int q) { return REV ? K - 1 - q : q; };
                     float2 Xv = make_float2(x, fmaf(A0h, x, B0h));   // states entering the two halves
 #pragma unroll
@@ -734,6 +757,7 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
                         b[J(q)] = Xv.x;
                         b[J(H + q)] = Xv.y;
                     }
+                  }
                 } else {
 #pragma unroll
                     for (int q = 0; q < K; ++q) {
