@@ -126,3 +126,27 @@ def test_small_workspace_steps_down_to_chained(cuda_device):
                                    ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     assert rc == 0
     assert rel_err(to_np(out2), want) <= 1e-5
+
+
+@pytest.mark.parametrize("lb_tiles", [4, 16])
+def test_lookback_with_other_segment_lengths(cuda_device, monkeypatch, lb_tiles):
+    """The look-back plan keeps per-lane prefixes for segments of up to 8 tiles; longer
+    segments (a sweep override) run the scan pass in full.  Both must agree with the oracle,
+    forward and backward."""
+    from accelerated_scan import _native
+
+    monkeypatch.setenv("ASCAN_LOOKBACK_TILES", str(lb_tiles))
+    rows, T = 5, 100000
+    assert _native.plan(rows, T, _native.F32, _native.KIND_FORWARD)["kernel"] == 1
+    gates, tokens, grad_out = real_inputs(33, (1, rows, T), law="near_one")
+    want = scan_oracle.scan(gates.numpy(), tokens.numpy())
+    want_dg, want_dx = scan_oracle.scan_backward(gates.numpy(), want, grad_out.numpy())
+    g, x, go = (t.to(cuda_device) for t in (gates, tokens, grad_out))
+    out = torch.empty_like(x)
+    _native.forward(g, x, out)
+    assert rel_err(to_np(out), want) <= 1e-5
+    dg, dx = torch.empty_like(x), torch.empty_like(x)
+    _native.backward(g, out, go, dg, dx)
+    assert rel_err(to_np(dx), want_dx) <= 1e-5
+    assert rel_err(to_np(dg), want_dg) <= 1e-5
+    _native.check_status(cuda_device)
