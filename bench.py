@@ -54,7 +54,14 @@ def parse_args():
     ap.add_argument("--e2e-slabs", type=int, default=16)
     ap.add_argument("--e2e-streams", type=int, default=4)
     ap.add_argument("--time-sharded-steps", type=int, default=5)
-    return ap.parse_args()
+    # other shapes for profiling runs (the contract's workload is the default (8, 1536, L));
+    # use with --no-sweep --no-also, which are written for the default shape
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--dim", type=int, default=1536)
+    args = ap.parse_args()
+    global B, C
+    B, C = args.batch, args.dim
+    return args
 
 
 def measured_peak():
