@@ -113,24 +113,46 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     // item, so that all warps work although only rows/G... teams can be busy at once.  G is
     // the smallest divisor of the warps per CTA with (warps / G) <= rows.
     int team = 1;
+    int team_wpc = kMaxWarpsPerCta;      // warps per CTA of a team plan
     const bool team_kind = scan_kind || in.dtype != ASCAN_C64;     // carry-only kinds: real dtypes
     if (!lookback && can_split && bulk && team_kind && in.allow_team && in.rows > 0 && in.rows < max_warps &&
         env_int("ASCAN_NO_TEAM", 0) == 0) {
-        const int64_t want = (max_warps + in.rows - 1) / in.rows;
-        for (int cand : {2, 3, 4, 6, 12}) {
-            if (cand >= want) {
-                team = cand;
-                break;
+        // The forward kinds need fewer registers and less shared memory per warp, so 16 warps
+        // fit in a CTA (teams of 2, 4, 8 or 16): with 12 the forward is bound by the time a warp
+        // needs per tile (4.4-5.4 TB/s at 150-800 rows), with 16 by HBM.
+        const bool wide_kind = in.kind == ASCAN_KIND_FORWARD || in.kind == ASCAN_KIND_REDUCE_FORWARD;
+        if (wide_kind && env_int("ASCAN_TEAM_WIDE", 1) != 0) {
+            const int64_t want16 = (static_cast<int64_t>(in.sm_count) * 16 + in.rows - 1) / in.rows;
+            for (int cand : {2, 4, 8, 16}) {
+                if (cand >= want16) {
+                    if (tiles_row >= 2 * cand) {       // else: rows too short for so wide a team
+                        team = cand;
+                        team_wpc = 16;
+                    }
+                    break;
+                }
             }
         }
-        if (team == 1) team = 12;
+        if (team == 1) {
+            const int64_t want = (max_warps + in.rows - 1) / in.rows;
+            for (int cand : {2, 3, 4, 6, 12}) {
+                if (cand >= want) {
+                    team = cand;
+                    break;
+                }
+            }
+            if (team == 1) team = 12;
+        }
         const int team_env = env_int("ASCAN_TEAM", 0);
-        if (team_env == 2 || team_env == 3 || team_env == 4 || team_env == 6 || team_env == 12) team = team_env;
+        if (team_env == 2 || team_env == 3 || team_env == 4 || team_env == 6 || team_env == 12) {
+            team = team_env;
+            team_wpc = kMaxWarpsPerCta;
+        }
         if (seg_tiles < 4 * team) seg_tiles = 4 * team;
         if (fine_tiles < 2 * team) fine_tiles = 2 * team;
         if (tiles_row < 2 * team) team = 1;           // rows too short to share
     }
-    const int64_t workers = max_warps / team;
+    const int64_t workers = static_cast<int64_t>(in.sm_count) * team_wpc / team;
     const int64_t split_min = lookback ? 2 * lb_tiles : (team > 1 ? 2 * fine_tiles : env_int("ASCAN_SPLIT_MIN_TILES", 32));
     if (can_split && tiles_row >= split_min && tiles_row >= 2 * fine_tiles) {
         int64_t fine_region = (static_cast<int64_t>(seg_tiles) * workers + in.rows - 1) / (in.rows > 0 ? in.rows : 1);
@@ -194,11 +216,11 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     // look-back kernels keep, per tile of a segment and lane, two values of the compute type
     // (must match lookback_prefix_bytes in stream.cuh)
     const int wsm = warp_smem(nch, pl.stages, in.kind, bulk) + (lookback ? 8 * 32 * 2 * (esize == 8 ? 8 : 4) : 0);
-    int wpc = (kMaxSmemPerCta - (team > 1 ? kMaxWarpsPerCta / team * 256 : 0)) / wsm;
+    int wpc = (kMaxSmemPerCta - (team > 1 ? team_wpc / team * kTeamSmemBytes : 0)) / wsm;
     // the stream kernels are compiled for 16 warps per CTA (14 for the fused backward, which
     // needs more registers); 14 measured best (more warps hide more of a tile's dependent
     // latency, 15-16 leave too few registers and shared memory per warp)
-    const int wpc_cap = team > 1 ? kMaxWarpsPerCta : ((in.kind == ASCAN_KIND_BACKWARD && nch > 2) ? 14 : 16);
+    const int wpc_cap = team > 1 ? team_wpc : ((in.kind == ASCAN_KIND_BACKWARD && nch > 2) ? 14 : 16);
     if (wpc > wpc_cap) wpc = wpc_cap;
     const int wpc_env = env_int("ASCAN_WPC", 0);
     if (wpc_env > 0 && wpc_env < wpc) wpc = wpc_env;
@@ -219,9 +241,13 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     }
     if (team > 1) {
         // whole teams only, one persistent CTA per SM
-        wpc = kMaxWarpsPerCta;
-        grid = in.sm_count;
-        if (pl.rows_per_item != 1 || static_cast<int64_t>(wpc) * wsm + wpc / team * 256 > kMaxSmemPerCta) team = 1;
+        if (pl.rows_per_item != 1 ||
+            static_cast<int64_t>(team_wpc) * wsm + team_wpc / team * kTeamSmemBytes > kMaxSmemPerCta) {
+            team = 1;              // does not fit (deep rings): the chained stream kernel, as planned above
+        } else {
+            wpc = team_wpc;
+            grid = in.sm_count;
+        }
     }
     // A problem of at most two items per warp gains nothing from tickets: deal statically and
     // save the ticket and exit-counter round trips (they are a fifth of a 15 us kernel).
@@ -232,7 +258,7 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     pl.team_size = team;
     pl.warps_per_cta = wpc;
     pl.grid = static_cast<int32_t>(grid);
-    pl.smem_bytes = static_cast<uint64_t>(wpc) * wsm + (team > 1 ? static_cast<uint64_t>(wpc / team) * 256 : 0);
+    pl.smem_bytes = static_cast<uint64_t>(wpc) * wsm + (team > 1 ? static_cast<uint64_t>(wpc / team) * kTeamSmemBytes : 0);
     pl.kernel = (lookback && pl.segs_per_row > 1) ? 1 : (team > 1 ? 2 : 0);
     pl.workspace_bytes = (!use_ws || !pl.dynamic) ? 0
                          : (pl.kernel == 1 ? static_cast<uint64_t>(kCtrlBytes) + static_cast<uint64_t>(in.rows) *

@@ -26,7 +26,7 @@
 
 namespace ascan {
 
-constexpr int TEAM_SMEM_BYTES = 256;          // per team: 12 mailboxes, ticket ring, abort flag
+constexpr int TEAM_SMEM_BYTES = 384;          // per team: 16 mailboxes of 16 bytes, ticket ring, abort flag
 constexpr uint32_t MAIL_WAIT_POLLS = 1u << 24;
 
 __host__ __device__ constexpr int team_stage_bytes(int nch, int kind) {
@@ -37,8 +37,9 @@ __host__ __device__ constexpr int team_warp_smem(int nch, int stages, int kind) 
     return stages * team_stage_bytes(nch, kind) + 2 * stream_nout(kind) * tb + 128;
 }
 
+// (the forward kinds run with up to 16 warps per CTA, the backward kinds with 12)
 template <class TR, int NCH, int KIND, bool REVERSE>
-__global__ void __launch_bounds__(384, 1) team_kernel(const StreamParams p) {
+__global__ void __launch_bounds__((KIND == K_BWD || KIND == K_REDUCE_BWD) ? 384 : 512, 1) team_kernel(const StreamParams p) {
     using V = typename TR::V;
     constexpr int EPC = TR::EPC;
     constexpr int K = NCH * EPC;
@@ -71,8 +72,8 @@ __global__ void __launch_bounds__(384, 1) team_kernel(const StreamParams p) {
     volatile uint32_t *mail_seq = reinterpret_cast<volatile uint32_t *>(tsm);          // [g*4]
     volatile float *mail_val = reinterpret_cast<volatile float *>(tsm);                // [g*4 + 2], [g*4 + 3]
     volatile unsigned long long *mail_word = reinterpret_cast<volatile unsigned long long *>(tsm);   // [g*2], real types
-    volatile unsigned long long *tix = reinterpret_cast<volatile unsigned long long *>(tsm + 192);   // ring of 4
-    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(tsm + 224);
+    volatile unsigned long long *tix = reinterpret_cast<volatile unsigned long long *>(tsm + 256);   // ring of 4
+    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(tsm + 288);
 
     const int64_t W = static_cast<int64_t>(gridDim.x) * wpc;
     const int64_t T = p.T;

@@ -67,8 +67,8 @@ def test_planner_invariants(T, dtype, kind):
             assert pl["segs_per_row"] == 1 and pl["kernel"] == 0 and pl["workspace_bytes"] == 0
             assert pl["items"] <= 2 * pl["grid"] * pl["warps_per_cta"]
         elif pl["kernel"] == 1:
-            # look-back plan: fewer rows than SMs, per-(row, segment) records, equal small segments
-            assert rows < 148 and kind in (0, 1) and pl["segs_per_row"] > 1
+            # look-back plan: fewer rows than 3/4 of the SMs, per-(row, segment) records, equal small segments
+            assert rows < 111 and kind in (0, 1) and pl["segs_per_row"] > 1
             assert pl["workspace_bytes"] == 256 + 64 * rows * pl["segs_per_row"]
             assert pl["seg_elems"] == pl["fine_elems"]
             chained = _native.plan(rows, T, dtype, kind, sm_count=148, lookback=False, team=False)
@@ -78,9 +78,14 @@ def test_planner_invariants(T, dtype, kind):
         if pl["kernel"] == 2:
             # team plan: fewer rows than warps, whole teams per CTA, rows never grouped
             assert rows < 148 * 12 and (kind in (0, 1) or dtype != _native.C64) and pl["loader"] == 0
-            assert pl["team_size"] in (2, 3, 4, 6, 12) and pl["warps_per_cta"] % pl["team_size"] == 0
+            # 16 warps per CTA for the forward kinds, 12 for the backward kinds
+            wide = pl["warps_per_cta"] == 16
+            assert kind in (0, 2) or not wide
+            assert pl["team_size"] in ((2, 4, 8, 16) if wide else (2, 3, 4, 6, 12))
+            assert pl["warps_per_cta"] % pl["team_size"] == 0
             assert pl["rows_per_item"] == 1 and pl["grid"] == 148
-            assert (148 * 12) // pl["team_size"] <= max(rows, 148) or pl["team_size"] == 12
+            per_cta = pl["warps_per_cta"]
+            assert (148 * per_cta) // pl["team_size"] <= max(rows, 148) or pl["team_size"] == per_cta
         else:
             assert pl["team_size"] == 1
         if pl["segs_per_row"] > 1:

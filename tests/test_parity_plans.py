@@ -25,22 +25,23 @@ def _up(t):
     return t.numpy() if t.dtype in (torch.float32, torch.complex64) else t.float().numpy()
 
 
-# rows, seqlen, expected plan kernel (0 stream, 1 look-back, 2 team), expected team size (0 = any)
+# rows, seqlen, expected plan kernel (0 stream, 1 look-back, 2 team), expected team size of the
+# backward (12 warps per CTA) and of the forward (16 warps per CTA)
 CASES = [
-    (2000, 8192, 0, 1),       # more rows than warps: chained stream kernel
-    (1024, 16384, 2, 2),      # config-5-like: two warps per item
-    (700, 9000, 2, 3),
-    (450, 12288, 2, 4),
-    (300, 20000, 2, 6),
-    (160, 33000, 2, 12),
-    (100, 50000, 1, 1),       # fewer rows than SMs: look-back
-    (3, 400000, 1, 1),
+    (2000, 8192, 0, 1, 1),       # more rows than warps: chained stream kernel
+    (1024, 16384, 2, 2, 4),      # config-5-like
+    (700, 9000, 2, 3, 4),
+    (450, 12288, 2, 4, 8),
+    (300, 20000, 2, 6, 8),
+    (160, 33000, 2, 12, 16),
+    (100, 50000, 1, 1, 1),       # clearly fewer rows than SMs: look-back
+    (3, 400000, 1, 1, 1),
 ]
 
 
-@pytest.mark.parametrize("rows,seqlen,kernel,team", CASES)
+@pytest.mark.parametrize("rows,seqlen,kernel,team,team_fwd", CASES)
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.complex64])
-def test_plan_parity(cuda_device, rows, seqlen, kernel, team, dtype):
+def test_plan_parity(cuda_device, rows, seqlen, kernel, team, team_fwd, dtype):
     from accelerated_scan import _native
 
     if dtype == torch.complex64:
@@ -49,7 +50,9 @@ def test_plan_parity(cuda_device, rows, seqlen, kernel, team, dtype):
     for kind in (_native.KIND_FORWARD, _native.KIND_BACKWARD):
         pl = _native.plan(rows, seqlen, code, kind)
         assert pl["kernel"] == kernel, pl
-        assert pl["team_size"] == team, pl
+        assert pl["team_size"] == (team_fwd if kind == _native.KIND_FORWARD else team), pl
+        if kernel == 2:
+            assert pl["warps_per_cta"] == (16 if kind == _native.KIND_FORWARD else 12), pl
     shape = (1, rows, seqlen)
     gates, tokens, grad_out = _inputs(dtype, shape)
     want = scan_oracle.scan(_up(gates), _up(tokens))
