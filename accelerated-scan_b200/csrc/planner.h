@@ -11,7 +11,7 @@
 namespace ascan {
 
 constexpr int kMaxSmemPerCta = 227 * 1024;   // opt-in dynamic shared memory per CTA on sm_100
-constexpr int kMaxWarpsPerCta = 12;          // kernels are compiled for at most 384 threads per CTA
+constexpr int kMaxWarpsPerCta = 12;          // warps per CTA of the kernels for grouped rows and of the backward team kernels
 constexpr int kTeamSmemBytes = 384;          // shared memory per team of the team kernel (TEAM_SMEM_BYTES)
 constexpr int kCtrlBytes = 256;              // control block at the start of a workspace
 constexpr int kCarryRecordBytes = 32;        // per-row carry record behind it
