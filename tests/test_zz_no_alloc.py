@@ -22,7 +22,7 @@ def _ptr(t):
     return ctypes.c_void_p(t.data_ptr())
 
 
-@pytest.mark.parametrize("shape,dtype", [((2, 32, 65536), torch.float32), ((1, 48, 40000), torch.bfloat16)])
+@pytest.mark.parametrize("shape,dtype", [((2, 32, 65536), torch.float32), ((1, 48, 160000), torch.bfloat16)])
 def test_no_alloc_matches_workspace_entry_point(cuda_device, shape, dtype):
     from accelerated_scan import _native
 
