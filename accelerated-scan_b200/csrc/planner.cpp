@@ -55,7 +55,11 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     // 16-bit dtypes in the plain stream plan: 24 elements x 3 streams per lane leave too few
     // registers, and 2 chunks (16 elements) measured 2-6 % faster there despite 2-way conflicts.
     const int64_t stream_warps = static_cast<int64_t>(in.sm_count) * kMaxWarpsPerCta;
-    const int nch = (in.kind == ASCAN_KIND_BACKWARD && esize == 2 && in.rows >= stream_warps &&
+    // Teams take over below two rows per warp: near one row per warp the chained stream plan has
+    // every segment of a row in flight right behind the one before it, so carries are waited
+    // for (fp32, 1800-3000 rows of 65536: stream 6.0-6.3 TB/s, teams of two 6.3-6.5).
+    const int64_t team_rows = env_int("ASCAN_TEAM_ROWS", static_cast<int>(2 * stream_warps));
+    const int nch = (in.kind == ASCAN_KIND_BACKWARD && esize == 2 && in.rows >= team_rows &&
                      env_int("ASCAN_NCH3_ONLY", 0) == 0)
                         ? 2
                         : 3;
@@ -115,7 +119,7 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     int team = 1;
     int team_wpc = kMaxWarpsPerCta;      // warps per CTA of a team plan
     const bool team_kind = scan_kind || in.dtype != ASCAN_C64;     // carry-only kinds: real dtypes
-    if (!lookback && can_split && bulk && team_kind && in.allow_team && in.rows > 0 && in.rows < max_warps &&
+    if (!lookback && can_split && bulk && team_kind && in.allow_team && in.rows > 0 && in.rows < team_rows &&
         env_int("ASCAN_NO_TEAM", 0) == 0) {
         // The forward kinds need fewer registers and less shared memory per warp, so 16 warps
         // fit in a CTA (teams of 2, 4, 8 or 16): with 12 the forward is bound by the time a warp

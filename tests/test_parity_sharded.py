@@ -95,7 +95,7 @@ def test_emulated_time_shards(cuda_device, world, seqlen, dtype):
     np.testing.assert_allclose(to_np(P[0]).astype(prod.dtype), prod, rtol=2e-4, atol=1e-30)
 
 
-@pytest.mark.parametrize("rows,seqlen", [(300, 24576), (1024, 6000), (2000, 4608)])
+@pytest.mark.parametrize("rows,seqlen", [(300, 24576), (1024, 6000), (2000, 9216), (3700, 3072)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_emulated_time_shards_many_rows(cuda_device, rows, seqlen, dtype):
     """The same with row counts that take the team plan (carry-only kinds included) and the
@@ -104,7 +104,7 @@ def test_emulated_time_shards_many_rows(cuda_device, rows, seqlen, dtype):
 
     world = 2
     code = _native.DTYPE_CODE[dtype]
-    expect = 2 if rows < 148 * 12 else 0
+    expect = 2 if rows < 2 * 148 * 12 else 0
     assert _native.plan(rows, seqlen // world, code, _native.KIND_REDUCE_FORWARD)["kernel"] == expect
     assert _native.plan(rows, seqlen // world, code, _native.KIND_REDUCE_BACKWARD)["kernel"] == expect
     shape = (1, rows, seqlen)
@@ -117,7 +117,9 @@ def test_emulated_time_shards_many_rows(cuda_device, rows, seqlen, dtype):
     saved = to_np(states) if dtype == torch.bfloat16 else want
     want_dg, want_dx = scan_oracle.scan_backward(up(gates), saved, up(grad_out))
     assert rel_err(to_np(d_tokens), want_dx) <= tol
-    assert rel_err(to_np(d_gates), want_dg) <= tol
+    # bf16: at a shard boundary d_gates uses the incoming state in fp32 (the folded carry), the
+    # oracle the saved state rounded to bf16: one more half-ulp on that element
+    assert rel_err(to_np(d_gates), want_dg) <= (2 * tol if dtype == torch.bfloat16 else tol)
     _native.check_status(cuda_device)
 
 
