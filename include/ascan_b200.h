@@ -58,7 +58,7 @@ typedef enum {
  * of warp.cuh:282-380.  Pure host arithmetic, usable without a GPU when
  * sm_count > 0 is passed. */
 typedef struct {
-    int32_t kernel;            /* 0 = stream: one warp per item, segments of a row chained; 1 = look-back (very few rows: segments of a row scanned concurrently); 2 = team (fewer rows than warps: several warps share an item) */
+    int32_t kernel;            /* 0 = stream: one warp per item, segments of a row chained; 1 = look-back (very few rows: segments of a row scanned concurrently); 2 = team (fewer than two rows per warp: several warps share an item) */
     int32_t loader;            /* 0 = bulk-async copies into shared-memory stages, 1 = plain element loads (unaligned data) */
     int32_t chunks_per_lane;   /* 16-byte chunks each lane owns per tile                  */
     int32_t stages;            /* shared-memory stages per warp                            */
@@ -200,7 +200,7 @@ int ascan_fold_carries(const void *gathered, int64_t rows, int world, int rank,
 /*
  * Scratch bytes a call of `kind` with these sizes can use: a control block
  * (status word, work ticket) plus one carry record per row, or per (row, segment)
- * when the look-back plan applies (fewer rows than warps).  With that much scratch
+ * when the look-back plan applies (clearly fewer rows than SMs).  With that much scratch
  * the kernels balance work over the SMs dynamically and split long rows across
  * warps and CTAs; with less they step down to the chained plan (256 + 32*rows
  * bytes), and with none (NULL) to a static deal of whole rows: correct, slower.
