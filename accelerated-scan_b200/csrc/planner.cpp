@@ -59,7 +59,7 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     // every segment of a row in flight right behind the one before it, so carries are waited
     // for (fp32, 1800-3000 rows of 65536: stream 6.0-6.3 TB/s, teams of two 6.3-6.5).
     const int64_t team_rows = env_int("ASCAN_TEAM_ROWS", static_cast<int>(2 * stream_warps));
-    const int nch = (in.kind == ASCAN_KIND_BACKWARD && esize == 2 && in.rows >= team_rows &&
+    const int nch = (in.kind == ASCAN_KIND_BACKWARD && esize == 2 && in.rows >= team_rows && !in.three_chunks &&
                      env_int("ASCAN_NCH3_ONLY", 0) == 0)
                         ? 2
                         : 3;

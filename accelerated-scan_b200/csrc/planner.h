@@ -26,6 +26,7 @@ struct PlanInput {
     bool workspace;   // a workspace of the plan's workspace_bytes is available
     bool allow_lookback = true;   // false: never choose the look-back plan (smaller workspace)
     bool allow_team = true;       // false: never choose the team plan
+    bool three_chunks = false;    // true: always 3 chunks per lane (variants without a 2-chunk kernel)
     int sm_count;
 };
 
