@@ -55,10 +55,13 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     // 16-bit dtypes in the plain stream plan: 24 elements x 3 streams per lane leave too few
     // registers, and 2 chunks (16 elements) measured 2-6 % faster there despite 2-way conflicts.
     const int64_t stream_warps = static_cast<int64_t>(in.sm_count) * kMaxWarpsPerCta;
-    // Teams take over below two rows per warp: near one row per warp the chained stream plan has
-    // every segment of a row in flight right behind the one before it, so carries are waited
-    // for (fp32, 1800-3000 rows of 65536: stream 6.0-6.3 TB/s, teams of two 6.3-6.5).
-    const int64_t team_rows = env_int("ASCAN_TEAM_ROWS", static_cast<int>(2 * stream_warps));
+    // Teams take over below four rows per warp: with few rows per warp the chained stream plan
+    // has every segment of a row in flight right behind the one before it, so carries are
+    // waited for (fp32, 1800-3000 rows of 65536: stream 6.0-6.3 TB/s, teams of two 6.3-6.5;
+    // 4096-6000 rows of 8192: 5.3-5.6 against 5.7-6.3).  Above two rows per warp only for rows
+    // long enough to be split (whole short rows run better one warp each); from 8000 rows on
+    // the stream plan is ahead again.
+    const int64_t team_rows = env_int("ASCAN_TEAM_ROWS", static_cast<int>(4 * stream_warps));
     const int nch = (in.kind == ASCAN_KIND_BACKWARD && esize == 2 && in.rows >= team_rows && !in.three_chunks &&
                      env_int("ASCAN_NCH3_ONLY", 0) == 0)
                         ? 2
@@ -155,9 +158,15 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
         // eight tiles per warp and coarse item, four per fine item: the team's barrier and
         // ticket hand-over per item cost about a tile (4 and 2 per warp measured 10 % slower
         // for teams of 16)
+        const int seg_tiles_single = seg_tiles, fine_tiles_single = fine_tiles;
         if (seg_tiles < 8 * team) seg_tiles = 8 * team;
         if (fine_tiles < 4 * team) fine_tiles = 4 * team;
         if (tiles_row < 2 * team) team = 1;           // rows too short to share
+        if (in.rows >= 2 * stream_warps && tiles_row < 2 * fine_tiles) team = 1;   // whole short rows: one warp each
+        if (team == 1) {
+            seg_tiles = seg_tiles_single;
+            fine_tiles = fine_tiles_single;
+        }
     }
     const int64_t workers = static_cast<int64_t>(in.sm_count) * team_wpc / team;
     const int64_t split_min = lookback ? 2 * lb_tiles : (team > 1 ? 2 * fine_tiles : env_int("ASCAN_SPLIT_MIN_TILES", 32));

@@ -58,7 +58,7 @@ typedef enum {
  * of warp.cuh:282-380.  Pure host arithmetic, usable without a GPU when
  * sm_count > 0 is passed. */
 typedef struct {
-    int32_t kernel;            /* 0 = stream: one warp per item, segments of a row chained; 1 = look-back (very few rows: segments of a row scanned concurrently); 2 = team (fewer than two rows per warp: several warps share an item) */
+    int32_t kernel;            /* 0 = stream: one warp per item, segments of a row chained; 1 = look-back (very few rows: segments of a row scanned concurrently); 2 = team (fewer than four rows per warp: several warps share an item) */
     int32_t loader;            /* 0 = bulk-async copies into shared-memory stages, 1 = plain element loads (unaligned data) */
     int32_t chunks_per_lane;   /* 16-byte chunks each lane owns per tile                  */
     int32_t stages;            /* shared-memory stages per warp                            */

@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 def test_expired_wait_is_reported_and_context_survives(cuda_device):
     from accelerated_scan import _native
 
-    rows, T = 3600, 20000          # chained stream plan: more than two rows per warp, several segments per row
+    rows, T = 7200, 16000          # chained stream plan: more than four rows per warp, several segments per row
     pl = _native.plan(rows, T, _native.F32, _native.KIND_FORWARD)
     assert pl["kernel"] == 0 and pl["segs_per_row"] > 1 and pl["dynamic"] == 1
     gates, tokens, _ = real_inputs(2, (1, rows, T), grad=False)

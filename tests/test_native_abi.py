@@ -52,7 +52,7 @@ def test_bad_arguments_rejected_without_gpu():
 @pytest.mark.parametrize("kind", [0, 1, 2, 3])
 def test_planner_invariants(T, dtype, kind):
     esize = {0: 4, 1: 2, 2: 2, 3: 8}[dtype]
-    for rows in (1, 16, 512, 2500, 12288):
+    for rows in (1, 16, 512, 2500, 5000, 12288):
         pl = _native.plan(rows, T, dtype, kind, aligned=True, sm_count=148)
         assert pl["grid"] >= 1 and pl["warps_per_cta"] >= 1
         assert pl["warps_per_cta"] * 32 <= (448 if kind == 1 else 512)
@@ -77,7 +77,7 @@ def test_planner_invariants(T, dtype, kind):
             assert pl["workspace_bytes"] == 256 + 32 * rows
         if pl["kernel"] == 2:
             # team plan: fewer rows than warps, whole teams per CTA, rows never grouped
-            assert rows < 2 * 148 * 12 and (kind in (0, 1) or dtype != _native.C64) and pl["loader"] == 0
+            assert rows < 4 * 148 * 12 and (kind in (0, 1) or dtype != _native.C64) and pl["loader"] == 0
             # 16 warps per CTA for the forward kinds, 12 for the backward kinds
             wide = pl["warps_per_cta"] == 16
             assert kind in (0, 2) or not wide

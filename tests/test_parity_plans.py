@@ -28,7 +28,8 @@ def _up(t):
 # rows, seqlen, expected plan kernel (0 stream, 1 look-back, 2 team), expected team size of the
 # backward (12 warps per CTA) and of the forward (16 warps per CTA)
 CASES = [
-    (4000, 8192, 0, 1, 1),       # more than two rows per warp: chained stream kernel
+    (7200, 13000, 0, 1, 1),      # more than four rows per warp: chained stream kernel
+    (4000, 16384, 2, 2, 2),      # two to four rows per warp, rows long enough to split: teams of two
     (2000, 8192, 2, 2, 2),       # about one row per warp: teams of two
     (1024, 16384, 2, 2, 4),      # config-5-like
     (700, 9000, 2, 3, 4),
@@ -74,7 +75,7 @@ def test_plan_parity(cuda_device, rows, seqlen, kernel, team, team_fwd, dtype):
     _native.check_status(cuda_device)
 
 
-@pytest.mark.parametrize("rows,seqlen", [(1024, 12000), (300, 20000), (100, 30000), (2000, 6000), (4000, 6000)])
+@pytest.mark.parametrize("rows,seqlen", [(1024, 12000), (300, 20000), (100, 30000), (2000, 6000), (7200, 6000)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.complex64])
 def test_plan_seeded_forms(cuda_device, rows, seqlen, dtype):
     """carry_in, halo_gate_right and halo_state_left under every plan: scanning the second
