@@ -7,6 +7,7 @@ missing, importing this module raises.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import os
 
@@ -79,6 +80,12 @@ def _load():
     lib.ascan_backward_sigmoid_gates.argtypes = [vp, vp, vp, vp, vp, i64, i64, i32, vp, sz, vp]
     lib.ascan_forward_no_alloc.restype = i32
     lib.ascan_forward_no_alloc.argtypes = [vp, vp, vp, i64, i64, i32, i32, vp]
+    lib.ascan_check_no_alloc.restype = i32
+    lib.ascan_check_no_alloc.argtypes = [vp]
+    lib.ascan_set_option.restype = i32
+    lib.ascan_set_option.argtypes = [i32, i32]
+    lib.ascan_get_option.restype = i32
+    lib.ascan_get_option.argtypes = [i32]
     return lib
 
 
@@ -89,7 +96,10 @@ EXPORTS = (
     "ascan_reduce_backward", "ascan_workspace_bytes", "ascan_plan_describe", "ascan_check",
     "ascan_forward_no_alloc", "ascan_fold_carries", "ascan_forward_complex_real_tokens",
     "ascan_forward_sigmoid_gates", "ascan_backward_sigmoid_gates", "ascan_backward_complex_real_tokens",
+    "ascan_check_no_alloc", "ascan_set_option", "ascan_get_option",
 )
+
+OPT_STAGES, OPT_WARPS_PER_CTA, OPT_LOOKBACK_TILES, OPT_DISABLE_PLANS, OPT_TEST_DROP_CARRY, OPT_TEST_EPOCH_BITS = range(6)
 
 
 def strerror(code: int) -> str:
@@ -103,6 +113,26 @@ def check(code: int, what: str) -> None:
         raise RuntimeError(f"{what}: {strerror(code)} (ascan status {code})")
 
 
+def set_option(option: int, value: int) -> None:
+    check(lib.ascan_set_option(int(option), int(value)), "ascan_set_option")
+
+
+def get_option(option: int) -> int:
+    return int(lib.ascan_get_option(int(option)))
+
+
+# Debug mode: synchronise after every launch and raise if a bounded device-side wait
+# expired in it (the reference raises on every failure, warp.cuh:396-421).  Off by
+# default, because the hot path must not synchronise; without it a failure is still
+# reported, one call late: see Workspace.raise_if_failed.
+_debug = os.environ.get("ASCAN_CHECK", "") not in ("", "0")
+
+
+def set_debug(on: bool) -> None:
+    global _debug
+    _debug = bool(on)
+
+
 def dtype_code(t: torch.Tensor) -> int:
     try:
         return DTYPE_CODE[t.dtype]
@@ -111,11 +141,7 @@ def dtype_code(t: torch.Tensor) -> int:
 
 
 def _ptr(t):
-    return None if t is None else ctypes.c_void_p(t.data_ptr())
-
-
-def _stream(t: torch.Tensor):
-    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+    return None if t is None else t.data_ptr()
 
 
 def _require_cuda(*tensors):
@@ -124,22 +150,81 @@ def _require_cuda(*tensors):
             raise RuntimeError("accelerated_scan runs on CUDA tensors only (no CPU path)")
 
 
+def _rows_T(t):
+    T = t.shape[-1]
+    return (t.numel() // T if T else 0), T
+
+
+_NULL_GUARD = contextlib.nullcontext()
+
+
+def _device_guard(device):
+    """The C ABI works on the current device: switch only when the tensors live elsewhere."""
+    return _NULL_GUARD if torch.cuda.current_device() == device.index else torch.cuda.device(device)
+
+
+class Workspace:
+    """Scratch of one (device, stream), owned by torch's allocator and zero-filled once
+    when it is created (the kernels rearm it themselves).  It holds the status word, the
+    work ticket and the carry records; launches on different streams get different
+    workspaces because they may overlap.  A word of pinned host memory is registered in
+    the control block as second status word: a kernel whose bounded wait expires writes
+    there too, so the failure is seen by a plain host read at the next call."""
+
+    def __init__(self, device, nbytes):
+        self.tensor = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        self.nbytes = nbytes
+        self.ptr = self.tensor.data_ptr()
+        self.sink = torch.zeros(4, dtype=torch.int32).pin_memory()
+        self.sink_np = self.sink.numpy()
+        self.tensor[16:24] = torch.tensor([self.sink.data_ptr()], dtype=torch.int64).view(torch.uint8).to(device)
+
+    def raise_if_failed(self):
+        if self.sink_np[0]:
+            self.sink_np[0] = 0
+            raise RuntimeError("accelerated_scan: a bounded device-side wait expired in an earlier launch on this "
+                               "stream; its result is invalid (ascan status 4)")
+
+
 _workspaces = {}
+_needs = {}
+
+
+def _workspace(device, stream, rows, seqlen, dtype, kind) -> Workspace:
+    key = (rows, seqlen, dtype, kind)
+    nbytes = _needs.get(key)
+    if nbytes is None:
+        nbytes = int(lib.ascan_workspace_bytes(rows, seqlen, dtype, kind))
+        if len(_needs) > 4096:
+            _needs.clear()
+        _needs[key] = nbytes
+    wkey = (device.index, stream)
+    ws = _workspaces.get(wkey)
+    if ws is None or ws.nbytes < nbytes:
+        ws = Workspace(device, max(4096, 2 * nbytes))
+        _workspaces[wkey] = ws
+    ws.raise_if_failed()
+    return ws
 
 
 def workspace(device: torch.device, rows: int = 0, seqlen: int = 1, dtype: int = 0, kind: int = 0) -> torch.Tensor:
-    """Scratch per (device, stream), owned by torch's allocator and zero-filled once
-    when it is created (the kernels rearm it themselves).  It holds the status word,
-    the work ticket and one carry record per row; launches on different streams get
-    different workspaces because they may overlap."""
-    nbytes = int(lib.ascan_workspace_bytes(int(rows), int(seqlen), int(dtype), int(kind)))
+    """The scratch tensor launches on the current stream of `device` use (see Workspace)."""
+    device = torch.device(device)
     stream = torch.cuda.current_stream(device).cuda_stream
-    key = (device.index, stream)
-    ws = _workspaces.get(key)
-    if ws is None or ws.numel() < nbytes:
-        ws = torch.zeros(max(4096, 2 * nbytes), dtype=torch.uint8, device=device)
-        _workspaces[key] = ws
-    return ws
+    return _workspace(device, stream, int(rows), int(seqlen), int(dtype), int(kind)).tensor
+
+
+launch_count = 0       # kernels launched through this module (every successful call is one launch)
+
+
+def _finish(rc, what, ws, stream):
+    global launch_count
+    check(rc, what)
+    launch_count += 1
+    if _debug:
+        rc = lib.ascan_check(ws.ptr, stream)
+        ws.sink_np[0] = 0
+        check(rc, what)
 
 
 def plan(rows: int, seqlen: int, dtype: int, kind: int, aligned: bool = True, workspace: bool = True,
@@ -154,13 +239,15 @@ def plan(rows: int, seqlen: int, dtype: int, kind: int, aligned: bool = True, wo
 
 def forward(gates, tokens, out, reverse=False, carry_in=None):
     _require_cuda(gates, tokens, out, carry_in)
-    rows = gates.numel() // gates.shape[-1] if gates.shape[-1] else 0
-    T = gates.shape[-1]
-    with torch.cuda.device(gates.device):
-        ws = workspace(gates.device, rows, T, dtype_code(gates), KIND_FORWARD)
-        rc = lib.ascan_forward(_ptr(gates), _ptr(tokens), _ptr(out), rows, T, dtype_code(gates), int(bool(reverse)),
-                               _ptr(carry_in), _ptr(ws), ws.numel(), _stream(gates))
-    check(rc, "ascan_forward")
+    rows, T = _rows_T(gates)
+    code = dtype_code(gates)
+    dev = gates.device
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    ws = _workspace(dev, stream, rows, T, code, KIND_FORWARD)
+    with _device_guard(dev):
+        rc = lib.ascan_forward(gates.data_ptr(), tokens.data_ptr(), out.data_ptr(), rows, T, code, int(bool(reverse)),
+                               _ptr(carry_in), ws.ptr, ws.nbytes, stream)
+    _finish(rc, "ascan_forward", ws, stream)
 
 
 UNSUPPORTED = 2
@@ -171,15 +258,16 @@ def forward_complex_real_tokens(gates, tokens_real, out, reverse=False) -> bool:
     when the library has no fused kernel for this shape or alignment (the caller then promotes
     the tokens to complex and calls `forward`)."""
     _require_cuda(gates, tokens_real, out)
-    rows = gates.numel() // gates.shape[-1] if gates.shape[-1] else 0
-    T = gates.shape[-1]
-    with torch.cuda.device(gates.device):
-        ws = workspace(gates.device, rows, T, C64, KIND_FORWARD)
-        rc = lib.ascan_forward_complex_real_tokens(_ptr(gates), _ptr(tokens_real), _ptr(out), rows, T,
-                                                   int(bool(reverse)), _ptr(ws), ws.numel(), _stream(gates))
+    rows, T = _rows_T(gates)
+    dev = gates.device
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    ws = _workspace(dev, stream, rows, T, C64, KIND_FORWARD)
+    with _device_guard(dev):
+        rc = lib.ascan_forward_complex_real_tokens(gates.data_ptr(), tokens_real.data_ptr(), out.data_ptr(), rows, T,
+                                                   int(bool(reverse)), ws.ptr, ws.nbytes, stream)
     if rc == UNSUPPORTED:
         return False
-    check(rc, "ascan_forward_complex_real_tokens")
+    _finish(rc, "ascan_forward_complex_real_tokens", ws, stream)
     return True
 
 
@@ -187,15 +275,17 @@ def backward_complex_real_tokens(gates, states, grad_out, d_gates, d_tokens_real
     """Fused complex backward that writes only the real part of the token gradient (float32).
     Returns False when the library has no fused kernel for this shape or alignment."""
     _require_cuda(gates, states, grad_out, d_gates, d_tokens_real)
-    rows = gates.numel() // gates.shape[-1] if gates.shape[-1] else 0
-    T = gates.shape[-1]
-    with torch.cuda.device(gates.device):
-        ws = workspace(gates.device, rows, T, C64, KIND_BACKWARD)
-        rc = lib.ascan_backward_complex_real_tokens(_ptr(gates), _ptr(states), _ptr(grad_out), _ptr(d_gates),
-                                                    _ptr(d_tokens_real), rows, T, _ptr(ws), ws.numel(), _stream(gates))
+    rows, T = _rows_T(gates)
+    dev = gates.device
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    ws = _workspace(dev, stream, rows, T, C64, KIND_BACKWARD)
+    with _device_guard(dev):
+        rc = lib.ascan_backward_complex_real_tokens(gates.data_ptr(), states.data_ptr(), grad_out.data_ptr(),
+                                                    d_gates.data_ptr(), d_tokens_real.data_ptr(), rows, T, ws.ptr,
+                                                    ws.nbytes, stream)
     if rc == UNSUPPORTED:
         return False
-    check(rc, "ascan_backward_complex_real_tokens")
+    _finish(rc, "ascan_backward_complex_real_tokens", ws, stream)
     return True
 
 
@@ -203,64 +293,76 @@ def forward_sigmoid_gates(gate_logits, tokens, out) -> bool:
     """out[t] = sigmoid(gate_logits[t]) * out[t-1] + tokens[t].  Returns False when the library
     has no fused kernel for this shape or alignment (the caller applies the sigmoid itself)."""
     _require_cuda(gate_logits, tokens, out)
-    rows = gate_logits.numel() // gate_logits.shape[-1] if gate_logits.shape[-1] else 0
-    T = gate_logits.shape[-1]
-    with torch.cuda.device(gate_logits.device):
-        ws = workspace(gate_logits.device, rows, T, dtype_code(gate_logits), KIND_FORWARD)
-        rc = lib.ascan_forward_sigmoid_gates(_ptr(gate_logits), _ptr(tokens), _ptr(out), rows, T,
-                                             dtype_code(gate_logits), _ptr(ws), ws.numel(), _stream(gate_logits))
+    rows, T = _rows_T(gate_logits)
+    code = dtype_code(gate_logits)
+    dev = gate_logits.device
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    ws = _workspace(dev, stream, rows, T, code, KIND_FORWARD)
+    with _device_guard(dev):
+        rc = lib.ascan_forward_sigmoid_gates(gate_logits.data_ptr(), tokens.data_ptr(), out.data_ptr(), rows, T, code,
+                                             ws.ptr, ws.nbytes, stream)
     if rc == UNSUPPORTED:
         return False
-    check(rc, "ascan_forward_sigmoid_gates")
+    _finish(rc, "ascan_forward_sigmoid_gates", ws, stream)
     return True
 
 
 def backward_sigmoid_gates(gate_logits, states, grad_out, d_logits, d_tokens) -> bool:
     """Fused backward of `forward_sigmoid_gates`: d_logits and d_tokens.  False when unsupported."""
     _require_cuda(gate_logits, states, grad_out, d_logits, d_tokens)
-    rows = gate_logits.numel() // gate_logits.shape[-1] if gate_logits.shape[-1] else 0
-    T = gate_logits.shape[-1]
-    with torch.cuda.device(gate_logits.device):
-        ws = workspace(gate_logits.device, rows, T, dtype_code(gate_logits), KIND_BACKWARD)
-        rc = lib.ascan_backward_sigmoid_gates(_ptr(gate_logits), _ptr(states), _ptr(grad_out), _ptr(d_logits),
-                                              _ptr(d_tokens), rows, T, dtype_code(gate_logits), _ptr(ws), ws.numel(),
-                                              _stream(gate_logits))
+    rows, T = _rows_T(gate_logits)
+    code = dtype_code(gate_logits)
+    dev = gate_logits.device
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    ws = _workspace(dev, stream, rows, T, code, KIND_BACKWARD)
+    with _device_guard(dev):
+        rc = lib.ascan_backward_sigmoid_gates(gate_logits.data_ptr(), states.data_ptr(), grad_out.data_ptr(),
+                                              d_logits.data_ptr(), d_tokens.data_ptr(), rows, T, code, ws.ptr,
+                                              ws.nbytes, stream)
     if rc == UNSUPPORTED:
         return False
-    check(rc, "ascan_backward_sigmoid_gates")
+    _finish(rc, "ascan_backward_sigmoid_gates", ws, stream)
     return True
 
 
 def backward(gates, states, grad_out, d_gates, d_tokens, carry_in=None, halo_gate_right=None, halo_state_left=None):
     _require_cuda(gates, states, grad_out, d_gates, d_tokens, carry_in, halo_gate_right, halo_state_left)
-    rows = gates.numel() // gates.shape[-1] if gates.shape[-1] else 0
-    T = gates.shape[-1]
-    with torch.cuda.device(gates.device):
-        ws = workspace(gates.device, rows, T, dtype_code(gates), KIND_BACKWARD)
-        rc = lib.ascan_backward(_ptr(gates), _ptr(states), _ptr(grad_out), _ptr(d_gates), _ptr(d_tokens), rows, T,
-                                dtype_code(gates), _ptr(carry_in), _ptr(halo_gate_right), _ptr(halo_state_left),
-                                _ptr(ws), ws.numel(), _stream(gates))
-    check(rc, "ascan_backward")
+    rows, T = _rows_T(gates)
+    code = dtype_code(gates)
+    dev = gates.device
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    ws = _workspace(dev, stream, rows, T, code, KIND_BACKWARD)
+    with _device_guard(dev):
+        rc = lib.ascan_backward(gates.data_ptr(), states.data_ptr(), grad_out.data_ptr(), d_gates.data_ptr(),
+                                d_tokens.data_ptr(), rows, T, code, _ptr(carry_in), _ptr(halo_gate_right),
+                                _ptr(halo_state_left), ws.ptr, ws.nbytes, stream)
+    _finish(rc, "ascan_backward", ws, stream)
 
 
 def reduce_forward(gates, tokens, carry_out):
     _require_cuda(gates, tokens, carry_out)
-    rows = gates.numel() // gates.shape[-1]
-    with torch.cuda.device(gates.device):
-        ws = workspace(gates.device, rows)
-        rc = lib.ascan_reduce_forward(_ptr(gates), _ptr(tokens), _ptr(carry_out), rows, gates.shape[-1],
-                                      dtype_code(gates), _ptr(ws), ws.numel(), _stream(gates))
-    check(rc, "ascan_reduce_forward")
+    rows, T = _rows_T(gates)
+    code = dtype_code(gates)
+    dev = gates.device
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    ws = _workspace(dev, stream, rows, T, code, KIND_REDUCE_FORWARD)
+    with _device_guard(dev):
+        rc = lib.ascan_reduce_forward(gates.data_ptr(), tokens.data_ptr(), carry_out.data_ptr(), rows, T, code,
+                                      ws.ptr, ws.nbytes, stream)
+    _finish(rc, "ascan_reduce_forward", ws, stream)
 
 
 def reduce_backward(gates, grad_out, halo_gate_right, carry_out):
     _require_cuda(gates, grad_out, halo_gate_right, carry_out)
-    rows = gates.numel() // gates.shape[-1]
-    with torch.cuda.device(gates.device):
-        ws = workspace(gates.device, rows)
-        rc = lib.ascan_reduce_backward(_ptr(gates), _ptr(grad_out), _ptr(halo_gate_right), _ptr(carry_out), rows,
-                                       gates.shape[-1], dtype_code(gates), _ptr(ws), ws.numel(), _stream(gates))
-    check(rc, "ascan_reduce_backward")
+    rows, T = _rows_T(gates)
+    code = dtype_code(gates)
+    dev = gates.device
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    ws = _workspace(dev, stream, rows, T, code, KIND_REDUCE_BACKWARD)
+    with _device_guard(dev):
+        rc = lib.ascan_reduce_backward(gates.data_ptr(), grad_out.data_ptr(), _ptr(halo_gate_right),
+                                       carry_out.data_ptr(), rows, T, code, ws.ptr, ws.nbytes, stream)
+    _finish(rc, "ascan_reduce_backward", ws, stream)
 
 
 def fold_carries(gathered, rank: int, suffix: bool, want_halo: bool = False):
@@ -271,17 +373,22 @@ def fold_carries(gathered, rank: int, suffix: bool, want_halo: bool = False):
     state = torch.empty(rows, dtype=gathered.dtype, device=gathered.device)
     halo = torch.empty(rows, dtype=gathered.dtype, device=gathered.device) if want_halo else None
     code = C64 if gathered.dtype == torch.complex64 else F32
-    with torch.cuda.device(gathered.device):
-        rc = lib.ascan_fold_carries(_ptr(gathered), rows, world, int(rank), stride, code, int(bool(suffix)),
-                                    _ptr(state), _ptr(halo), _stream(gathered))
+    with _device_guard(gathered.device):
+        rc = lib.ascan_fold_carries(gathered.data_ptr(), rows, world, int(rank), stride, code, int(bool(suffix)),
+                                    state.data_ptr(), _ptr(halo), torch.cuda.current_stream(gathered.device).cuda_stream)
     check(rc, "ascan_fold_carries")
     return state, halo
 
 
 def check_status(device=None) -> None:
-    """Synchronise and raise if a bounded device-side wait expired in an earlier launch."""
+    """Synchronise the current stream of `device` and raise if a bounded device-side wait
+    expired in an earlier launch on it."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    with torch.cuda.device(device):
-        ws = workspace(device)
-        rc = lib.ascan_check(_ptr(ws), ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream))
+    stream = torch.cuda.current_stream(device).cuda_stream
+    ws = _workspaces.get((device.index, stream))
+    if ws is None:
+        return
+    with _device_guard(device):
+        rc = lib.ascan_check(ws.ptr, stream)
+    ws.sink_np[0] = 0
     check(rc, "ascan_check")

@@ -15,8 +15,10 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "accelerated_scan", "libascan_b200.so")
-SOURCES = ["api.cu", "planner.cpp"]
-HEADERS = ["common.cuh", "stream.cuh", "team.cuh", "planner.h", os.path.join("..", "..", "include", "ascan_b200.h")]
+SOURCES = ["api.cu", "planner.cpp", "inst_f32.cu", "inst_bf16.cu", "inst_f16.cu", "inst_c64.cu"]
+HEADERS = ["common.cuh", "stream.cuh", "team.cuh", "dispatch.cuh", "launch.h", "planner.h",
+           os.path.join("..", "..", "include", "ascan_b200.h")]
+OBJ_DIR = os.path.join(HERE, "build", "obj")
 
 
 def _nvcc() -> str:
@@ -37,15 +39,23 @@ def needs_build() -> bool:
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not needs_build():
         return OUT
-    cmd = [
-        _nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-        "-Xcompiler", "-fPIC", "-shared", "-o", OUT,
-    ] + [os.path.join(CSRC, s) for s in SOURCES]
+    # one nvcc process per translation unit, all at once, then one link
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    flags = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"]
     if verbose:
-        cmd.insert(1, "-Xptxas")
-        cmd.insert(2, "-v")
-        print(" ".join(cmd))
-    subprocess.run(cmd, check=True)
+        flags += ["-Xptxas", "-v"]
+    jobs = []
+    for src in SOURCES:
+        obj = os.path.join(OBJ_DIR, os.path.splitext(src)[0] + ".o")
+        cmd = [_nvcc()] + flags + ["-c", os.path.join(CSRC, src), "-o", obj]
+        if verbose:
+            print(" ".join(cmd))
+        jobs.append((cmd, obj, subprocess.Popen(cmd)))
+    failed = [cmd for cmd, _, proc in jobs if proc.wait() != 0]
+    if failed:
+        raise RuntimeError("nvcc failed: " + " ".join(failed[0]))
+    link = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", OUT] + [obj for _, obj, _ in jobs]
+    subprocess.run(link, check=True)
     return OUT
 
 

@@ -2,111 +2,103 @@
 // argument validation, planning, kernel dispatch, launch-error reporting.
 #include <cuda_runtime.h>
 #include <stdint.h>
-#include <stdlib.h>
 
+#include <atomic>
 #include <mutex>
-#include <set>
-#include <utility>
 
 #include "../../include/ascan_b200.h"
+#include "launch.h"
 #include "planner.h"
 #include "stream.cuh"
-#include "team.cuh"
 
 namespace ascan {
 
 static int cached_sm_count(int *out) {
-    static int counts[64] = {0};
+    static std::atomic<int> counts[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return ASCAN_ERR_DEVICE;
-    if (dev >= 0 && dev < 64 && counts[dev] > 0) {
-        *out = counts[dev];
-        return ASCAN_OK;
+    if (dev >= 0 && dev < 64) {
+        const int c = counts[dev].load(std::memory_order_relaxed);
+        if (c > 0) {
+            *out = c;
+            return ASCAN_OK;
+        }
     }
     int n = 0, major = 0;
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return ASCAN_ERR_DEVICE;
     if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return ASCAN_ERR_DEVICE;
     if (major != 10 || n < 1) return ASCAN_ERR_DEVICE;   // built for sm_100a only
-    if (dev >= 0 && dev < 64) counts[dev] = n;
+    if (dev >= 0 && dev < 64) counts[dev].store(n, std::memory_order_relaxed);
     *out = n;
     return ASCAN_OK;
 }
 
-// Opt in to the large dynamic shared-memory carve-out once per (kernel, device).
-static int ensure_smem(const void *fn, size_t bytes) {
-    static std::mutex mu;
-    static std::set<std::pair<const void *, int>> done;
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return ASCAN_ERR_DEVICE;
-    std::lock_guard<std::mutex> lock(mu);
-    if (done.count({fn, dev})) return ASCAN_OK;
-    (void)bytes;
-    if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemPerCta) != cudaSuccess) {
-        cudaGetLastError();
-        return ASCAN_ERR_LAUNCH;
-    }
-    done.insert({fn, dev});
-    return ASCAN_OK;
+// ---- options (ascan_set_option): process-wide, read on every call, never from the environment
+static std::atomic<int> g_opt_stages{2}, g_opt_wpc{0}, g_opt_lookback_tiles{8}, g_opt_disable_plans{0};
+static std::atomic<int> g_opt_drop_carry{0}, g_opt_epoch_bits{17};
+static std::atomic<uint32_t> g_opt_generation{0};
+
+static PlanTuning current_tuning() {
+    PlanTuning t;
+    t.stages = g_opt_stages.load(std::memory_order_relaxed);
+    t.warps_per_cta = g_opt_wpc.load(std::memory_order_relaxed);
+    t.lookback_tiles = g_opt_lookback_tiles.load(std::memory_order_relaxed);
+    t.disable_plans = g_opt_disable_plans.load(std::memory_order_relaxed);
+    return t;
 }
 
-template <class TR, int NCH, int KIND, bool REVERSE, bool BULK, bool INTERIOR, bool LOOKBACK = false>
-static int launch_one(const StreamParams &p, const ascan_plan &pl, cudaStream_t stream) {
-    auto kfn = stream_kernel<TR, NCH, KIND, REVERSE, BULK, INTERIOR, LOOKBACK>;
-    int rc = ensure_smem(reinterpret_cast<const void *>(kfn), pl.smem_bytes);
-    if (rc != ASCAN_OK) return rc;
-    kfn<<<pl.grid, pl.warps_per_cta * 32, pl.smem_bytes, stream>>>(p);
-    return cudaGetLastError() == cudaSuccess ? ASCAN_OK : ASCAN_ERR_LAUNCH;
-}
-
-// INTERIOR: items that group several rows have row boundaries inside their tiles.
-template <class TR, int NCH, int KIND, bool REVERSE, bool BULK>
-static int launch_interior(const StreamParams &p, const ascan_plan &pl, cudaStream_t stream) {
-    // look-back plans exist for the bulk loader and the two scan kinds; team plans also for
-    // the carry-only kinds of the real dtypes
-    if constexpr (BULK && (KIND == K_SCAN || KIND == K_BWD)) {
-        if (pl.kernel == 1) return launch_one<TR, NCH, KIND, REVERSE, BULK, false, true>(p, pl, stream);
+// ---- plan memo: the last few plans of this thread.  make_plan is pure arithmetic on its
+// input, so an equal key means an equal plan; options changes bump the generation.
+struct PlanKey {
+    int64_t rows, seqlen;
+    int dtype, kind, sm_count;
+    uint32_t flags, generation;
+    bool operator==(const PlanKey &o) const {
+        return rows == o.rows && seqlen == o.seqlen && dtype == o.dtype && kind == o.kind && sm_count == o.sm_count &&
+               flags == o.flags && generation == o.generation;
     }
-    if constexpr (BULK && (KIND == K_SCAN || KIND == K_BWD || sizeof(typename TR::V) == 4)) {
-        if (pl.kernel == 2) {
-            auto kfn = team_kernel<TR, NCH, KIND, REVERSE>;
-            int rc = ensure_smem(reinterpret_cast<const void *>(kfn), pl.smem_bytes);
-            if (rc != ASCAN_OK) return rc;
-            kfn<<<pl.grid, pl.warps_per_cta * 32, pl.smem_bytes, stream>>>(p);
-            return cudaGetLastError() == cudaSuccess ? ASCAN_OK : ASCAN_ERR_LAUNCH;
+};
+struct PlanMemo {
+    static constexpr int N = 8;
+    PlanKey key[N];
+    ascan_plan plan[N];
+    int rc[N];
+    int used = 0, next = 0;
+};
+static int make_plan_cached(const PlanInput &in, ascan_plan *pl) {
+    thread_local PlanMemo memo;
+    PlanKey k;
+    k.rows = in.rows;
+    k.seqlen = in.seqlen;
+    k.dtype = in.dtype;
+    k.kind = in.kind;
+    k.sm_count = in.sm_count;
+    k.flags = (in.reverse ? 1u : 0u) | (in.aligned ? 2u : 0u) | (in.workspace ? 4u : 0u) | (in.allow_lookback ? 8u : 0u) |
+              (in.allow_team ? 16u : 0u) | (in.three_chunks ? 32u : 0u);
+    k.generation = g_opt_generation.load(std::memory_order_relaxed);
+    for (int i = 0; i < memo.used; ++i) {
+        if (memo.key[i] == k) {
+            *pl = memo.plan[i];
+            return memo.rc[i];
         }
     }
-    if (pl.kernel != 0) return ASCAN_ERR_UNSUPPORTED;
-    return pl.rows_per_item > 1 ? launch_one<TR, NCH, KIND, REVERSE, BULK, true>(p, pl, stream)
-                                : launch_one<TR, NCH, KIND, REVERSE, BULK, false>(p, pl, stream);
+    const int rc = make_plan(in, pl);
+    const int slot = memo.next;
+    memo.key[slot] = k;
+    memo.plan[slot] = *pl;
+    memo.rc[slot] = rc;
+    memo.next = (slot + 1) % PlanMemo::N;
+    if (memo.used < PlanMemo::N) ++memo.used;
+    return rc;
 }
 
-template <class TR, int NCH, int KIND, bool REVERSE>
-static int launch_loader(const StreamParams &p, const ascan_plan &pl, cudaStream_t stream) {
-    return pl.loader == 0 ? launch_interior<TR, NCH, KIND, REVERSE, true>(p, pl, stream)
-                          : launch_interior<TR, NCH, KIND, REVERSE, false>(p, pl, stream);
-}
-
-template <class TR, int KIND, bool REVERSE>
-static int launch_nch(const StreamParams &p, const ascan_plan &pl, cudaStream_t stream) {
-    switch (pl.chunks_per_lane) {
-        case 3: return launch_loader<TR, 3, KIND, REVERSE>(p, pl, stream);
-        case 2:
-            // two chunks per lane: planned for the fused backward of the 16-bit dtypes only
-            if constexpr (KIND == K_BWD && TR::EPC == 8) {
-                if (pl.kernel == 0) return launch_loader<TR, 2, KIND, REVERSE>(p, pl, stream);
-            }
-            return ASCAN_ERR_UNSUPPORTED;
-        default: return ASCAN_ERR_UNSUPPORTED;
-    }
-}
-
-template <int KIND, bool REVERSE>
-static int launch_dtype(int dtype, const StreamParams &p, const ascan_plan &pl, cudaStream_t stream) {
+static int launch_by_dtype(int dtype, int variant, int kind, bool reverse, const StreamParams &p, const ascan_plan &pl,
+                           cudaStream_t st) {
     switch (dtype) {
-        case ASCAN_F32: return launch_nch<TraitsF32, KIND, REVERSE>(p, pl, stream);
-        case ASCAN_BF16: return launch_nch<TraitsBF16, KIND, REVERSE>(p, pl, stream);
-        case ASCAN_F16: return launch_nch<TraitsF16, KIND, REVERSE>(p, pl, stream);
-        case ASCAN_C64: return launch_nch<TraitsC64, KIND, REVERSE>(p, pl, stream);
+        case ASCAN_F32: return launch_f32(variant, kind, reverse, p, pl, st);
+        case ASCAN_BF16: return launch_bf16(variant, kind, reverse, p, pl, st);
+        case ASCAN_F16: return launch_f16(variant, kind, reverse, p, pl, st);
+        case ASCAN_C64: return launch_c64(variant, kind, reverse, p, pl, st);
         default: return ASCAN_ERR_INVALID_ARG;
     }
 }
@@ -140,15 +132,6 @@ __global__ void fold_carries_kernel(const V *gathered, int64_t rows, int world, 
     }
 }
 
-static int l2_hints_env() {
-    const char *v = getenv("ASCAN_L2_HINTS");
-    int bits = (v && *v) ? (atoi(v) & 15) : 0;
-    // test hook: one carry hand-over is dropped so that a bounded device-side wait expires
-    const char *d = getenv("ASCAN_TEST_DROP_CARRY");
-    if (d && *d == '1') bits |= 256;
-    return bits;
-}
-
 static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 static int plan_for(int64_t rows, int64_t seqlen, int dtype, int kind, bool aligned, const void *ws, size_t ws_bytes,
@@ -161,23 +144,24 @@ static int plan_for(int64_t rows, int64_t seqlen, int dtype, int kind, bool alig
     in.kind = kind;
     in.aligned = aligned;
     in.workspace = ws && (reinterpret_cast<uintptr_t>(ws) & 255u) == 0;
+    in.tune = current_tuning();
     int rc = cached_sm_count(&in.sm_count);
     if (rc != ASCAN_OK) return rc;
     // prefer the plan that wants the most scratch; step down while the caller's is too small
-    rc = make_plan(in, pl);
+    rc = make_plan_cached(in, pl);
     if (rc == ASCAN_OK && pl->workspace_bytes > ws_bytes && in.workspace) {
         in.allow_lookback = false;
-        rc = make_plan(in, pl);
+        rc = make_plan_cached(in, pl);
         if (rc == ASCAN_OK && pl->workspace_bytes > ws_bytes) {
             in.workspace = false;
-            rc = make_plan(in, pl);
+            rc = make_plan_cached(in, pl);
         }
     }
     return rc;
 }
 
 // Copies the plan's decomposition and the workspace pointers into the kernel parameters.
-static void fill_common(StreamParams &p, const ascan_plan &pl, int64_t rows, int64_t seqlen, void *ws) {
+static void fill_common(StreamParams &p, const ascan_plan &pl, int64_t rows, int64_t seqlen, void *ws, size_t ws_bytes) {
     p.rows = rows;
     p.T = seqlen;
     p.rows_per_item = pl.rows_per_item;
@@ -191,8 +175,10 @@ static void fill_common(StreamParams &p, const ascan_plan &pl, int64_t rows, int
     p.ctrl = pl.dynamic ? static_cast<uint32_t *>(ws) : nullptr;
     p.records = pl.dynamic ? static_cast<unsigned char *>(ws) + CTRL_BYTES : nullptr;
     p.stages = pl.stages;
-    p.l2_hints = l2_hints_env();
     p.team_size = pl.team_size;
+    p.test_drop_carry = g_opt_drop_carry.load(std::memory_order_relaxed);
+    p.epoch_mask = (1u << g_opt_epoch_bits.load(std::memory_order_relaxed)) - 1u;
+    p.scratch_bytes = (pl.dynamic && ws_bytes > static_cast<size_t>(CTRL_BYTES)) ? ws_bytes - CTRL_BYTES : 0;
 }
 
 // Plan for the fused variants, which exist only in the chained stream plan with the bulk
@@ -210,43 +196,17 @@ static int plan_for_variant(int64_t rows, int64_t seqlen, int dtype, int kind, b
     in.workspace = ws && (reinterpret_cast<uintptr_t>(ws) & 255u) == 0;
     in.allow_lookback = false;
     in.allow_team = false;
+    in.tune = current_tuning();
     int rc = cached_sm_count(&in.sm_count);
     if (rc != ASCAN_OK) return rc;
-    rc = make_plan(in, pl);
+    rc = make_plan_cached(in, pl);
     if (rc == ASCAN_OK && pl->workspace_bytes > ws_bytes && in.workspace) {
         in.workspace = false;
-        rc = make_plan(in, pl);
+        rc = make_plan_cached(in, pl);
     }
     if (rc != ASCAN_OK) return rc;
     if (pl->loader != 0 || pl->rows_per_item != 1 || pl->kernel != 0) return ASCAN_ERR_UNSUPPORTED;
     return ASCAN_OK;
-}
-
-template <class KFN>
-static int launch_variant(KFN kfn, const StreamParams &p, const ascan_plan &pl, cudaStream_t st) {
-    int rc = ensure_smem(reinterpret_cast<const void *>(kfn), pl.smem_bytes);
-    if (rc != ASCAN_OK) return rc;
-    kfn<<<pl.grid, pl.warps_per_cta * 32, pl.smem_bytes, st>>>(p);
-    return cudaGetLastError() == cudaSuccess ? ASCAN_OK : ASCAN_ERR_LAUNCH;
-}
-
-template <class TR>
-static int launch_sigmoid(int kind, const StreamParams &p, const ascan_plan &pl, cudaStream_t st) {
-    if (kind == ASCAN_KIND_FORWARD) {
-        if (pl.chunks_per_lane != 3) return ASCAN_ERR_UNSUPPORTED;
-        return launch_variant(stream_kernel<TR, 3, K_SCAN, false, true, false, false, false, 1>, p, pl, st);
-    }
-    if (pl.chunks_per_lane != 3) return ASCAN_ERR_UNSUPPORTED;
-    return launch_variant(stream_kernel<TR, 3, K_BWD, true, true, false, false, false, 1>, p, pl, st);
-}
-
-static int launch_sigmoid_dtype(int dtype, int kind, const StreamParams &p, const ascan_plan &pl, cudaStream_t st) {
-    switch (dtype) {
-        case ASCAN_F32: return launch_sigmoid<TraitsF32>(kind, p, pl, st);
-        case ASCAN_BF16: return launch_sigmoid<TraitsBF16>(kind, p, pl, st);
-        case ASCAN_F16: return launch_sigmoid<TraitsF16>(kind, p, pl, st);
-        default: return ASCAN_ERR_UNSUPPORTED;
-    }
 }
 
 }  // namespace ascan
@@ -286,9 +246,8 @@ int ascan_forward(const void *gates, const void *tokens, void *out, int64_t rows
     p.in1 = tokens;
     p.out0 = out;
     p.carry_in = carry_in;
-    fill_common(p, pl, rows, seqlen, ws);
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    return reverse ? launch_dtype<K_SCAN, true>(dtype, p, pl, st) : launch_dtype<K_SCAN, false>(dtype, p, pl, st);
+    fill_common(p, pl, rows, seqlen, ws, ws_bytes);
+    return launch_by_dtype(dtype, VARIANT_PLAIN, ASCAN_KIND_FORWARD, reverse != 0, p, pl, static_cast<cudaStream_t>(stream));
 }
 
 int ascan_backward(const void *gates, const void *states, const void *grad_out, void *d_gates, void *d_tokens,
@@ -312,8 +271,8 @@ int ascan_backward(const void *gates, const void *states, const void *grad_out, 
     p.carry_in = carry_in;
     p.halo_gate = halo_gate_right;
     p.halo_state = halo_state_left;
-    fill_common(p, pl, rows, seqlen, ws);
-    return launch_dtype<K_BWD, true>(dtype, p, pl, static_cast<cudaStream_t>(stream));
+    fill_common(p, pl, rows, seqlen, ws, ws_bytes);
+    return launch_by_dtype(dtype, VARIANT_PLAIN, ASCAN_KIND_BACKWARD, true, p, pl, static_cast<cudaStream_t>(stream));
 }
 
 int ascan_reduce_forward(const void *gates, const void *tokens, void *carry_out, int64_t rows, int64_t seqlen,
@@ -329,8 +288,8 @@ int ascan_reduce_forward(const void *gates, const void *tokens, void *carry_out,
     p.in0 = gates;
     p.in1 = tokens;
     p.carry_out = carry_out;
-    fill_common(p, pl, rows, seqlen, ws);
-    return launch_dtype<K_REDUCE, false>(dtype, p, pl, static_cast<cudaStream_t>(stream));
+    fill_common(p, pl, rows, seqlen, ws, ws_bytes);
+    return launch_by_dtype(dtype, VARIANT_PLAIN, ASCAN_KIND_REDUCE_FORWARD, false, p, pl, static_cast<cudaStream_t>(stream));
 }
 
 int ascan_reduce_backward(const void *gates, const void *grad_out, const void *halo_gate_right, void *carry_out,
@@ -347,8 +306,8 @@ int ascan_reduce_backward(const void *gates, const void *grad_out, const void *h
     p.in1 = grad_out;
     p.halo_gate = halo_gate_right;
     p.carry_out = carry_out;
-    fill_common(p, pl, rows, seqlen, ws);
-    return launch_dtype<K_REDUCE_BWD, true>(dtype, p, pl, static_cast<cudaStream_t>(stream));
+    fill_common(p, pl, rows, seqlen, ws, ws_bytes);
+    return launch_by_dtype(dtype, VARIANT_PLAIN, ASCAN_KIND_REDUCE_BACKWARD, true, p, pl, static_cast<cudaStream_t>(stream));
 }
 
 size_t ascan_workspace_bytes(int64_t rows, int64_t seqlen, int dtype, int kind) {
@@ -360,12 +319,13 @@ size_t ascan_workspace_bytes(int64_t rows, int64_t seqlen, int dtype, int kind) 
     in.aligned = true;
     in.workspace = true;
     in.reverse = false;
+    in.tune = current_tuning();
     if (cached_sm_count(&in.sm_count) != ASCAN_OK) {
         cudaGetLastError();
         in.sm_count = 148;          // no device to ask: size for a full B200
     }
     ascan_plan pl;
-    if (make_plan(in, &pl) != ASCAN_OK) return static_cast<size_t>(workspace_bytes(rows));
+    if (make_plan_cached(in, &pl) != ASCAN_OK) return static_cast<size_t>(workspace_bytes(rows));
     return static_cast<size_t>(pl.workspace_bytes);
 }
 
@@ -386,7 +346,49 @@ int ascan_plan_describe(int64_t rows, int64_t seqlen, int dtype, int kind, int f
         int rc = cached_sm_count(&in.sm_count);
         if (rc != ASCAN_OK) return rc;
     }
+    in.tune = current_tuning();
     return make_plan(in, plan);
+}
+
+int ascan_set_option(int option, int value) {
+    switch (option) {
+        case ASCAN_OPT_STAGES:
+            if (value < 1 || value > 8) return ASCAN_ERR_INVALID_ARG;
+            g_opt_stages.store(value);
+            break;
+        case ASCAN_OPT_WARPS_PER_CTA:
+            if (value < 0 || value > 16) return ASCAN_ERR_INVALID_ARG;
+            g_opt_wpc.store(value);
+            break;
+        case ASCAN_OPT_LOOKBACK_TILES:
+            if (value < 1 || value > 64) return ASCAN_ERR_INVALID_ARG;
+            g_opt_lookback_tiles.store(value);
+            break;
+        case ASCAN_OPT_DISABLE_PLANS:
+            if (value < 0 || value > 15) return ASCAN_ERR_INVALID_ARG;
+            g_opt_disable_plans.store(value);
+            break;
+        case ASCAN_OPT_TEST_DROP_CARRY: g_opt_drop_carry.store(value ? 1 : 0); break;
+        case ASCAN_OPT_TEST_EPOCH_BITS:
+            if (value < 1 || value > 17) return ASCAN_ERR_INVALID_ARG;
+            g_opt_epoch_bits.store(value);
+            break;
+        default: return ASCAN_ERR_INVALID_ARG;
+    }
+    g_opt_generation.fetch_add(1);
+    return ASCAN_OK;
+}
+
+int ascan_get_option(int option) {
+    switch (option) {
+        case ASCAN_OPT_STAGES: return g_opt_stages.load();
+        case ASCAN_OPT_WARPS_PER_CTA: return g_opt_wpc.load();
+        case ASCAN_OPT_LOOKBACK_TILES: return g_opt_lookback_tiles.load();
+        case ASCAN_OPT_DISABLE_PLANS: return g_opt_disable_plans.load();
+        case ASCAN_OPT_TEST_DROP_CARRY: return g_opt_drop_carry.load();
+        case ASCAN_OPT_TEST_EPOCH_BITS: return g_opt_epoch_bits.load();
+        default: return -1;
+    }
 }
 
 int ascan_forward_complex_real_tokens(const void *gates, const void *tokens_real, void *out, int64_t rows,
@@ -398,40 +400,15 @@ int ascan_forward_complex_real_tokens(const void *gates, const void *tokens_real
     // chained stream plan; the real rows must start 16-byte aligned as well (seqlen % 4 == 0).
     const bool al = aligned16(gates) && aligned16(tokens_real) && aligned16(out);
     if (!al || seqlen % 4 != 0) return ASCAN_ERR_UNSUPPORTED;
-    PlanInput in;
-    in.reverse = reverse != 0;
-    in.rows = rows;
-    in.seqlen = seqlen;
-    in.dtype = ASCAN_C64;
-    in.kind = ASCAN_KIND_FORWARD;
-    in.aligned = true;
-    in.workspace = ws && (reinterpret_cast<uintptr_t>(ws) & 255u) == 0;
-    in.allow_lookback = false;
-    in.allow_team = false;
-    int rc = cached_sm_count(&in.sm_count);
-    if (rc != ASCAN_OK) return rc;
     ascan_plan pl;
-    rc = make_plan(in, &pl);
-    if (rc == ASCAN_OK && pl.workspace_bytes > ws_bytes && in.workspace) {
-        in.workspace = false;
-        rc = make_plan(in, &pl);
-    }
+    int rc = plan_for_variant(rows, seqlen, ASCAN_C64, ASCAN_KIND_FORWARD, reverse != 0, ws, ws_bytes, &pl);
     if (rc != ASCAN_OK) return rc;
-    if (pl.loader != 0 || pl.rows_per_item != 1 || pl.kernel != 0) return ASCAN_ERR_UNSUPPORTED;
     StreamParams p = {};
     p.in0 = gates;
     p.in1 = tokens_real;
     p.out0 = out;
-    fill_common(p, pl, rows, seqlen, ws);
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    auto launch = [&](auto kfn) -> int {
-        int r2 = ensure_smem(reinterpret_cast<const void *>(kfn), pl.smem_bytes);
-        if (r2 != ASCAN_OK) return r2;
-        kfn<<<pl.grid, pl.warps_per_cta * 32, pl.smem_bytes, st>>>(p);
-        return cudaGetLastError() == cudaSuccess ? ASCAN_OK : ASCAN_ERR_LAUNCH;
-    };
-    return reverse ? launch(stream_kernel<TraitsC64, 3, K_SCAN, true, true, false, false, true>)
-                   : launch(stream_kernel<TraitsC64, 3, K_SCAN, false, true, false, false, true>);
+    fill_common(p, pl, rows, seqlen, ws, ws_bytes);
+    return launch_c64(VARIANT_REAL_TOKENS, ASCAN_KIND_FORWARD, reverse != 0, p, pl, static_cast<cudaStream_t>(stream));
 }
 
 int ascan_backward_complex_real_tokens(const void *gates, const void *states, const void *grad_out, void *d_gates,
@@ -453,9 +430,8 @@ int ascan_backward_complex_real_tokens(const void *gates, const void *states, co
     p.in2 = states;
     p.out0 = d_tokens_real;
     p.out1 = d_gates;
-    fill_common(p, pl, rows, seqlen, ws);
-    return launch_variant(stream_kernel<TraitsC64, 3, K_BWD, true, true, false, false, true>, p, pl,
-                          static_cast<cudaStream_t>(stream));
+    fill_common(p, pl, rows, seqlen, ws, ws_bytes);
+    return launch_c64(VARIANT_REAL_TOKENS, ASCAN_KIND_BACKWARD, true, p, pl, static_cast<cudaStream_t>(stream));
 }
 
 int ascan_forward_sigmoid_gates(const void *gate_logits, const void *tokens, void *out, int64_t rows, int64_t seqlen,
@@ -472,8 +448,8 @@ int ascan_forward_sigmoid_gates(const void *gate_logits, const void *tokens, voi
     p.in0 = gate_logits;
     p.in1 = tokens;
     p.out0 = out;
-    fill_common(p, pl, rows, seqlen, ws);
-    return launch_sigmoid_dtype(dtype, ASCAN_KIND_FORWARD, p, pl, static_cast<cudaStream_t>(stream));
+    fill_common(p, pl, rows, seqlen, ws, ws_bytes);
+    return launch_by_dtype(dtype, VARIANT_SIGMOID, ASCAN_KIND_FORWARD, false, p, pl, static_cast<cudaStream_t>(stream));
 }
 
 int ascan_backward_sigmoid_gates(const void *gate_logits, const void *states, const void *grad_out, void *d_logits,
@@ -495,8 +471,8 @@ int ascan_backward_sigmoid_gates(const void *gate_logits, const void *states, co
     p.in2 = states;
     p.out0 = d_tokens;
     p.out1 = d_logits;
-    fill_common(p, pl, rows, seqlen, ws);
-    return launch_sigmoid_dtype(dtype, ASCAN_KIND_BACKWARD, p, pl, static_cast<cudaStream_t>(stream));
+    fill_common(p, pl, rows, seqlen, ws, ws_bytes);
+    return launch_by_dtype(dtype, VARIANT_SIGMOID, ASCAN_KIND_BACKWARD, true, p, pl, static_cast<cudaStream_t>(stream));
 }
 
 int ascan_fold_carries(const void *gathered, int64_t rows, int world, int rank, int stride, int dtype, int suffix,
@@ -576,10 +552,11 @@ int ascan_forward_no_alloc(const void *gates, const void *tokens, void *out, int
     int rc = no_alloc_scratch_address(&scratch);
     if (rc != ASCAN_OK) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    // The array keeps whatever the previous call left.  The status word, the work ticket
-    // and the exit counter must start at zero; the launch epoch behind them must survive,
-    // because it is what tells this call's carry records from older ones.
-    if (cudaMemsetAsync(scratch, 0, 3 * sizeof(uint32_t), st) != cudaSuccess) {
+    // The array keeps whatever the previous call left.  The work ticket and the exit
+    // counter must start at zero.  The status word in front of them is left alone, so a
+    // timeout of an earlier call stays readable by ascan_check_no_alloc; so is the launch
+    // epoch behind them, which tells this call's carry records from older ones.
+    if (cudaMemsetAsync(scratch + sizeof(uint32_t), 0, 2 * sizeof(uint32_t), st) != cudaSuccess) {
         cudaGetLastError();
         return ASCAN_ERR_LAUNCH;
     }
@@ -591,8 +568,15 @@ int ascan_forward_no_alloc(const void *gates, const void *tokens, void *out, int
     p.in0 = gates;
     p.in1 = tokens;
     p.out0 = out;
-    fill_common(p, pl, rows, seqlen, scratch);
-    return reverse ? launch_dtype<K_SCAN, true>(dtype, p, pl, st) : launch_dtype<K_SCAN, false>(dtype, p, pl, st);
+    fill_common(p, pl, rows, seqlen, scratch, sizeof(g_no_alloc_scratch));
+    return launch_by_dtype(dtype, VARIANT_PLAIN, ASCAN_KIND_FORWARD, reverse != 0, p, pl, st);
+}
+
+int ascan_check_no_alloc(void *stream) {
+    unsigned char *scratch = nullptr;
+    int rc = no_alloc_scratch_address(&scratch);
+    if (rc != ASCAN_OK) return rc;
+    return ascan_check(scratch, stream);
 }
 
 }  // extern "C"

@@ -1,7 +1,5 @@
 #include "planner.h"
 
-#include <stdlib.h>
-
 #include <initializer_list>
 
 namespace ascan {
@@ -19,12 +17,6 @@ int dtype_size(int dtype) {
 uint64_t workspace_bytes(int64_t rows) {
     if (rows < 0) rows = 0;
     return static_cast<uint64_t>(kCtrlBytes) + static_cast<uint64_t>(rows) * kCarryRecordBytes;
-}
-
-static int env_int(const char *name, int fallback) {
-    const char *v = getenv(name);
-    if (!v || !*v) return fallback;
-    return atoi(v);
 }
 
 static int nin_of(int kind) { return kind == ASCAN_KIND_BACKWARD ? 3 : 2; }
@@ -61,14 +53,13 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     // 4096-6000 rows of 8192: 5.3-5.6 against 5.7-6.3).  Above two rows per warp only for rows
     // long enough to be split (whole short rows run better one warp each); from 8000 rows on
     // the stream plan is ahead again.
-    const int64_t team_rows = env_int("ASCAN_TEAM_ROWS", static_cast<int>(4 * stream_warps));
-    const int nch = (in.kind == ASCAN_KIND_BACKWARD && esize == 2 && in.rows >= team_rows && !in.three_chunks &&
-                     env_int("ASCAN_NCH3_ONLY", 0) == 0)
+    const int64_t team_rows = 4 * stream_warps;
+    const int nch = (in.kind == ASCAN_KIND_BACKWARD && esize == 2 && in.rows >= team_rows && !in.three_chunks)
                         ? 2
                         : 3;
     const int64_t te = 32 * nch * (16 / esize);
     // tickets and split-row item numbers are 32-bit
-    const bool use_ws = in.workspace && env_int("ASCAN_STATIC", 0) == 0 && in.rows < (1ll << 30) &&
+    const bool use_ws = in.workspace && (in.tune.disable_plans & 4) == 0 && in.rows < (1ll << 30) &&
                         in.rows * ((in.seqlen + te - 1) / te) < (1ll << 31);
     pl.dynamic = use_ws ? 1 : 0;
 
@@ -82,7 +73,7 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     while ((align_rows * row_bytes_mod) % 16 != 0) align_rows *= 2;          // at most 16
     // ... and the whole matrix must end on a 16-byte boundary (the last item may be short)
     const bool total_ok = ((in.rows % 16) * row_bytes_mod) % 16 == 0;
-    const bool bulk = in.aligned && total_ok && env_int("ASCAN_FORCE_PLAIN", 0) == 0;
+    const bool bulk = in.aligned && total_ok && (in.tune.disable_plans & 8) == 0;
     pl.loader = bulk ? 0 : 1;
 
     // Item size.  Long rows are split into segments (needs the workspace for the per-row
@@ -91,27 +82,24 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     // fine segments of `fine_tiles` tiles, so that the warps run out of work within one
     // small item of each other.  The fine part holds about one coarse item per warp.
     // Short rows are grouped into items of about four per warp, at most `seg_tiles` tiles.
-    int seg_tiles = env_int("ASCAN_SEG_TILES", 16);
-    if (seg_tiles < 1) seg_tiles = 1;
-    int fine_tiles = env_int("ASCAN_FINE_TILES", 4);
-    if (fine_tiles < 1) fine_tiles = 1;
-    if (fine_tiles > seg_tiles) fine_tiles = seg_tiles;
+    int seg_tiles = 16;
+    int fine_tiles = 4;
     const int64_t max_warps = static_cast<int64_t>(in.sm_count) * kMaxWarpsPerCta;
     const int64_t tiles_row = (in.seqlen + te - 1) / te;
     const bool reverse_order = in.kind == ASCAN_KIND_BACKWARD || in.kind == ASCAN_KIND_REDUCE_BACKWARD || in.reverse;
-    const bool can_split = use_ws && (!bulk || align_rows == 1) && env_int("ASCAN_NO_SPLIT", 0) == 0;
+    const bool can_split = use_ws && (!bulk || align_rows == 1);
     // Clearly fewer rows than SMs: a whole CTA per row (the team plan below) would leave SMs
     // idle, so the look-back plan lets warps of many CTAs scan segments of one row at once.
     // Every segment but a row's first is streamed twice (aggregate pass, scan pass; the second
     // read finds the data in L2), which caps this plan near 4 TB/s.
     const bool scan_kind = in.kind == ASCAN_KIND_FORWARD || in.kind == ASCAN_KIND_BACKWARD;
-    int lb_tiles = env_int("ASCAN_LOOKBACK_TILES", 8);
+    int lb_tiles = in.tune.lookback_tiles;
     // below three rows per four SMs (measured on 148 SMs: at 96 rows look-back and teams of 12
     // warps tie, at 128 rows the teams win by 10-20 %)
-    const int64_t lookback_rows = env_int("ASCAN_LOOKBACK_ROWS", in.sm_count * 3 / 4);
+    const int64_t lookback_rows = in.sm_count * 3 / 4;
     if (lb_tiles < 1) lb_tiles = 1;
     const bool lookback = can_split && bulk && scan_kind && in.allow_lookback && in.rows < lookback_rows &&
-                          tiles_row >= 2 * lb_tiles && env_int("ASCAN_NO_LOOKBACK", 0) == 0;
+                          tiles_row >= 2 * lb_tiles && (in.tune.disable_plans & 1) == 0;
     if (lookback) {
         seg_tiles = lb_tiles;
         fine_tiles = lb_tiles;
@@ -123,12 +111,12 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     int team_wpc = kMaxWarpsPerCta;      // warps per CTA of a team plan
     const bool team_kind = scan_kind || in.dtype != ASCAN_C64;     // carry-only kinds: real dtypes
     if (!lookback && can_split && bulk && team_kind && in.allow_team && in.rows > 0 && in.rows < team_rows &&
-        env_int("ASCAN_NO_TEAM", 0) == 0) {
+        (in.tune.disable_plans & 2) == 0) {
         // The forward kinds need fewer registers and less shared memory per warp, so 16 warps
         // fit in a CTA (teams of 2, 4, 8 or 16): with 12 the forward is bound by the time a warp
         // needs per tile (4.4-5.4 TB/s at 150-800 rows), with 16 by HBM.
         const bool wide_kind = in.kind == ASCAN_KIND_FORWARD || in.kind == ASCAN_KIND_REDUCE_FORWARD;
-        if (wide_kind && env_int("ASCAN_TEAM_WIDE", 1) != 0) {
+        if (wide_kind) {
             const int64_t want16 = (static_cast<int64_t>(in.sm_count) * 16 + in.rows - 1) / in.rows;
             for (int cand : {2, 4, 8, 16}) {
                 if (cand >= want16) {
@@ -150,11 +138,6 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
             }
             if (team == 1) team = 12;
         }
-        const int team_env = env_int("ASCAN_TEAM", 0);
-        if (team_env == 2 || team_env == 3 || team_env == 4 || team_env == 6 || team_env == 12) {
-            team = team_env;
-            team_wpc = kMaxWarpsPerCta;
-        }
         // eight tiles per warp and coarse item, four per fine item: the team's barrier and
         // ticket hand-over per item cost about a tile (4 and 2 per warp measured 10 % slower
         // for teams of 16)
@@ -169,7 +152,7 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
         }
     }
     const int64_t workers = static_cast<int64_t>(in.sm_count) * team_wpc / team;
-    const int64_t split_min = lookback ? 2 * lb_tiles : (team > 1 ? 2 * fine_tiles : env_int("ASCAN_SPLIT_MIN_TILES", 32));
+    const int64_t split_min = lookback ? 2 * lb_tiles : (team > 1 ? 2 * fine_tiles : 32);
     if (can_split && tiles_row >= split_min && tiles_row >= 2 * fine_tiles) {
         int64_t fine_region = (static_cast<int64_t>(seg_tiles) * workers + in.rows - 1) / (in.rows > 0 ? in.rows : 1);
         fine_region = (fine_region + fine_tiles - 1) / fine_tiles * fine_tiles;      // tiles, multiple of a fine item
@@ -210,8 +193,6 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
         if (fit < seg_tiles) seg_tiles = static_cast<int>(fit);
         int64_t rpi = (seg_tiles * te) / in.seqlen;
         if (rpi < 1) rpi = 1;
-        const int rpi_env = env_int("ASCAN_RPI", 0);                     // sweep/test override
-        if (rpi_env > 0) rpi = rpi_env;
         if (bulk) rpi = (rpi + align_rows - 1) / align_rows * align_rows;
         pl.rows_per_item = rpi;
         pl.row_groups = (in.rows + rpi - 1) / rpi;
@@ -223,7 +204,7 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     }
     pl.items = pl.row_groups * pl.segs_per_row;
 
-    int stages = env_int("ASCAN_STAGES", 2);
+    int stages = in.tune.stages;
     if (stages < 1) stages = 1;
     if (stages > 8) stages = 8;
     pl.stages = bulk ? stages : 1;
@@ -238,7 +219,7 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     // latency, 15-16 leave too few registers and shared memory per warp)
     const int wpc_cap = team > 1 ? team_wpc : ((in.kind == ASCAN_KIND_BACKWARD && nch > 2) ? 14 : 16);
     if (wpc > wpc_cap) wpc = wpc_cap;
-    const int wpc_env = env_int("ASCAN_WPC", 0);
+    const int wpc_env = in.tune.warps_per_cta;
     if (wpc_env > 0 && wpc_env < wpc) wpc = wpc_env;
     else if (wpc > 14) wpc = 14;
     if (wpc < 1) return ASCAN_ERR_UNSUPPORTED;
@@ -267,8 +248,7 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     }
     // A problem of at most two items per warp gains nothing from tickets: deal statically and
     // save the ticket and exit-counter round trips (they are a fifth of a 15 us kernel).
-    if (pl.dynamic && team == 1 && pl.segs_per_row == 1 && pl.items <= 2 * grid * wpc &&
-        env_int("ASCAN_NO_SMALL_STATIC", 0) == 0) {
+    if (pl.dynamic && team == 1 && pl.segs_per_row == 1 && pl.items <= 2 * grid * wpc) {
         pl.dynamic = 0;
     }
     pl.team_size = team;

@@ -16,6 +16,15 @@ constexpr int kTeamSmemBytes = 384;          // shared memory per team of the te
 constexpr int kCtrlBytes = 256;              // control block at the start of a workspace
 constexpr int kCarryRecordBytes = 32;        // per-row carry record behind it
 
+// Tuning values of the planner.  The defaults are the measured optimum; tests and sweeps
+// change them through ascan_set_option (the library reads no environment variables).
+struct PlanTuning {
+    int stages = 2;            // shared-memory stages per warp of the stream and team kernels
+    int warps_per_cta = 0;     // 0 = planner's choice; otherwise an upper bound
+    int lookback_tiles = 8;    // tiles per segment of the look-back plan
+    int disable_plans = 0;     // bit 0: no look-back, bit 1: no team, bit 2: static deal (no tickets), bit 3: plain loader
+};
+
 struct PlanInput {
     int64_t rows;
     int64_t seqlen;
@@ -28,6 +37,7 @@ struct PlanInput {
     bool allow_team = true;       // false: never choose the team plan
     bool three_chunks = false;    // true: always 3 chunks per lane (variants without a 2-chunk kernel)
     int sm_count;
+    PlanTuning tune;
 };
 
 int dtype_size(int dtype);   // bytes per element, 0 if unknown

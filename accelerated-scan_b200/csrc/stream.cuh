@@ -61,8 +61,12 @@ namespace ascan {
 
 enum : int { K_SCAN = 0, K_BWD = 1, K_REDUCE = 2, K_REDUCE_BWD = 3 };
 
-// Control words at the start of the workspace (uint32 each).
-enum : int { CTRL_STATUS = 0, CTRL_TICKET = 1, CTRL_DONE = 2, CTRL_EPOCH = 3 };
+// Control words at the start of the workspace (uint32 each).  Words 4-5 hold an optional
+// 64-bit device-accessible address (for instance mapped pinned host memory) of a second
+// status word: a kernel that records status bits also ORs them in there, so the host can
+// notice a failure by reading its own memory, without a copy or a synchronisation.
+enum : int { CTRL_STATUS = 0, CTRL_TICKET = 1, CTRL_DONE = 2, CTRL_EPOCH = 3, CTRL_SINK = 4 };
+constexpr int EPOCH_SHIFT = 15;        // a carry tag is (epoch << 15) | segment number
 constexpr int CTRL_BYTES = 256;        // control block, then one carry record per row
 constexpr int CARRY_RECORD_BYTES = 32;
 constexpr int LOOKBACK_RECORD_BYTES = 64;   // per (row, segment): aggregate A, aggregate B, outgoing state
@@ -89,10 +93,52 @@ struct StreamParams {
     uint32_t *ctrl;          // control words, or null (static dealing, no status)
     unsigned char *records;  // per-row carry records (segs_per_row > 1)
     int32_t stages;          // shared-memory stages per warp (bulk loader)
-    int32_t l2_hints;        // bits 0-1: loads (0 none, 1 evict_first, 2 evict_last); bits 2-3: stores;
-                             // bit 8: test hook, drop one carry hand-over (see the item epilogue)
     int32_t team_size;       // warps per team (team kernel only)
+    int32_t test_drop_carry; // test hook: drop one carry hand-over (see the item epilogue); 0 in production
+    uint32_t epoch_mask;     // the launch epoch is taken modulo epoch_mask + 1 (2^17 - 1 unless a test lowers it)
+    uint64_t scratch_bytes;  // bytes of records behind the control block (wiped when the epoch wraps)
 };
+
+// Records status bits in the workspace and, when the caller registered one, in the
+// second status word (control words 4-5; typically mapped host memory, hence a plain
+// system-scope store: any non-zero value means "a wait expired").
+__device__ __forceinline__ void report_status(uint32_t *ctrl, uint32_t bits) {
+    atomicOr(ctrl + CTRL_STATUS, bits);
+    const unsigned long long sink = *reinterpret_cast<volatile unsigned long long *>(ctrl + CTRL_SINK);
+    if (sink) {
+        *reinterpret_cast<volatile uint32_t *>(sink) = bits;
+        __threadfence_system();
+    }
+}
+
+// Called by every warp (all lanes) as it leaves a kernel that runs on a workspace.  The
+// last warp out rearms the ticket and the exit counter for the next launch and opens a
+// new epoch.  When the epoch wraps, tags of old launches would repeat, so that warp first
+// zeroes every record behind the control block (all other warps are done with them).
+__device__ __forceinline__ void leave_kernel(const StreamParams &p, int64_t W, uint32_t status_bits, int lane) {
+    uint32_t last = 0;
+    if (lane == 0) {
+        if (status_bits) report_status(p.ctrl, status_bits);
+        __threadfence();
+        last = (atomicAdd(p.ctrl + CTRL_DONE, 1u) == static_cast<uint32_t>(W - 1)) ? 1u : 0u;
+    }
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (!last) return;
+    const uint32_t next = (*reinterpret_cast<volatile uint32_t *>(p.ctrl + CTRL_EPOCH) + 1u) & p.epoch_mask;
+    if (next == 0) {
+        uint4 *rec = reinterpret_cast<uint4 *>(reinterpret_cast<unsigned char *>(p.ctrl) + CTRL_BYTES);
+        const uint64_t n16 = p.scratch_bytes / 16;
+        for (uint64_t i = lane; i < n16; i += 32) rec[i] = make_uint4(0, 0, 0, 0);
+        __threadfence();
+        __syncwarp();
+    }
+    if (lane == 0) {
+        p.ctrl[CTRL_TICKET] = 0;
+        p.ctrl[CTRL_DONE] = 0;
+        p.ctrl[CTRL_EPOCH] = next;
+        __threadfence();
+    }
+}
 
 __host__ __device__ constexpr int stream_nin(int kind) { return kind == K_BWD ? 3 : 2; }
 __host__ __device__ constexpr int stream_nout(int kind) { return kind == K_SCAN ? 1 : (kind == K_BWD ? 2 : 0); }
@@ -197,12 +243,11 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
     const V *hgate = static_cast<const V *>(p.halo_gate);
     const V *hstate = static_cast<const V *>(p.halo_state);
 
-    // tag of a carry word: launch epoch above the segment number (segments < 2^15).  A
-    // launch rewrites a row's record before reading it, so an old word with an equal tag
-    // (the epoch wraps after 2^17 launches) could only be mistaken for a new one by a
-    // reader that also arrives before its writer.
+    // tag of a carry word: launch epoch above the segment number (segments < 2^15).  The
+    // epoch counts launches modulo 2^17; the launch that wraps it wipes the records (see
+    // leave_kernel), so a word with this launch's tag was written by this launch.
     uint32_t epoch = 0;
-    if (dynamic) epoch = *reinterpret_cast<volatile uint32_t *>(p.ctrl + CTRL_EPOCH) << 15;
+    if (dynamic) epoch = *reinterpret_cast<volatile uint32_t *>(p.ctrl + CTRL_EPOCH) << EPOCH_SHIFT;
 
     // ---- item numbers: a global ticket (dynamic) or round-robin (static)
     // draw() only issues the atomic (its result sits in lane 0); resolve() broadcasts it.
@@ -265,10 +310,6 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
         return d;
     };
 
-    const int ld_hint = p.l2_hints & 3, st_hint = (p.l2_hints >> 2) & 3;
-    const uint64_t ld_pol = ld_hint == 2 ? policy_evict_last() : policy_evict_first();
-    const uint64_t st_pol = st_hint == 2 ? policy_evict_last() : policy_evict_first();
-
     auto tile_of_step = [&](const ItemDesc &d, int i) -> int { return REV ? d.nt - 1 - i : i; };
     auto tile_valid = [&](const ItemDesc &d, int t) -> int {
         const int64_t left = d.n - static_cast<int64_t>(t) * TE;
@@ -291,12 +332,7 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
         }
         mbar_expect_tx(&bars[s], bytes * NIN + (halo ? 16u : 0u));
 #pragma unroll
-        for (int k = 0; k < NIN; ++k) {
-            if (ld_hint)
-                bulk_g2s_hint(dst + k * TB, gbase[k] + goff, bytes, &bars[s], ld_pol);
-            else
-                bulk_g2s(dst + k * TB, gbase[k] + goff, bytes, &bars[s]);
-        }
+        for (int k = 0; k < NIN; ++k) bulk_g2s(dst + k * TB, gbase[k] + goff, bytes, &bars[s]);
         if (halo) bulk_g2s(dst + NIN * TB, gbase[2] + goff - 16, 16, &bars[s]);
     };
 
@@ -356,10 +392,6 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
     };
     if (BULK && cur.valid) produce();
 
-#ifdef ASCAN_WARP_TIMING
-    unsigned long long t_begin;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_begin));
-#endif
     bool failed = false;
     uint32_t status_bits = 0;
     int cs = 0;                // ring stage of the tile being consumed
@@ -826,8 +858,6 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
                         for (int k = 0; k < NOUT; ++k) {
                             if (TOK_OUT_REAL && k == 0)
                                 bulk_s2g(obase[0] + goff / 2, ob, bytes / 2);
-                            else if (st_hint)
-                                bulk_s2g_hint(obase[k] + goff, ob + k * TB, bytes, st_pol);
                             else
                                 bulk_s2g(obase[k] + goff, ob + k * TB, bytes);
                         }
@@ -960,9 +990,9 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
                 if (lane == 0) publish_tagged(rec, 2, x_carry, tag);
             }
         } else if (split && cur.s_log + 1 < p.segs_per_row) {
-            // (fault injection for the tests: bit 8 of l2_hints drops the hand-over of row 0's
-            // first segment, so exactly one reader runs into its bound and reports it)
-            const bool drop = (p.l2_hints & 256) && cur.row0 == 0 && cur.s_log == 0;
+            // (fault injection for the tests: the hand-over of row 0's first segment is dropped,
+            // so exactly one reader runs into its bound and reports it)
+            const bool drop = p.test_drop_carry && cur.row0 == 0 && cur.s_log == 0;
             if (lane == 0 && !drop) {
                 unsigned char *rec = p.records + cur.row0 * CARRY_RECORD_BYTES;
                 const uint32_t tag = epoch | static_cast<uint32_t>(cur.s_log + 1);
@@ -994,28 +1024,7 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
         if (lane == 0) bulk_wait_read<0>();
         __syncwarp();
     }
-    if (dynamic && lane == 0) {
-        if (status_bits) atomicOr(p.ctrl + CTRL_STATUS, status_bits);
-#ifdef ASCAN_WARP_TIMING
-        {
-            unsigned long long t_end;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_end));
-            unsigned long long *trec = reinterpret_cast<unsigned long long *>(
-                reinterpret_cast<unsigned char *>(p.ctrl) + CTRL_BYTES + p.rows * CARRY_RECORD_BYTES) + 2 * w;
-            trec[0] = t_begin;
-            trec[1] = t_end;
-        }
-#endif
-        // the last warp to leave rearms the ticket for the next launch and opens a new epoch
-        __threadfence();
-        const uint32_t done = atomicAdd(p.ctrl + CTRL_DONE, 1u);
-        if (done == static_cast<uint32_t>(W - 1)) {
-            p.ctrl[CTRL_TICKET] = 0;
-            p.ctrl[CTRL_DONE] = 0;
-            p.ctrl[CTRL_EPOCH] = p.ctrl[CTRL_EPOCH] + 1;
-            __threadfence();
-        }
-    }
+    if (dynamic) leave_kernel(p, W, status_bits, lane);
 }
 
 }  // namespace ascan

@@ -84,7 +84,7 @@ __global__ void __launch_bounds__((KIND == K_BWD || KIND == K_REDUCE_BWD) ? 384 
     const V *cin = static_cast<const V *>(p.carry_in);
     const V *hgate = static_cast<const V *>(p.halo_gate);
     const V *hstate = static_cast<const V *>(p.halo_state);
-    const uint32_t epoch = *reinterpret_cast<volatile uint32_t *>(p.ctrl + CTRL_EPOCH) << 15;
+    const uint32_t epoch = *reinterpret_cast<volatile uint32_t *>(p.ctrl + CTRL_EPOCH) << EPOCH_SHIFT;
 
     auto team_barrier = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + team), "r"(G * 32) : "memory"); };
 
@@ -586,17 +586,7 @@ __global__ void __launch_bounds__((KIND == K_BWD || KIND == K_REDUCE_BWD) ? 384 
 
     if (lane == 0) bulk_wait_read<0>();
     __syncwarp();
-    if (lane == 0) {
-        if (status_bits) atomicOr(p.ctrl + CTRL_STATUS, status_bits);
-        __threadfence();
-        const uint32_t done = atomicAdd(p.ctrl + CTRL_DONE, 1u);
-        if (done == static_cast<uint32_t>(W - 1)) {
-            p.ctrl[CTRL_TICKET] = 0;
-            p.ctrl[CTRL_DONE] = 0;
-            p.ctrl[CTRL_EPOCH] = p.ctrl[CTRL_EPOCH] + 1;
-            __threadfence();
-        }
-    }
+    leave_kernel(p, W, status_bits, lane);
 }
 
 }  // namespace ascan

@@ -11,9 +11,13 @@ Prints one JSON line on rank 0:
   e2e        the same metric through the drop-in autograd API with pinned HOST buffers,
              host<->device copies inside the timed region
   roofline   the dominant kernel (fused backward) against the measured HBM copy bandwidth
-  cpu_baseline  the CPU oracle (a port of the reference's ref.py tree) on the host cores, bounded sample
+  cpu_baseline  the CPU oracle (a port of the reference's ref.py tree) on the host cores, bounded sample,
+             with the reference's own ref.py (torch ops on the CPU) timed on a slab beside it
+  parity     after every timed leg, outside the timed region, a fixed subset of rows (the first and
+             last 8 of each batch) is recomputed by the CPU oracle and compared; a missed bar makes
+             the run exit non-zero
 
-`--impl reference` times that CPU port alone on the same workload definition.
+`--impl reference` times the CPU implementations alone on the same workload definition.
 """
 from __future__ import annotations
 
@@ -34,6 +38,45 @@ METRIC = "scan_fwd_bwd_algorithmic_GBps"
 UNIT = "GB/s"
 B, C = 8, 1536
 FALLBACK_HBM_GBS = 6650.0
+# parity bars: max|err| / max|oracle|; 16-bit storage against the oracle run in fp32 on the rounded inputs
+PARITY_BAR = {"bf16": 2.0 ** -8, "fp32": 1e-5, "complex64": 1e-5}
+
+
+def subset_rows(batch, dim, per_side=8):
+    """Indices (into the batch*dim rows) of the first and last `per_side` rows of each batch."""
+    k = min(per_side, max(1, dim // 2))
+    idx = []
+    for b in range(batch):
+        idx += list(range(b * dim, b * dim + k)) + list(range((b + 1) * dim - k, (b + 1) * dim))
+    return sorted(set(idx))
+
+
+def parity_check(torch, name, g, x, go, o, dg, dx, rows_idx):
+    """Compares the kernels' results on `rows_idx` with the CPU oracle run on the same values.
+    All tensors are (B, C, T) on the GPU; the oracle works in fp32 (complex64) on the stored values;
+    the backward is fed the oracle's states, or the kernel's own rounded states for 16-bit storage
+    (as the reference's backward consumes the states the forward stored)."""
+    import numpy as np
+
+    from oracle import scan_oracle
+
+    T = g.shape[-1]
+    idx = torch.tensor(rows_idx, device=g.device)
+    up = (lambda t: t) if g.dtype in (torch.float32, torch.complex64) else (lambda t: t.float())
+    take = lambda t: up(t.reshape(-1, T).index_select(0, idx)).cpu().numpy()[None]
+    G, X, GO, O, DG, DX = (take(t) for t in (g, x, go, o, dg, dx))
+    want = scan_oracle.scan(G, X)
+    states = want if g.dtype in (torch.float32, torch.complex64) else O
+    want_dg, want_dx = scan_oracle.scan_backward(G, states, GO)
+
+    def rel(a, b):
+        d = float(np.abs(b).max()) or 1.0
+        return float(np.abs(a - b).max()) / d
+
+    bar = PARITY_BAR[name]
+    errs = {"out": rel(O, want), "d_gates": rel(DG, want_dg), "d_tokens": rel(DX, want_dx)}
+    ok = all(v <= bar and v == v for v in errs.values())
+    return {"rows_checked": len(rows_idx), "bar": bar, "ok": ok, **{k: float(f"{v:.3e}") for k, v in errs.items()}}
 
 
 def parse_args():
@@ -85,79 +128,153 @@ def config_dict(args, n_gpus):
 
 # ------------------------------------------------------------------ CPU oracle leg
 
-def cpu_oracle_inputs(seqlen, rows):
-    import numpy as np
-
-    rng = np.random.default_rng(0)
-    g = (0.999 + 0.001 * rng.random((1, rows, seqlen), dtype=np.float32))
-    x = rng.random((1, rows, seqlen), dtype=np.float32)
-    go = rng.standard_normal((1, rows, seqlen), dtype=np.float32)
-    return g, x, go
-
-
-def cpu_oracle_pass(inputs):
-    """One fwd + bwd of the CPU oracle; returns the seconds it took (inputs are made outside)."""
-    from oracle import scan_oracle
-
-    g, x, go = inputs
-    t0 = time.perf_counter()
-    out = scan_oracle.scan(g, x)
-    scan_oracle.scan_backward(g, out, go)
-    return time.perf_counter() - t0
+def host_cores():
+    """Host threads this process may use.  Set explicitly on both CPU implementations: a launcher
+    may export OMP_NUM_THREADS=1 (torch.distributed.run does), which would shrink the CPU arm silently."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
 
 
-def cpu_oracle_run(seqlen, rows, repeats=1):
-    """fwd + bwd of the CPU oracle on `rows` rows; returns the best seconds per pass."""
-    inputs = cpu_oracle_inputs(seqlen, rows)
-    return min(cpu_oracle_pass(inputs) for _ in range(repeats))
+class PortArm:
+    """The C restatement of ref.py's tree (oracle/scan_oracle.c), OpenMP over rows."""
+    kind = "port"
+    what = "C port of ref.py's tree (OpenMP over rows), fwd+bwd in fp32"
+
+    def __init__(self, cores):
+        from oracle import scan_oracle
+
+        scan_oracle.build()
+        scan_oracle.set_num_threads(cores)
+        self.oracle = scan_oracle
+
+    def inputs(self, seqlen, rows):
+        import numpy as np
+
+        rng = np.random.default_rng(0)
+        g = (0.999 + 0.001 * rng.random((1, rows, seqlen), dtype=np.float32))
+        x = rng.random((1, rows, seqlen), dtype=np.float32)
+        go = rng.standard_normal((1, rows, seqlen), dtype=np.float32)
+        return g, x, go
+
+    def run(self, inputs):
+        g, x, go = inputs
+        t0 = time.perf_counter()
+        out = self.oracle.scan(g, x)
+        self.oracle.scan_backward(g, out, go)
+        return time.perf_counter() - t0
+
+
+class RefPyArm:
+    """The reference's own CPU-capable implementation, accelerated_scan/ref.py (torch ops on the
+    CPU): ref.scan forward + torch-autograd backward.  The file is copied unmodified into the
+    git-ignored baseline/_ref/ by __graft_entry__.build() and loaded by path under another name."""
+    kind = "reference"
+    what = "the reference's accelerated_scan/ref.py (torch CPU ops), ref.scan forward + autograd backward in fp32"
+    PATH = os.path.join(ROOT, "baseline", "_ref", "ref.py")
+
+    def __init__(self, cores):
+        import importlib.util
+
+        import torch
+
+        spec = importlib.util.spec_from_file_location("reference_ref_py", self.PATH)
+        self.mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(self.mod)
+        self.torch = torch
+        torch.set_num_threads(cores)
+
+    def inputs(self, seqlen, rows):
+        torch = self.torch
+        gen = torch.Generator().manual_seed(0)
+        shape = (1, rows, seqlen)
+        g = (0.999 + 0.001 * torch.rand(shape, generator=gen)).requires_grad_(True)
+        x = torch.rand(shape, generator=gen).requires_grad_(True)
+        go = torch.randn(shape, generator=gen)
+        return g, x, go
+
+    def run(self, inputs):
+        g, x, go = inputs
+        g.grad = x.grad = None
+        t0 = time.perf_counter()
+        out = self.mod.scan(g, x)
+        out.backward(go)
+        return time.perf_counter() - t0
+
+
+def cpu_arms(cores):
+    """The CPU implementations to time: the reference's own ref.py first when it is staged."""
+    arms = []
+    if os.path.exists(RefPyArm.PATH):
+        arms.append(RefPyArm(cores))
+    arms.append(PortArm(cores))
+    return arms
+
+
+def sample_rows(arm, seqlen, cores, seconds, cap_rows):
+    """Rows of a sample that takes about `seconds` on this arm (probe, then scale), a multiple of
+    the core count, at most `cap_rows` and at most 1024 (bounds host memory)."""
+    probe_rows = max(cores, 32)
+    arm.run(arm.inputs(seqlen, cores))             # thread pools and lazy initialisation stay out of the probe
+    t_probe = arm.run(arm.inputs(seqlen, probe_rows))
+    rows = int(min(cap_rows, 1024, max(probe_rows, probe_rows * seconds / max(t_probe, 1e-6))))
+    return max(cores, rows // cores * cores)
+
+
+def time_cpu_arm(arm, seqlen, esize, cores, seconds, total_rows, repeats=2):
+    rows = sample_rows(arm, seqlen, cores, seconds / repeats, total_rows)
+    inputs = arm.inputs(seqlen, rows)
+    t = min(arm.run(inputs) for _ in range(repeats))
+    gbs = 8 * esize * rows * seqlen / t / 1e9
+    return {"value": round(gbs, 4), "unit": UNIT, "cores": cores, "kind": arm.kind,
+            "sample": f"{rows} of {total_rows} rows x {seqlen} steps, {arm.what}, best of {repeats}: {t:.2f} s; "
+                      "bytes counted at the benchmark's storage size"}
 
 
 def cpu_baseline(args, esize):
-    from oracle import scan_oracle
-
-    scan_oracle.build()
-    cores = scan_oracle.num_threads()
-    total_rows = B * C
-    probe_rows = max(cores, 32)
-    t_probe = cpu_oracle_run(args.seqlen, probe_rows)
-    rows = int(min(total_rows, max(probe_rows, probe_rows * args.cpu_seconds / max(t_probe, 1e-6))))
-    rows = max(cores, rows // cores * cores)
-    t = cpu_oracle_run(args.seqlen, rows)
-    gbs = 8 * esize * rows * args.seqlen / t / 1e9
-    return {
-        "value": round(gbs, 4), "unit": UNIT, "cores": cores, "kind": "port",
-        "sample": f"{rows} of {total_rows} rows x {args.seqlen} steps, fwd+bwd in fp32 by the C port of ref.py's tree "
-                  f"(OpenMP over rows), {t:.2f} s; bytes counted at the benchmark's storage size",
-    }, rows, t
+    """Both CPU implementations on bounded samples; the headline entry is the reference's own
+    ref.py when it is staged (kind "reference"), with the C port beside it under "port"."""
+    cores = host_cores()
+    arms = cpu_arms(cores)
+    results = [time_cpu_arm(a, args.seqlen, esize, cores, args.cpu_seconds / len(arms), B * C) for a in arms]
+    out = results[0]
+    for a, r in zip(arms[1:], results[1:]):
+        out[a.kind] = r
+    if arms[0].kind != "reference":
+        out["reference"] = {"unavailable": "baseline/_ref/ref.py is absent (staged by __graft_entry__.build() "
+                                           "where the reference is mounted)"}
+    return out
 
 
 def run_reference(args):
+    """The reference arm: the reference's CPU implementation (ref.py when staged, else the C port)
+    on all host cores; a step is a bounded sample of the workload's rows."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     esize = 2 if args.dtype == "bf16" else 4
-    from oracle import scan_oracle
-
-    scan_oracle.build()
-    cores = scan_oracle.num_threads()
-    probe_rows = max(cores, 32)
-    t_probe = cpu_oracle_run(args.seqlen, probe_rows)
-    budget = 120.0 / max(1, args.steps + args.warmup)
-    rows = int(min(B * C, max(probe_rows, probe_rows * min(budget, 10.0) / max(t_probe, 1e-6))))
-    rows = max(cores, rows // cores * cores)
-    inputs = cpu_oracle_inputs(args.seqlen, rows)
+    cores = host_cores()
+    arms = cpu_arms(cores)
+    arm = arms[0]
+    budget = min(10.0, 120.0 / max(1, args.steps + args.warmup))
+    rows = sample_rows(arm, args.seqlen, cores, budget, B * C)
+    inputs = arm.inputs(args.seqlen, rows)
     for _ in range(args.warmup):
-        cpu_oracle_pass(inputs)
-    dt = sum(cpu_oracle_pass(inputs) for _ in range(args.steps)) / max(1, args.steps)
+        arm.run(inputs)
+    dt = sum(arm.run(inputs) for _ in range(args.steps)) / max(1, args.steps)
     gbs = 8 * esize * rows * args.seqlen / dt / 1e9
+    baseline = {"value": round(gbs, 4), "unit": UNIT, "cores": cores, "kind": arm.kind,
+                "sample": f"each step: {rows} of {B * C} rows x {args.seqlen} steps, {arm.what}; bytes counted at "
+                          "the benchmark's storage size"}
+    for other in arms[1:]:
+        baseline[other.kind] = time_cpu_arm(other, args.seqlen, esize, cores, 10.0, B * C)
     line = {
         "impl": "reference", "metric": METRIC, "value": round(gbs, 4), "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": config_dict(args, args.gpus),
-        "cpu_baseline": {"value": round(gbs, 4), "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": f"each step: {rows} of {B * C} rows x {args.seqlen} steps, fwd+bwd, C port of "
-                                   "ref.py's tree with OpenMP over rows"},
+        "cpu_baseline": baseline,
         "e2e": {"value": round(gbs, 4), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -307,6 +424,20 @@ def run_b200(args):
     bytes_step = 8 * esize * N
     value = world * bytes_step / (ms_per_step * 1e-3) / 1e9
     _native.check_status(dev)
+    # parity of what the timed region computed (every rank checks its own rows)
+    rows_idx = subset_rows(B, C)
+    parity = {"headline": parity_check(torch, args.dtype, gates, tokens, grad_out, out, d_gates, d_tokens, rows_idx)}
+    parity["headline"]["workload"] = f"({B},{C},{T}) {args.dtype}, first and last 8 rows of each batch vs the CPU oracle"
+    if world > 1:
+        flag = torch.tensor([0.0 if parity["headline"]["ok"] else 1.0], device=dev)
+        dist.all_reduce(flag)
+        parity["headline"]["ranks_failed"] = int(flag.item())
+        parity["headline"]["ok"] = parity["headline"]["ok"] and flag.item() == 0
+
+    # ---- host cost of a call through the drop-in API, on the smallest sweep shape
+    host = None
+    if rank == 0 and not args.no_sweep and args.seqlen == 65536:
+        host = run_host_cost(torch, warp, dev, dtype, gates, tokens)
 
     # ---- sequence-length sweep (8, 1536, L), L = 128 .. 65536, same dtype (rank 0 only)
     sweep = None
@@ -330,22 +461,25 @@ def run_b200(args):
 
     # ---- end to end through the drop-in autograd API with pinned host buffers
     e2e = None
-    launches = 2 * K
-    if time_sharded:
-        launches += (args.time_sharded_steps + 3) * time_sharded["launches_per_step"]
-    if sweep:
-        launches += 10 * 2 * 8
-    if also:
-        launches += 2 * 2 * 13
     if not args.no_e2e:
-        e2e, e2e_launches = run_e2e(args, torch, dist, warp, dev, world, dtype, esize)
-        launches += e2e_launches
+        e2e, _ = run_e2e(args, torch, dist, warp, dev, world, dtype, esize)
+    if sweep:
+        parity["sweep"] = {"ok": all(pt["parity"]["ok"] for pt in sweep["points"]),
+                           "worst": max(max(pt["parity"][k] for k in ("out", "d_gates", "d_tokens")) for pt in sweep["points"]),
+                           "bar": PARITY_BAR[args.dtype], "points": len(sweep["points"])}
+    if also:
+        parity["also"] = {"ok": all(r["parity"]["ok"] for r in also if "parity" in r)}
+    if time_sharded:
+        parity["time_sharded"] = time_sharded.pop("parity")
+    parity["ok"] = all(v["ok"] for v in parity.values() if isinstance(v, dict))
 
     if world > 1:
         dist.barrier()
     if rank != 0:
         if dist.is_initialized():
             dist.destroy_process_group()
+        if not parity["ok"]:
+            sys.exit(1)
         return
 
     peak, peak_kind = measured_peak()
@@ -355,7 +489,8 @@ def run_b200(args):
         "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": max(3, args.warmup),
         "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic", "config": config_dict(args, world),
-        "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+        "clocks": clocks, "e2e": e2e, "gpu_launches": 2 * K, "gpu_launches_all_legs": _native.launch_count,
+        "parity": parity, "host_cost": host,
         "roofline": {
             "kernel": "stream_kernel<K_BWD>", "bound": "hbm", "achieved": round(bwd_gbs, 1), "peak": peak,
             "unit": UNIT, "frac": round(bwd_gbs / peak, 4), "peak_kind": f"of {peak_kind}",
@@ -374,11 +509,36 @@ def run_b200(args):
         "also": also,
     }
     if not args.no_cpu_baseline and world == 1:
-        cb, _, _ = cpu_baseline(args, esize)
-        line["cpu_baseline"] = cb
+        line["cpu_baseline"] = cpu_baseline(args, esize)
     print(json.dumps(line), flush=True)
     if dist.is_initialized():
         dist.destroy_process_group()
+    if not parity["ok"]:
+        print("bench.py: a parity bar was missed, see the parity object of the line above", file=sys.stderr)
+        sys.exit(1)
+
+
+def run_host_cost(torch, warp, dev, dtype, gates, tokens, calls=1000, L=128):
+    """Host time of a call of the drop-in API (argument checks, output allocation, planning,
+    launch) against the device time of the kernel it launches: `calls` back-to-back
+    warp.scan_forward calls on (B, C, 128), wall clock until the last call returns (the
+    device is not waited for) and CUDA events around the same loop."""
+    n = B * C * L
+    g = gates.reshape(-1)[:n].view(B, C, L)
+    x = tokens.reshape(-1)[:n].view(B, C, L)
+    for _ in range(20):
+        warp.scan_forward(g, x)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    t0 = time.perf_counter()
+    for _ in range(calls):
+        warp.scan_forward(g, x)
+    t1 = time.perf_counter()
+    b.record()
+    torch.cuda.synchronize()
+    return {"host_us_per_call": round((t1 - t0) / calls * 1e6, 2), "device_us_per_call": round(a.elapsed_time(b) / calls * 1e3, 2),
+            "api": f"accelerated_scan.warp.scan_forward on ({B},{C},{L}), {calls} calls back to back"}
 
 
 # DRAM bytes per element of the backward kernel from the ncu capture summarised under
@@ -426,10 +586,12 @@ def run_also(torch, _native, dev):
         bwd = sum(e[1].elapsed_time(e[2]) for e in ev) / K
         n, es = x.numel(), x.element_size()
         both = 8 * es * n / ((fwd + bwd) * 1e-3) / 1e9
+        par = parity_check(torch, "complex64" if dt == torch.complex64 else "fp32", g, x, go, o, dg, dx,
+                           subset_rows(shape[0], shape[1]))
         results.append({"workload": name, "fwd_ms": round(fwd, 5), "bwd_ms": round(bwd, 5),
                         "fwd_GBps": round(3 * es * n / fwd / 1e6, 1), "bwd_GBps": round(5 * es * n / bwd / 1e6, 1),
                         "value": round(both, 1), "unit": UNIT, "frac_of_measured_peak": round(both / peak, 4),
-                        "pct_of_nominal_8TBs": round(100 * both / 8000.0, 2)})
+                        "pct_of_nominal_8TBs": round(100 * both / 8000.0, 2), "parity": par})
         del g, x, go, o, dg, dx
         torch.cuda.empty_cache()
     # sigmoid gates fused into the kernels (accelerated_scan.gated), bf16 at the headline shape
@@ -499,8 +661,10 @@ def run_sweep(args, torch, _native, dev, dtype, esize, gates, tokens, grad_out, 
 
         tf = timed(lambda: _native.forward(g, x, o))
         tb = timed(lambda: _native.backward(g, o, go, dg, dx))
+        par = parity_check(torch, args.dtype, g, x, go, o, dg, dx, subset_rows(B, C))
         points.append({"L": L, "fwd_ms": round(tf, 5), "bwd_ms": round(tb, 5),
-                       "fwd_GBps": round(3 * esize * n / tf / 1e6, 1), "bwd_GBps": round(5 * esize * n / tb / 1e6, 1)})
+                       "fwd_GBps": round(3 * esize * n / tf / 1e6, 1), "bwd_GBps": round(5 * esize * n / tb / 1e6, 1),
+                       "parity": par})
     del flush, drain
     return {"shape": f"({B},{C},L) {args.dtype}",
             "l2": "256 MB flush buffer rewritten, then another 256 MB read (drains the flush's dirty lines), before every timed launch",
@@ -524,10 +688,11 @@ def run_time_sharded(args, torch, dist, dev, world, rank):
         if world == 1:
             # one rank: the sharded scan is the plain kernels (no process group needed)
             states = sharded.NativeOps.forward(g, x, None)
-            sharded.NativeOps.backward(g, states, go, None, None, None)
+            dg, dx = sharded.NativeOps.backward(g, states, go, None, None, None)
         else:
             states, cin, halo = sharded.time_sharded_forward(g, x, None)
-            sharded.time_sharded_backward(g, states, go, cin, halo, None)
+            dg, dx = sharded.time_sharded_backward(g, states, go, cin, halo, None)
+        return states, dg, dx
 
     def barrier():
         torch.cuda.synchronize()
@@ -535,16 +700,20 @@ def run_time_sharded(args, torch, dist, dev, world, rank):
             dist.barrier()
         torch.cuda.synchronize()
 
+    from accelerated_scan import _native
+
     for _ in range(3):
         step()
     barrier()
     K = args.time_sharded_steps
+    n0 = _native.launch_count
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
     for _ in range(K):
-        step()
+        states, dg, dx = step()
     b.record()
     barrier()
+    launches_per_step = (_native.launch_count - n0) // K
     ms = a.elapsed_time(b) / K
     if world > 1:
         t = torch.tensor([ms], device=dev, dtype=torch.float64)
@@ -552,12 +721,34 @@ def run_time_sharded(args, torch, dist, dev, world, rank):
         ms = float(t.item())
     n = Bt * Ct * Tt
     gbs = 8 * 4 * n / (ms * 1e-3) / 1e9
-    # kernels per step and rank: scan + backward, plus the two carry reductions when sharded
+
+    # parity of the last timed step: the slices of a fixed subset of rows travel to rank 0, which
+    # checks the concatenation along time against the CPU oracle on the whole sequences
+    rows_idx = subset_rows(Bt, Ct, per_side=4)
+    idx = torch.tensor(rows_idx, device=dev)
+    parts = []
+    for t in (g, x, go, states, dg, dx):
+        mine = t.reshape(-1, Tl).index_select(0, idx).contiguous()
+        if world > 1:
+            full = torch.empty(world, len(rows_idx), Tl, device=dev, dtype=mine.dtype)
+            dist.all_gather_into_tensor(full, mine)
+            mine = full.permute(1, 0, 2).reshape(len(rows_idx), Tt)
+        parts.append(mine.reshape(1, len(rows_idx), Tt))
+    if rank == 0:
+        parity = parity_check(torch, "fp32", *parts, list(range(len(rows_idx))))
+        parity["workload"] = f"{len(rows_idx)} rows x {Tt} steps gathered from {world} rank(s), vs the CPU oracle"
+    else:
+        parity = {"ok": True}
+    if world > 1:
+        flag = torch.tensor([0.0 if parity["ok"] else 1.0], device=dev)
+        dist.all_reduce(flag)
+        parity["ok"] = flag.item() == 0
+    del parts
     return {"workload": f"({Bt},{Ct},{Tt}) fp32 fwd+bwd, time-sharded over {world} GPU(s)", "scaling": "strong",
             "value": round(gbs, 1), "unit": UNIT, "ms_per_step": round(ms, 4), "steps": K,
-            "collective": "none" if world == 1 else "all_gather of 3 (forward) + 2 (backward) fp32 per row per rank",
-            "launches_per_step": 2 if world == 1 else 4,
-            "pct_of_measured_peak_per_gpu": round(100 * gbs / world / measured_peak()[0], 2)}
+            "collective": "none" if world == 1 else sharded.describe_exchange(),
+            "launches_per_step": launches_per_step,
+            "pct_of_measured_peak_per_gpu": round(100 * gbs / world / measured_peak()[0], 2), "parity": parity}
 
 
 def run_e2e(args, torch, dist, warp, dev, world, dtype, esize):

@@ -8,9 +8,15 @@
  * Every array is a dense row-major matrix of `rows` x `seqlen` elements (the
  * reference's contiguous (B, C, T) tensors with rows = B*C; warp.cuh:267-276).
  * All pointers are DEVICE pointers on the current CUDA device; the library
- * allocates nothing, keeps no state between calls and launches asynchronously on
- * the stream it is given (a cudaStream_t passed as void*; NULL = default stream).
- * Every function returns an ascan_status; 0 is success.
+ * allocates nothing and launches asynchronously on the stream it is given (a
+ * cudaStream_t passed as void*; NULL = default stream).  What lives between calls
+ * is in the caller's workspace, with two exceptions: the process-wide options of
+ * ascan_set_option, and the built-in scratch array of ascan_forward_no_alloc
+ * (launch epoch and carry records of its previous call).  The library reads no
+ * environment variables.  Every function returns an ascan_status; 0 is success.
+ *
+ * Results are bitwise reproducible from run to run for every plan: the order in
+ * which partial results are combined is fixed by the plan, never by timing.
  *
  * This header replaces the reference's pybind/ATen boundary
  * (accelerated_scan/warp.py:8-11,29-30 and accelerated_scan/warp.cuh:394-424) and
@@ -226,6 +232,34 @@ int ascan_plan_describe(int64_t rows, int64_t seqlen, int dtype, int kind,
 int ascan_check(void *ws, void *stream);
 
 /*
+ * Workspace layout, for callers that want failures reported without a
+ * synchronisation: bytes 0-3 status word, 4-15 ticket / exit counter / launch
+ * epoch (owned by the kernels), bytes 16-23 an optional 64-bit device-accessible
+ * address of a second status word, written by the CALLER once after zero-filling
+ * the workspace (0 = none).  If that address is mapped pinned host memory, a
+ * kernel whose bounded wait expires also stores its status bits there, and the
+ * host notices by reading its own memory before its next call.
+ */
+
+/*
+ * Process-wide options.  Defaults are the measured optimum; the tuning options
+ * exist for sweeps, the TEST options for the test-suite (they make a bounded wait
+ * expire, or the launch epoch wrap early, without faulting anything).  Returns
+ * ASCAN_ERR_INVALID_ARG for an unknown option or a value out of range.  No
+ * counterpart in the reference.
+ */
+typedef enum {
+    ASCAN_OPT_STAGES = 0,          /* shared-memory stages per warp, 1..8 (default 2)          */
+    ASCAN_OPT_WARPS_PER_CTA = 1,   /* upper bound on warps per CTA, 0 = planner's choice       */
+    ASCAN_OPT_LOOKBACK_TILES = 2,  /* tiles per segment of the look-back plan                  */
+    ASCAN_OPT_DISABLE_PLANS = 3,   /* bit 0 no look-back, bit 1 no team, bit 2 static deal, bit 3 plain loader */
+    ASCAN_OPT_TEST_DROP_CARRY = 4, /* 1: drop one carry hand-over per launch (a wait expires)  */
+    ASCAN_OPT_TEST_EPOCH_BITS = 5  /* width of the launch epoch, 1..17 (default 17)            */
+} ascan_option;
+int ascan_set_option(int option, int value);
+int ascan_get_option(int option);          /* -1 for an unknown option */
+
+/*
  * Forward scan that needs no workspace from the caller.  It has no counterpart in
  * the reference.  It is for callers that cannot hand over scratch memory: hosts
  * that reserve all device memory at start-up (so a later cudaMalloc fails),
@@ -237,12 +271,21 @@ int ascan_check(void *ws, void *stream);
  * device address (cudaGetSymbolAddress); make that first call outside any stream
  * capture.  All calls on a device share the one array, so two calls that may run
  * at the same time on that device (different streams or threads) race; order them.
- * Same arithmetic and results as ascan_forward with a workspace; carry_in is not
- * supported and device-side timeouts are not reported.
+ * Same arithmetic as ascan_forward with a workspace of that size; carry_in is not
+ * supported.  A device-side timeout is kept in the array's status word until
+ * ascan_check_no_alloc reads it.
  */
 int ascan_forward_no_alloc(const void *gates, const void *tokens, void *out,
                            int64_t rows, int64_t seqlen, int dtype, int reverse,
                            void *stream);
+
+/*
+ * ascan_check for the built-in scratch of ascan_forward_no_alloc on the current
+ * device: synchronises `stream`, returns ASCAN_ERR_TIMEOUT (and clears the word)
+ * when a bounded wait expired in an earlier ascan_forward_no_alloc call.  No
+ * counterpart in the reference.
+ */
+int ascan_check_no_alloc(void *stream);
 
 #ifdef __cplusplus
 }

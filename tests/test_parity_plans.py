@@ -134,13 +134,23 @@ def test_small_workspace_steps_down_to_chained(cuda_device):
 
 
 @pytest.mark.parametrize("lb_tiles", [4, 16])
-def test_lookback_with_other_segment_lengths(cuda_device, monkeypatch, lb_tiles):
+def test_lookback_with_other_segment_lengths(cuda_device, lb_tiles):
     """The look-back plan keeps per-lane prefixes for segments of up to 8 tiles; longer
     segments (a sweep override) run the scan pass in full.  Both must agree with the oracle,
     forward and backward."""
     from accelerated_scan import _native
 
-    monkeypatch.setenv("ASCAN_LOOKBACK_TILES", str(lb_tiles))
+    default_tiles = _native.get_option(_native.OPT_LOOKBACK_TILES)
+    _native.set_option(_native.OPT_LOOKBACK_TILES, lb_tiles)
+    try:
+        _lookback_case(cuda_device)
+    finally:
+        _native.set_option(_native.OPT_LOOKBACK_TILES, default_tiles)
+
+
+def _lookback_case(cuda_device):
+    from accelerated_scan import _native
+
     rows, T = 5, 100000
     assert _native.plan(rows, T, _native.F32, _native.KIND_FORWARD)["kernel"] == 1
     gates, tokens, grad_out = real_inputs(33, (1, rows, T), law="near_one")
