@@ -82,6 +82,23 @@ def _load():
     lib.ascan_forward_no_alloc.argtypes = [vp, vp, vp, i64, i64, i32, i32, vp]
     lib.ascan_check_no_alloc.restype = i32
     lib.ascan_check_no_alloc.argtypes = [vp]
+    u32 = ctypes.c_uint32
+    lib.ascan_exchange_bytes.restype = sz
+    lib.ascan_exchange_bytes.argtypes = [i64, i32]
+    lib.ascan_workspace_bytes_time_sharded.restype = sz
+    lib.ascan_workspace_bytes_time_sharded.argtypes = [i64, i64, i32, i32]
+    lib.ascan_forward_time_sharded.restype = i32
+    lib.ascan_forward_time_sharded.argtypes = [vp, vp, vp, i64, i64, i32, i32, i32, u32, vp, vp, vp, sz, vp]
+    lib.ascan_backward_time_sharded.restype = i32
+    lib.ascan_backward_time_sharded.argtypes = [vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, u32, vp, vp, vp, sz, vp]
+    lib.ascan_peer_alloc.restype = i32
+    lib.ascan_peer_alloc.argtypes = [sz, ctypes.POINTER(ctypes.c_void_p), vp]
+    lib.ascan_peer_open.restype = i32
+    lib.ascan_peer_open.argtypes = [vp, ctypes.POINTER(ctypes.c_void_p)]
+    lib.ascan_peer_close.restype = i32
+    lib.ascan_peer_close.argtypes = [vp]
+    lib.ascan_peer_free.restype = i32
+    lib.ascan_peer_free.argtypes = [vp]
     lib.ascan_set_option.restype = i32
     lib.ascan_set_option.argtypes = [i32, i32]
     lib.ascan_get_option.restype = i32
@@ -97,6 +114,8 @@ EXPORTS = (
     "ascan_forward_no_alloc", "ascan_fold_carries", "ascan_forward_complex_real_tokens",
     "ascan_forward_sigmoid_gates", "ascan_backward_sigmoid_gates", "ascan_backward_complex_real_tokens",
     "ascan_check_no_alloc", "ascan_set_option", "ascan_get_option",
+    "ascan_exchange_bytes", "ascan_workspace_bytes_time_sharded", "ascan_forward_time_sharded",
+    "ascan_backward_time_sharded", "ascan_peer_alloc", "ascan_peer_open", "ascan_peer_close", "ascan_peer_free",
 )
 
 OPT_STAGES, OPT_WARPS_PER_CTA, OPT_LOOKBACK_TILES, OPT_DISABLE_PLANS, OPT_TEST_DROP_CARRY, OPT_TEST_EPOCH_BITS = range(6)
@@ -150,6 +169,11 @@ def _require_cuda(*tensors):
             raise RuntimeError("accelerated_scan runs on CUDA tensors only (no CPU path)")
 
 
+def _raw_stream(device) -> int:
+    """cudaStream_t of torch's current stream on `device`, as an integer."""
+    return torch._C._cuda_getCurrentRawStream(device.index)
+
+
 def _rows_T(t):
     T = t.shape[-1]
     return (t.numel() // T if T else 0), T
@@ -181,7 +205,9 @@ class Workspace:
 
     def raise_if_failed(self):
         if self.sink_np[0]:
+            # reported here: clear both copies of the status (the device word in stream order)
             self.sink_np[0] = 0
+            self.tensor[0:4].zero_()
             raise RuntimeError("accelerated_scan: a bounded device-side wait expired in an earlier launch on this "
                                "stream; its result is invalid (ascan status 4)")
 
@@ -210,7 +236,7 @@ def _workspace(device, stream, rows, seqlen, dtype, kind) -> Workspace:
 def workspace(device: torch.device, rows: int = 0, seqlen: int = 1, dtype: int = 0, kind: int = 0) -> torch.Tensor:
     """The scratch tensor launches on the current stream of `device` use (see Workspace)."""
     device = torch.device(device)
-    stream = torch.cuda.current_stream(device).cuda_stream
+    stream = _raw_stream(device)
     return _workspace(device, stream, int(rows), int(seqlen), int(dtype), int(kind)).tensor
 
 
@@ -242,7 +268,7 @@ def forward(gates, tokens, out, reverse=False, carry_in=None):
     rows, T = _rows_T(gates)
     code = dtype_code(gates)
     dev = gates.device
-    stream = torch.cuda.current_stream(dev).cuda_stream
+    stream = _raw_stream(dev)
     ws = _workspace(dev, stream, rows, T, code, KIND_FORWARD)
     with _device_guard(dev):
         rc = lib.ascan_forward(gates.data_ptr(), tokens.data_ptr(), out.data_ptr(), rows, T, code, int(bool(reverse)),
@@ -260,7 +286,7 @@ def forward_complex_real_tokens(gates, tokens_real, out, reverse=False) -> bool:
     _require_cuda(gates, tokens_real, out)
     rows, T = _rows_T(gates)
     dev = gates.device
-    stream = torch.cuda.current_stream(dev).cuda_stream
+    stream = _raw_stream(dev)
     ws = _workspace(dev, stream, rows, T, C64, KIND_FORWARD)
     with _device_guard(dev):
         rc = lib.ascan_forward_complex_real_tokens(gates.data_ptr(), tokens_real.data_ptr(), out.data_ptr(), rows, T,
@@ -277,7 +303,7 @@ def backward_complex_real_tokens(gates, states, grad_out, d_gates, d_tokens_real
     _require_cuda(gates, states, grad_out, d_gates, d_tokens_real)
     rows, T = _rows_T(gates)
     dev = gates.device
-    stream = torch.cuda.current_stream(dev).cuda_stream
+    stream = _raw_stream(dev)
     ws = _workspace(dev, stream, rows, T, C64, KIND_BACKWARD)
     with _device_guard(dev):
         rc = lib.ascan_backward_complex_real_tokens(gates.data_ptr(), states.data_ptr(), grad_out.data_ptr(),
@@ -296,7 +322,7 @@ def forward_sigmoid_gates(gate_logits, tokens, out) -> bool:
     rows, T = _rows_T(gate_logits)
     code = dtype_code(gate_logits)
     dev = gate_logits.device
-    stream = torch.cuda.current_stream(dev).cuda_stream
+    stream = _raw_stream(dev)
     ws = _workspace(dev, stream, rows, T, code, KIND_FORWARD)
     with _device_guard(dev):
         rc = lib.ascan_forward_sigmoid_gates(gate_logits.data_ptr(), tokens.data_ptr(), out.data_ptr(), rows, T, code,
@@ -313,7 +339,7 @@ def backward_sigmoid_gates(gate_logits, states, grad_out, d_logits, d_tokens) ->
     rows, T = _rows_T(gate_logits)
     code = dtype_code(gate_logits)
     dev = gate_logits.device
-    stream = torch.cuda.current_stream(dev).cuda_stream
+    stream = _raw_stream(dev)
     ws = _workspace(dev, stream, rows, T, code, KIND_BACKWARD)
     with _device_guard(dev):
         rc = lib.ascan_backward_sigmoid_gates(gate_logits.data_ptr(), states.data_ptr(), grad_out.data_ptr(),
@@ -330,7 +356,7 @@ def backward(gates, states, grad_out, d_gates, d_tokens, carry_in=None, halo_gat
     rows, T = _rows_T(gates)
     code = dtype_code(gates)
     dev = gates.device
-    stream = torch.cuda.current_stream(dev).cuda_stream
+    stream = _raw_stream(dev)
     ws = _workspace(dev, stream, rows, T, code, KIND_BACKWARD)
     with _device_guard(dev):
         rc = lib.ascan_backward(gates.data_ptr(), states.data_ptr(), grad_out.data_ptr(), d_gates.data_ptr(),
@@ -344,7 +370,7 @@ def reduce_forward(gates, tokens, carry_out):
     rows, T = _rows_T(gates)
     code = dtype_code(gates)
     dev = gates.device
-    stream = torch.cuda.current_stream(dev).cuda_stream
+    stream = _raw_stream(dev)
     ws = _workspace(dev, stream, rows, T, code, KIND_REDUCE_FORWARD)
     with _device_guard(dev):
         rc = lib.ascan_reduce_forward(gates.data_ptr(), tokens.data_ptr(), carry_out.data_ptr(), rows, T, code,
@@ -357,12 +383,88 @@ def reduce_backward(gates, grad_out, halo_gate_right, carry_out):
     rows, T = _rows_T(gates)
     code = dtype_code(gates)
     dev = gates.device
-    stream = torch.cuda.current_stream(dev).cuda_stream
+    stream = _raw_stream(dev)
     ws = _workspace(dev, stream, rows, T, code, KIND_REDUCE_BACKWARD)
     with _device_guard(dev):
         rc = lib.ascan_reduce_backward(gates.data_ptr(), grad_out.data_ptr(), _ptr(halo_gate_right),
                                        carry_out.data_ptr(), rows, T, code, ws.ptr, ws.nbytes, stream)
     _finish(rc, "ascan_reduce_backward", ws, stream)
+
+
+def _sharded_workspace(dev, stream, rows, T, code, kind) -> Workspace:
+    key = ("time_sharded", rows, T, code, kind)
+    nbytes = _needs.get(key)
+    if nbytes is None:
+        nbytes = int(lib.ascan_workspace_bytes_time_sharded(rows, T, code, kind))
+        _needs[key] = nbytes
+    wkey = (dev.index, stream)
+    ws = _workspaces.get(wkey)
+    if ws is None or ws.nbytes < nbytes:
+        ws = Workspace(dev, max(4096, 2 * nbytes))
+        _workspaces[wkey] = ws
+    ws.raise_if_failed()
+    return ws
+
+
+def forward_time_sharded(gates, tokens, out, rank: int, world: int, call: int, exchange_ptrs, carry_save=None):
+    """This rank's slice of a time-sharded forward scan (ascan_forward_time_sharded).
+    exchange_ptrs: `world` integers, the ranks' forward exchange buffers as mapped here."""
+    _require_cuda(gates, tokens, out, carry_save)
+    rows, T = _rows_T(gates)
+    code = dtype_code(gates)
+    dev = gates.device
+    stream = _raw_stream(dev)
+    ws = _sharded_workspace(dev, stream, rows, T, code, KIND_FORWARD)
+    table = (ctypes.c_void_p * world)(*exchange_ptrs) if world > 1 else None
+    with _device_guard(dev):
+        rc = lib.ascan_forward_time_sharded(gates.data_ptr(), tokens.data_ptr(), out.data_ptr(), rows, T, code,
+                                            int(rank), int(world), int(call), table, _ptr(carry_save), ws.ptr,
+                                            ws.nbytes, stream)
+    _finish(rc, "ascan_forward_time_sharded", ws, stream)
+
+
+def backward_time_sharded(gates, states, grad_out, d_gates, d_tokens, rank: int, world: int, call: int, exchange_ptrs,
+                          halo_state_left=None):
+    """This rank's slice of the fused backward of a time-sharded scan (ascan_backward_time_sharded).
+    exchange_ptrs: the ranks' backward exchange buffers; halo_state_left: carry_save of the forward."""
+    _require_cuda(gates, states, grad_out, d_gates, d_tokens, halo_state_left)
+    rows, T = _rows_T(gates)
+    code = dtype_code(gates)
+    dev = gates.device
+    stream = _raw_stream(dev)
+    ws = _sharded_workspace(dev, stream, rows, T, code, KIND_BACKWARD)
+    table = (ctypes.c_void_p * world)(*exchange_ptrs) if world > 1 else None
+    with _device_guard(dev):
+        rc = lib.ascan_backward_time_sharded(gates.data_ptr(), states.data_ptr(), grad_out.data_ptr(), d_gates.data_ptr(),
+                                             d_tokens.data_ptr(), rows, T, code, int(rank), int(world), int(call), table,
+                                             _ptr(halo_state_left), ws.ptr, ws.nbytes, stream)
+    _finish(rc, "ascan_backward_time_sharded", ws, stream)
+
+
+def exchange_bytes(rows: int, world: int) -> int:
+    return int(lib.ascan_exchange_bytes(int(rows), int(world)))
+
+
+def peer_alloc(nbytes: int):
+    """(device pointer, 64-byte inter-process handle) of a zero-filled peer-visible buffer."""
+    ptr = ctypes.c_void_p()
+    handle = ctypes.create_string_buffer(64)
+    check(lib.ascan_peer_alloc(int(nbytes), ctypes.byref(ptr), handle), "ascan_peer_alloc")
+    return int(ptr.value), handle.raw
+
+
+def peer_open(handle: bytes) -> int:
+    ptr = ctypes.c_void_p()
+    check(lib.ascan_peer_open(ctypes.create_string_buffer(handle, 64), ctypes.byref(ptr)), "ascan_peer_open")
+    return int(ptr.value)
+
+
+def peer_close(ptr: int) -> None:
+    check(lib.ascan_peer_close(ptr), "ascan_peer_close")
+
+
+def peer_free(ptr: int) -> None:
+    check(lib.ascan_peer_free(ptr), "ascan_peer_free")
 
 
 def fold_carries(gathered, rank: int, suffix: bool, want_halo: bool = False):
@@ -375,7 +477,7 @@ def fold_carries(gathered, rank: int, suffix: bool, want_halo: bool = False):
     code = C64 if gathered.dtype == torch.complex64 else F32
     with _device_guard(gathered.device):
         rc = lib.ascan_fold_carries(gathered.data_ptr(), rows, world, int(rank), stride, code, int(bool(suffix)),
-                                    state.data_ptr(), _ptr(halo), torch.cuda.current_stream(gathered.device).cuda_stream)
+                                    state.data_ptr(), _ptr(halo), _raw_stream(gathered.device))
     check(rc, "ascan_fold_carries")
     return state, halo
 
@@ -384,7 +486,7 @@ def check_status(device=None) -> None:
     """Synchronise the current stream of `device` and raise if a bounded device-side wait
     expired in an earlier launch on it."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    stream = torch.cuda.current_stream(device).cuda_stream
+    stream = _raw_stream(device)
     ws = _workspaces.get((device.index, stream))
     if ws is None:
         return

@@ -2,6 +2,7 @@
 // argument validation, planning, kernel dispatch, launch-error reporting.
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <string.h>
 
 #include <atomic>
 #include <mutex>
@@ -9,6 +10,7 @@
 #include "../../include/ascan_b200.h"
 #include "launch.h"
 #include "planner.h"
+#include "lookback.cuh"
 #include "stream.cuh"
 
 namespace ascan {
@@ -34,7 +36,7 @@ static int cached_sm_count(int *out) {
 }
 
 // ---- options (ascan_set_option): process-wide, read on every call, never from the environment
-static std::atomic<int> g_opt_stages{2}, g_opt_wpc{0}, g_opt_lookback_tiles{8}, g_opt_disable_plans{0};
+static std::atomic<int> g_opt_stages{2}, g_opt_wpc{0}, g_opt_lookback_tiles{0}, g_opt_disable_plans{0};
 static std::atomic<int> g_opt_drop_carry{0}, g_opt_epoch_bits{17};
 static std::atomic<uint32_t> g_opt_generation{0};
 
@@ -74,7 +76,7 @@ static int make_plan_cached(const PlanInput &in, ascan_plan *pl) {
     k.kind = in.kind;
     k.sm_count = in.sm_count;
     k.flags = (in.reverse ? 1u : 0u) | (in.aligned ? 2u : 0u) | (in.workspace ? 4u : 0u) | (in.allow_lookback ? 8u : 0u) |
-              (in.allow_team ? 16u : 0u) | (in.three_chunks ? 32u : 0u);
+              (in.allow_team ? 16u : 0u) | (in.three_chunks ? 32u : 0u) | (in.force_lookback ? 64u : 0u);
     k.generation = g_opt_generation.load(std::memory_order_relaxed);
     for (int i = 0; i < memo.used; ++i) {
         if (memo.key[i] == k) {
@@ -93,12 +95,12 @@ static int make_plan_cached(const PlanInput &in, ascan_plan *pl) {
 }
 
 static int launch_by_dtype(int dtype, int variant, int kind, bool reverse, const StreamParams &p, const ascan_plan &pl,
-                           cudaStream_t st) {
+                           cudaStream_t st, const ShardParams *sp = nullptr) {
     switch (dtype) {
-        case ASCAN_F32: return launch_f32(variant, kind, reverse, p, pl, st);
-        case ASCAN_BF16: return launch_bf16(variant, kind, reverse, p, pl, st);
-        case ASCAN_F16: return launch_f16(variant, kind, reverse, p, pl, st);
-        case ASCAN_C64: return launch_c64(variant, kind, reverse, p, pl, st);
+        case ASCAN_F32: return launch_f32(variant, kind, reverse, p, pl, st, sp);
+        case ASCAN_BF16: return launch_bf16(variant, kind, reverse, p, pl, st, sp);
+        case ASCAN_F16: return launch_f16(variant, kind, reverse, p, pl, st, sp);
+        case ASCAN_C64: return launch_c64(variant, kind, reverse, p, pl, st, sp);
         default: return ASCAN_ERR_INVALID_ARG;
     }
 }
@@ -361,7 +363,7 @@ int ascan_set_option(int option, int value) {
             g_opt_wpc.store(value);
             break;
         case ASCAN_OPT_LOOKBACK_TILES:
-            if (value < 1 || value > 64) return ASCAN_ERR_INVALID_ARG;
+            if (value < 0 || value > 8) return ASCAN_ERR_INVALID_ARG;
             g_opt_lookback_tiles.store(value);
             break;
         case ASCAN_OPT_DISABLE_PLANS:
@@ -494,6 +496,159 @@ int ascan_fold_carries(const void *gathered, int64_t rows, int world, int rank, 
                                                               static_cast<float *>(halo_out));
     }
     return cudaGetLastError() == cudaSuccess ? ASCAN_OK : ASCAN_ERR_LAUNCH;
+}
+
+size_t ascan_exchange_bytes(int64_t rows, int world) {
+    if (rows < 0 || world < 1 || world > MAX_WORLD) return 0;
+    return static_cast<size_t>(xchg_bytes(rows, world));
+}
+
+size_t ascan_workspace_bytes_time_sharded(int64_t rows, int64_t seqlen, int dtype, int kind) {
+    PlanInput in;
+    in.rows = rows;
+    in.seqlen = seqlen < 1 ? 1 : seqlen;
+    in.dtype = dtype;
+    in.kind = kind;
+    in.aligned = true;
+    in.workspace = true;
+    in.reverse = false;
+    in.force_lookback = true;
+    in.tune = current_tuning();
+    if (cached_sm_count(&in.sm_count) != ASCAN_OK) {
+        cudaGetLastError();
+        in.sm_count = 148;
+    }
+    ascan_plan pl;
+    if (make_plan_cached(in, &pl) != ASCAN_OK) return 0;
+    return static_cast<size_t>(pl.workspace_bytes);
+}
+
+// Plan and shard parameters shared by the two time-sharded entry points.
+static int plan_time_sharded(int64_t rows, int64_t seqlen, int dtype, int kind, int rank, int world, uint32_t call,
+                             void *const *exchange, void *ws, size_t ws_bytes, ascan_plan *pl, ShardParams *sp) {
+    if (world < 1 || world > MAX_WORLD || rank < 0 || rank >= world || call == 0) return ASCAN_ERR_INVALID_ARG;
+    if (world > 1 && !exchange) return ASCAN_ERR_INVALID_ARG;
+    if (!ws || (reinterpret_cast<uintptr_t>(ws) & 255u) != 0) return ASCAN_ERR_WORKSPACE;
+    PlanInput in;
+    in.reverse = false;
+    in.rows = rows;
+    in.seqlen = seqlen;
+    in.dtype = dtype;
+    in.kind = kind;
+    in.aligned = true;
+    in.workspace = true;
+    in.force_lookback = true;
+    in.tune = current_tuning();
+    int rc = cached_sm_count(&in.sm_count);
+    if (rc != ASCAN_OK) return rc;
+    rc = make_plan_cached(in, pl);
+    if (rc != ASCAN_OK) return rc;
+    if (pl->workspace_bytes > ws_bytes) return ASCAN_ERR_WORKSPACE;
+    *sp = ShardParams{};
+    sp->rank = rank;
+    sp->world = world;
+    sp->call = call;
+    for (int j = 0; j < world && world > 1; ++j) {
+        if (!exchange[j] || (reinterpret_cast<uintptr_t>(exchange[j]) & 15u) != 0) return ASCAN_ERR_INVALID_ARG;
+        sp->xchg[j] = static_cast<unsigned char *>(exchange[j]);
+    }
+    return ASCAN_OK;
+}
+
+int ascan_forward_time_sharded(const void *gates, const void *tokens, void *out, int64_t rows, int64_t seqlen,
+                               int dtype, int rank, int world, uint32_t call, void *const *exchange, void *carry_save,
+                               void *ws, size_t ws_bytes, void *stream) {
+    if (rows < 0 || seqlen < 1 || dtype_size(dtype) == 0) return ASCAN_ERR_INVALID_ARG;
+    if (rows == 0) return ASCAN_OK;
+    if (!gates || !tokens || !out) return ASCAN_ERR_INVALID_ARG;
+    if (!(aligned16(gates) && aligned16(tokens) && aligned16(out))) return ASCAN_ERR_UNSUPPORTED;
+    ascan_plan pl;
+    ShardParams sp;
+    int rc = plan_time_sharded(rows, seqlen, dtype, ASCAN_KIND_FORWARD, rank, world, call, exchange, ws, ws_bytes, &pl, &sp);
+    if (rc != ASCAN_OK) return rc;
+    sp.carry_save = carry_save;
+    StreamParams p = {};
+    p.in0 = gates;
+    p.in1 = tokens;
+    p.out0 = out;
+    fill_common(p, pl, rows, seqlen, ws, ws_bytes);
+    return launch_by_dtype(dtype, VARIANT_PLAIN, ASCAN_KIND_FORWARD, false, p, pl, static_cast<cudaStream_t>(stream), &sp);
+}
+
+int ascan_backward_time_sharded(const void *gates, const void *states, const void *grad_out, void *d_gates,
+                                void *d_tokens, int64_t rows, int64_t seqlen, int dtype, int rank, int world,
+                                uint32_t call, void *const *exchange, const void *halo_state_left, void *ws,
+                                size_t ws_bytes, void *stream) {
+    if (rows < 0 || seqlen < 1 || dtype_size(dtype) == 0) return ASCAN_ERR_INVALID_ARG;
+    if (rows == 0) return ASCAN_OK;
+    if (!gates || !states || !grad_out || !d_gates || !d_tokens) return ASCAN_ERR_INVALID_ARG;
+    if (!(aligned16(gates) && aligned16(states) && aligned16(grad_out) && aligned16(d_gates) && aligned16(d_tokens)))
+        return ASCAN_ERR_UNSUPPORTED;
+    ascan_plan pl;
+    ShardParams sp;
+    int rc = plan_time_sharded(rows, seqlen, dtype, ASCAN_KIND_BACKWARD, rank, world, call, exchange, ws, ws_bytes, &pl, &sp);
+    if (rc != ASCAN_OK) return rc;
+    StreamParams p = {};
+    p.in0 = gates;
+    p.in1 = grad_out;
+    p.in2 = states;
+    p.out0 = d_tokens;
+    p.out1 = d_gates;
+    p.halo_state = halo_state_left;
+    fill_common(p, pl, rows, seqlen, ws, ws_bytes);
+    return launch_by_dtype(dtype, VARIANT_PLAIN, ASCAN_KIND_BACKWARD, true, p, pl, static_cast<cudaStream_t>(stream), &sp);
+}
+
+// ---- peer-visible buffers for the exchange of time-sharded scans (the only functions of
+// the library that allocate; nothing else calls them)
+int ascan_peer_alloc(size_t bytes, void **ptr, void *handle64) {
+    if (!ptr || !handle64 || bytes == 0) return ASCAN_ERR_INVALID_ARG;
+    void *d = nullptr;
+    if (cudaMalloc(&d, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return ASCAN_ERR_DEVICE;
+    }
+    cudaIpcMemHandle_t h;
+    if (cudaMemset(d, 0, bytes) != cudaSuccess || cudaIpcGetMemHandle(&h, d) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(d);
+        return ASCAN_ERR_DEVICE;
+    }
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    memcpy(handle64, &h, 64);
+    *ptr = d;
+    return ASCAN_OK;
+}
+
+int ascan_peer_open(const void *handle64, void **ptr) {
+    if (!handle64 || !ptr) return ASCAN_ERR_INVALID_ARG;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    void *d = nullptr;
+    if (cudaIpcOpenMemHandle(&d, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+        cudaGetLastError();
+        return ASCAN_ERR_DEVICE;
+    }
+    *ptr = d;
+    return ASCAN_OK;
+}
+
+int ascan_peer_close(void *ptr) {
+    if (!ptr) return ASCAN_ERR_INVALID_ARG;
+    if (cudaIpcCloseMemHandle(ptr) != cudaSuccess) {
+        cudaGetLastError();
+        return ASCAN_ERR_DEVICE;
+    }
+    return ASCAN_OK;
+}
+
+int ascan_peer_free(void *ptr) {
+    if (!ptr) return ASCAN_ERR_INVALID_ARG;
+    if (cudaFree(ptr) != cudaSuccess) {
+        cudaGetLastError();
+        return ASCAN_ERR_DEVICE;
+    }
+    return ASCAN_OK;
 }
 
 int ascan_check(void *ws, void *stream) {

@@ -11,6 +11,7 @@
 
 #include "launch.h"
 #include "planner.h"
+#include "lookback.cuh"
 #include "stream.cuh"
 #include "team.cuh"
 
@@ -40,20 +41,27 @@ static int launch_kernel(KFN kfn, const StreamParams &p, const ascan_plan &pl, c
     return cudaGetLastError() == cudaSuccess ? ASCAN_OK : ASCAN_ERR_LAUNCH;
 }
 
+// The look-back plan (bulk loader, three chunks per lane, the two scan kinds).
+template <class TR, int KIND, bool REVERSE>
+static int launch_lookback(const StreamParams &p, const ascan_plan &pl, cudaStream_t stream, const ShardParams *sp) {
+    auto kfn = lookback_kernel<TR, 3, KIND, REVERSE>;
+    int rc = ensure_smem(reinterpret_cast<const void *>(kfn));
+    if (rc != ASCAN_OK) return rc;
+    ShardParams none = {};
+    kfn<<<pl.grid, pl.warps_per_cta * 32, pl.smem_bytes, stream>>>(p, sp ? *sp : none);
+    return cudaGetLastError() == cudaSuccess ? ASCAN_OK : ASCAN_ERR_LAUNCH;
+}
+
 // INTERIOR: items that group several rows have row boundaries inside their tiles.
 template <class TR, int NCH, int KIND, bool REVERSE, bool BULK>
 static int launch_interior(const StreamParams &p, const ascan_plan &pl, cudaStream_t stream) {
-    // look-back plans exist for the bulk loader and the two scan kinds; team plans also for
-    // the carry-only kinds of the real dtypes
-    if constexpr (BULK && (KIND == K_SCAN || KIND == K_BWD)) {
-        if (pl.kernel == 1) return launch_kernel(stream_kernel<TR, NCH, KIND, REVERSE, BULK, false, true>, p, pl, stream);
-    }
+    // team plans exist for the bulk loader: the scan kinds, and the carry-only kinds of the real dtypes
     if constexpr (BULK && (KIND == K_SCAN || KIND == K_BWD || sizeof(typename TR::V) == 4)) {
         if (pl.kernel == 2) return launch_kernel(team_kernel<TR, NCH, KIND, REVERSE>, p, pl, stream);
     }
     if (pl.kernel != 0) return ASCAN_ERR_UNSUPPORTED;
-    return pl.rows_per_item > 1 ? launch_kernel(stream_kernel<TR, NCH, KIND, REVERSE, BULK, true, false>, p, pl, stream)
-                                : launch_kernel(stream_kernel<TR, NCH, KIND, REVERSE, BULK, false, false>, p, pl, stream);
+    return pl.rows_per_item > 1 ? launch_kernel(stream_kernel<TR, NCH, KIND, REVERSE, BULK, true>, p, pl, stream)
+                                : launch_kernel(stream_kernel<TR, NCH, KIND, REVERSE, BULK, false>, p, pl, stream);
 }
 
 template <class TR, int NCH, int KIND, bool REVERSE>
@@ -78,7 +86,16 @@ static int launch_nch(const StreamParams &p, const ascan_plan &pl, cudaStream_t 
 
 // The plain kinds of one element type.
 template <class TR>
-static int launch_plain(int kind, bool reverse, const StreamParams &p, const ascan_plan &pl, cudaStream_t stream) {
+static int launch_plain(int kind, bool reverse, const StreamParams &p, const ascan_plan &pl, cudaStream_t stream,
+                        const ShardParams *sp) {
+    if (pl.kernel == 1) {
+        if (pl.loader != 0 || pl.chunks_per_lane != 3) return ASCAN_ERR_UNSUPPORTED;
+        if (kind == ASCAN_KIND_FORWARD)
+            return reverse ? launch_lookback<TR, K_SCAN, true>(p, pl, stream, sp) : launch_lookback<TR, K_SCAN, false>(p, pl, stream, sp);
+        if (kind == ASCAN_KIND_BACKWARD) return launch_lookback<TR, K_BWD, true>(p, pl, stream, sp);
+        return ASCAN_ERR_UNSUPPORTED;
+    }
+    if (sp) return ASCAN_ERR_UNSUPPORTED;       // time sharding exists in the look-back plan only
     switch (kind) {
         case ASCAN_KIND_FORWARD:
             return reverse ? launch_nch<TR, K_SCAN, true>(p, pl, stream) : launch_nch<TR, K_SCAN, false>(p, pl, stream);
@@ -95,8 +112,8 @@ template <class TR>
 static int launch_sigmoid(int kind, const StreamParams &p, const ascan_plan &pl, cudaStream_t stream) {
     if (pl.chunks_per_lane != 3) return ASCAN_ERR_UNSUPPORTED;
     if (kind == ASCAN_KIND_FORWARD)
-        return launch_kernel(stream_kernel<TR, 3, K_SCAN, false, true, false, false, false, 1>, p, pl, stream);
-    return launch_kernel(stream_kernel<TR, 3, K_BWD, true, true, false, false, false, 1>, p, pl, stream);
+        return launch_kernel(stream_kernel<TR, 3, K_SCAN, false, true, false, false, 1>, p, pl, stream);
+    return launch_kernel(stream_kernel<TR, 3, K_BWD, true, true, false, false, 1>, p, pl, stream);
 }
 
 }  // namespace ascan

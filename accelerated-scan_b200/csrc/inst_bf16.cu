@@ -3,8 +3,9 @@
 
 namespace ascan {
 
-int launch_bf16(int variant, int kind, bool reverse, const StreamParams &p, const ascan_plan &pl, cudaStream_t st) {
-    if (variant == VARIANT_PLAIN) return launch_plain<TraitsBF16>(kind, reverse, p, pl, st);
+int launch_bf16(int variant, int kind, bool reverse, const StreamParams &p, const ascan_plan &pl, cudaStream_t st,
+               const ShardParams *sp) {
+    if (variant == VARIANT_PLAIN) return launch_plain<TraitsBF16>(kind, reverse, p, pl, st, sp);
     if (variant == VARIANT_SIGMOID) return launch_sigmoid<TraitsBF16>(kind, p, pl, st);
     return ASCAN_ERR_UNSUPPORTED;
 }

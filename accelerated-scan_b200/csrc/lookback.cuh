@@ -1,0 +1,643 @@
+// Look-back scan kernel: single pass, for matrices with clearly fewer rows than SMs and for
+// rows whose time axis is sharded over several GPUs.
+//
+// A row is cut into SEGMENTS of a few tiles; an item is one segment, items are numbered
+// row-major (all segments of row 0 in processing order, then row 1, ...) and drawn from
+// the ticket counter by persistent warps, so the segments of a handful of rows are in
+// flight at any time, spread over every SM.
+//
+// A warp keeps its whole segment in shared memory.  It
+//   1. loads the segment's tiles with bulk asynchronous copies (one stage per tile),
+//   2. computes the segment's AGGREGATE, the affine map x -> A*x + B from the state before
+//      the segment to the state after it, leaving in shared memory, per tile and lane, the
+//      map from the segment's start to the lane's first element,
+//   3. publishes the aggregate in the segment's record,
+//   4. composes the aggregates of all earlier segments of the row into its incoming state,
+//   5. runs the recurrence from shared memory (no second read of global memory), writes the
+//      results over the inputs in shared memory and stores them with bulk copies; a stage
+//      whose store has been read out is refilled with the matching tile of the next item.
+//
+// Step 4 never waits for another warp's step 4: it reads only aggregates, which depend on
+// nothing but their own segment's data.  Aggregates are kept at three levels -- segments,
+// blocks of 32 segments, super-blocks of 32 blocks; the warp that owns the last segment of a
+// block (super-block) composes and publishes the block's (super-block's) aggregate -- so a
+// look-back reads at most 31 records per level (plus one window per 32 super-blocks in very
+// long rows).  Which records are composed, and in which order, depends only on the segment's
+// number: results are bitwise reproducible.  Records are self-tagged 64-bit words (payload,
+// launch tag); every wait is bounded and ends in a status bit.
+//
+// Time sharding over GPUs (ShardParams.world > 1): every rank runs this kernel on its time
+// slice of all rows.  The warp that owns the last segment of a row's slice composes the
+// slice's aggregate and stores it, with plain 64-bit stores, into the exchange buffers of
+// the ranks that come later in processing order; a segment's incoming state is then the
+// fold, in rank order, of the earlier ranks' slice aggregates (read from this rank's own
+// exchange buffer) followed by the local look-back.  No rank waits for another rank's
+// results, only for its aggregates, so all ranks stream at the same time.
+#pragma once
+
+#include "stream.cuh"
+
+namespace ascan {
+
+constexpr int LB_RECORD_BYTES = 32;          // one affine pair of the compute type in tagged 64-bit words
+constexpr int LB_MAX_TILES = 8;              // tiles per segment (= shared-memory stages per warp), at most
+constexpr int MAX_WORLD = 16;                // ranks of a time-sharded scan, at most
+constexpr uint32_t LB_WAIT_POLLS = 1u << 20;      // about a second
+
+// Exchange buffer of one rank and one direction (forward or backward channel), written by the
+// other ranks with peer stores:
+//   [0, 256)                      done[src]: last call that rank `src` has completed (u64 each)
+//   [256, +2*rows*16)             gate halo per (call parity, row): first gate of the next rank's slice
+//   [.., +2*world*rows*32)        slice aggregates per (call parity, source rank, row)
+__host__ __device__ constexpr uint64_t xchg_halo_offset() { return 256; }
+__host__ __device__ constexpr uint64_t xchg_carry_offset(int64_t rows) { return 256 + 2ull * rows * 16; }
+__host__ __device__ constexpr uint64_t xchg_bytes(int64_t rows, int world) {
+    return xchg_carry_offset(rows) + 2ull * world * rows * LB_RECORD_BYTES;
+}
+
+struct ShardParams {
+    int32_t rank, world;              // world <= 1: the rows are not sharded along time
+    uint32_t call;                    // number of this call on the channel (same on every rank, 1, 2, 3, ...)
+    int32_t reserved;
+    unsigned char *xchg[MAX_WORLD];   // xchg[j]: exchange buffer of rank j as mapped in this process (xchg[rank]: local)
+    void *carry_save;                 // forward: rows values of the compute type, the state entering this rank's slice
+};
+
+__host__ __device__ constexpr int lb_stage_bytes(int nch, int kind) {
+    return stream_nin(kind) * 32 * nch * 16 + (kind == K_BWD ? 128 : 0);
+}
+__host__ __device__ constexpr int lb_warp_smem(int nch, int nt, int kind, int vsize) {
+    return nt * lb_stage_bytes(nch, kind) + 128 + nt * 32 * 2 * vsize;
+}
+// Workspace of the look-back plan: control block, then the records of the three levels.
+__host__ __device__ constexpr uint64_t lb_level_count(int64_t n) { return static_cast<uint64_t>((n + 31) / 32); }
+__host__ __device__ constexpr uint64_t lb_records_per_row(int64_t segs) {
+    return static_cast<uint64_t>(segs) + lb_level_count(segs) + lb_level_count(static_cast<int64_t>(lb_level_count(segs)));
+}
+
+__device__ __forceinline__ void st_relaxed_sys_u64(void *p, uint64_t v) {
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint64_t ld_relaxed_sys_u64(const void *p) {
+    uint64_t v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// ---- records: an affine pair (A, B) in tagged words.  SYS = the record crosses GPUs.
+template <bool SYS>
+__device__ __forceinline__ void put_word(unsigned char *p, float v, uint32_t tag) {
+    if (SYS) st_relaxed_sys_u64(p, tagged_word(v, tag));
+    else st_relaxed_u64(p, tagged_word(v, tag));
+}
+template <bool SYS>
+__device__ __forceinline__ bool get_word(const unsigned char *p, uint32_t tag, float &v) {
+    const uint64_t w = SYS ? ld_relaxed_sys_u64(p) : ld_relaxed_u64(p);
+    v = __uint_as_float(static_cast<uint32_t>(w));
+    return static_cast<uint32_t>(w >> 32) == tag;
+}
+template <bool SYS>
+__device__ __forceinline__ void put_pair(unsigned char *rec, float A, float B, uint32_t tag) {
+    put_word<SYS>(rec, A, tag);
+    put_word<SYS>(rec + 8, B, tag);
+}
+template <bool SYS>
+__device__ __forceinline__ void put_pair(unsigned char *rec, float2 A, float2 B, uint32_t tag) {
+    put_word<SYS>(rec, A.x, tag);
+    put_word<SYS>(rec + 8, A.y, tag);
+    put_word<SYS>(rec + 16, B.x, tag);
+    put_word<SYS>(rec + 24, B.y, tag);
+}
+template <bool SYS>
+__device__ __forceinline__ bool get_pair(const unsigned char *rec, uint32_t tag, float &A, float &B) {
+    const bool a = get_word<SYS>(rec, tag, A);
+    const bool b = get_word<SYS>(rec + 8, tag, B);
+    return a && b;
+}
+template <bool SYS>
+__device__ __forceinline__ bool get_pair(const unsigned char *rec, uint32_t tag, float2 &A, float2 &B) {
+    const bool a = get_word<SYS>(rec, tag, A.x);
+    const bool b = get_word<SYS>(rec + 8, tag, A.y);
+    const bool c = get_word<SYS>(rec + 16, tag, B.x);
+    const bool d = get_word<SYS>(rec + 24, tag, B.y);
+    return a && b && c && d;
+}
+
+// Composes the `n` (<= 32) records base[0], base[stride], ... in that order: on return every
+// lane holds (A, B) with  x -> A*x + B  = record n-1 after ... after record 0.  Lane i reads
+// record i and polls until it carries `tag`; false when the bound expires.  The combine is a
+// Kogge-Stone scan over the lanes with identity in the unused lanes: a fixed tree.
+template <class V, bool SYS>
+__device__ __forceinline__ bool compose_window(const unsigned char *base, int64_t stride, int n, uint32_t tag, int lane,
+                                               V &A, V &B) {
+    V a = vone(V()), b = vzero(V());
+    bool ok = lane >= n;
+    bool all = false;
+    for (uint32_t poll = 0; poll < LB_WAIT_POLLS; ++poll) {
+        if (!ok) ok = get_pair<SYS>(base + lane * stride, tag, a, b);
+        all = __all_sync(0xffffffffu, ok);
+        if (all) break;
+        if (poll > 8) __nanosleep(poll > 64 ? 200 : 40);
+    }
+    if (!all) {
+        A = vone(V());
+        B = vzero(V());
+        return false;
+    }
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const V Ap = shfl_up(a, d), Bp = shfl_up(b, d);
+        if (lane >= d) {
+            b = vfma(a, Bp, b);
+            a = vmul(a, Ap);
+        }
+    }
+    A = shfl_idx(a, 31);
+    B = shfl_idx(b, 31);
+    return true;
+}
+
+// KIND: K_SCAN (REVERSE selects the direction) or K_BWD.  Bulk loader, one segment per item.
+template <class TR, int NCH, int KIND, bool REVERSE>
+__global__ void __launch_bounds__(KIND == K_BWD ? 448 : 512, 1) lookback_kernel(const StreamParams p, const ShardParams sp) {
+    using V = typename TR::V;
+    constexpr int EPC = TR::EPC;
+    constexpr int K = NCH * EPC;
+    constexpr int TE = 32 * K;
+    constexpr int TB = 32 * NCH * 16;
+    constexpr bool BACK = (KIND == K_BWD);
+    constexpr bool REV = REVERSE || BACK;
+    constexpr int NIN = stream_nin(KIND);
+    constexpr int NOUT = stream_nout(KIND);
+    constexpr int STAGE_BYTES = lb_stage_bytes(NCH, KIND);
+    constexpr bool PACKED = sizeof(V) == 4 && (K % 2 == 0);
+    constexpr int H = K / 2;
+    const int NT = p.stages;                                  // tiles per segment
+    const int WARP_SMEM = lb_warp_smem(NCH, NT, KIND, sizeof(V));
+
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int lane = threadIdx.x & 31;
+    const int wib = threadIdx.x >> 5;
+    const int wpc = blockDim.x >> 5;
+    unsigned char *wsm = smem_raw + static_cast<size_t>(wib) * WARP_SMEM;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(wsm + NT * STAGE_BYTES);
+    V *lane_prefix = reinterpret_cast<V *>(wsm + NT * STAGE_BYTES + 128);
+
+    const int64_t W = static_cast<int64_t>(gridDim.x) * wpc;
+    const int64_t T = p.T;
+    const int64_t S = p.segs_per_row;
+    const int64_t L = p.seg_elems;
+    const unsigned char *gbase[3] = {static_cast<const unsigned char *>(p.in0), static_cast<const unsigned char *>(p.in1),
+                                     static_cast<const unsigned char *>(p.in2)};
+    unsigned char *obase[2] = {static_cast<unsigned char *>(p.out0), static_cast<unsigned char *>(p.out1)};
+    const V *cin = static_cast<const V *>(p.carry_in);
+    const V *hgate = static_cast<const V *>(p.halo_gate);
+    const V *hstate = static_cast<const V *>(p.halo_state);
+
+    const uint32_t tag = *reinterpret_cast<volatile uint32_t *>(p.ctrl + CTRL_EPOCH) + 1u;   // never zero
+    const uint64_t S1 = lb_level_count(S), S2 = lb_level_count(static_cast<int64_t>(S1));
+    const uint64_t per_row = static_cast<uint64_t>(S) + S1 + S2;
+    unsigned char *records = p.records;
+
+    // ---- time sharding
+    const bool sharded = sp.world > 1;
+    const int n_before = !sharded ? 0 : (REV ? sp.world - 1 - sp.rank : sp.rank);   // ranks earlier in processing order
+    const int n_after = !sharded ? 0 : (REV ? sp.rank : sp.world - 1 - sp.rank);
+    const uint32_t parity_slot = sp.call & 1u;
+    unsigned char *xl = sharded ? sp.xchg[sp.rank] : nullptr;
+    uint32_t status_bits = 0;
+
+    // backward: the first gate of every row of this slice is the gate halo of the rank before
+    if (BACK && sharded && sp.rank > 0) {
+        const int64_t w = static_cast<int64_t>(blockIdx.x) * wpc + wib;
+        unsigned char *peer = sp.xchg[sp.rank - 1];
+        // the slot was last used two calls ago: the receiver must have finished that call
+        bool ok = true;
+        if (sp.call > 2) {
+            ok = false;
+            for (uint32_t poll = 0; poll < LB_WAIT_POLLS && !ok; ++poll) {
+                ok = static_cast<int32_t>(static_cast<uint32_t>(ld_relaxed_sys_u64(xl + 8 * (sp.rank - 1))) - (sp.call - 2)) >= 0;
+                if (!ok) __nanosleep(200);
+            }
+        }
+        if (!ok) status_bits |= STATUS_LOOKBACK_TIMEOUT;
+        for (int64_t r = w * 32 + lane; r < p.rows; r += W * 32) {
+            const V g0 = TR::load_one(p.in0, r * T);
+            unsigned char *slot = peer + xchg_halo_offset() + (static_cast<uint64_t>(parity_slot) * p.rows + r) * 16;
+            if (ok) {
+                if constexpr (sizeof(V) == 4) {
+                    put_word<true>(slot, g0, sp.call);
+                } else {
+                    put_word<true>(slot, g0.x, sp.call);
+                    put_word<true>(slot + 8, g0.y, sp.call);
+                }
+            }
+        }
+    }
+
+    // ---- items
+    auto draw = [&]() -> uint32_t {
+        uint32_t t = 0;
+        if (lane == 0) t = atomicAdd(p.ctrl + CTRL_TICKET, 1u);
+        return t;
+    };
+    auto resolve = [&](uint32_t raw) -> int64_t { return __shfl_sync(0xffffffffu, raw, 0); };
+    auto describe = [&](int64_t q) -> ItemDesc {
+        ItemDesc d;
+        d.valid = q < p.items;
+        d.e_begin = 0; d.row0 = 0; d.pos0 = 0; d.s_log = 0; d.n = 0; d.nt = 0;
+        if (!d.valid) return d;
+        const uint32_t qq = static_cast<uint32_t>(q), ss = static_cast<uint32_t>(S);
+        const uint32_t row = qq / ss;
+        d.row0 = row;
+        d.s_log = static_cast<int32_t>(qq - row * ss);
+        const int64_t from_start = REV ? S - 1 - d.s_log : d.s_log;      // segments are aligned to the row start
+        d.pos0 = from_start * L;
+        d.e_begin = d.row0 * T + d.pos0;
+        const int64_t left = T - d.pos0;
+        d.n = left < L ? left : L;
+        d.nt = static_cast<int32_t>((d.n + TE - 1) / TE);
+        return d;
+    };
+    auto tile_of_step = [&](const ItemDesc &d, int i) -> int { return REV ? d.nt - 1 - i : i; };
+    auto tile_valid = [&](const ItemDesc &d, int t) -> int {
+        const int64_t left = d.n - static_cast<int64_t>(t) * TE;
+        return left < TE ? static_cast<int>(left) : TE;
+    };
+    // step i of an item lives in stage i.  Lane 0 arms the stage's mbarrier, then one lane per
+    // stream issues its copy (and one more the 16 bytes of saved states just below the tile).
+    auto issue = [&](const ItemDesc &d, int i) {
+        const int t = tile_of_step(d, i);
+        const uint32_t bytes = static_cast<uint32_t>(tile_valid(d, t)) * TR::ESIZE;
+        const int64_t goff = (d.e_begin + static_cast<int64_t>(t) * TE) * TR::ESIZE;
+        const bool halo = BACK && goff > 0;
+        unsigned char *dst = wsm + i * STAGE_BYTES;
+        if (lane == 0) mbar_expect_tx(&bars[i], bytes * NIN + (halo ? 16u : 0u));
+        __syncwarp();
+        if (lane < NIN) bulk_g2s(dst + lane * TB, gbase[lane] + goff, bytes, &bars[i]);
+        if (lane == NIN && halo) bulk_g2s(dst + NIN * TB, gbase[2] + goff - 16, 16, &bars[i]);
+    };
+
+    if (lane == 0) {
+        for (int s = 0; s < NT; ++s) mbar_init(&bars[s], 1);
+        mbar_init_fence();
+    }
+    __syncwarp();
+
+    // backward: the gate of the step right after a segment, loaded when the item is drawn and
+    // used an item later (the load's latency never shows)
+    using Raw = typename TR::Raw;
+    auto end_gate_raw = [&](const ItemDesc &d) -> Raw {
+        Raw r = 0;
+        if (BACK && d.valid && d.pos0 + d.n < T) r = TR::load_raw(p.in0, d.e_begin + d.n);
+        return r;
+    };
+    ItemDesc cur = describe(resolve(draw()));
+    if (cur.valid) {
+        for (int i = 0; i < cur.nt; ++i) issue(cur, i);
+    }
+    Raw cur_gate_raw = end_gate_raw(cur);
+    uint32_t phase_bits = 0;       // bit i: parity to wait for on stage i
+    bool failed = false;
+
+    while (cur.valid && !failed) {
+        const uint32_t raw_next = draw();          // resolved when the scan pass starts
+        const int64_t row = cur.row0;
+        const int s = cur.s_log;
+        unsigned char *row_rec = records + static_cast<uint64_t>(row) * per_row * LB_RECORD_BYTES;
+
+        // A wait that expires ends this warp's work: the status bit is set, the warp leaves after
+        // the aggregate pass (when none of its copies is in flight any more) and the launch's
+        // result is invalid.  Every warp gives up at its first expired wait, so a launch whose
+        // partner never shows up ends after about one bound, not one bound per item.
+        bool waits_ok = true;
+        // ---- what the segment needs from outside its own range (backward): the gate of the
+        // step right after it
+        V item_end_gate = vone(V());
+        if (BACK) {
+            if (cur.pos0 + cur.n < T) {
+                item_end_gate = TR::decode(cur_gate_raw);
+            } else if (sharded && sp.rank + 1 < sp.world) {
+                // first gate of the next rank's slice, stored into this rank's exchange buffer
+                const unsigned char *slot = xl + xchg_halo_offset() + (static_cast<uint64_t>(parity_slot) * p.rows + row) * 16;
+                bool got = false;
+                for (uint32_t poll = 0; poll < LB_WAIT_POLLS && !got; ++poll) {
+                    if constexpr (sizeof(V) == 4) {
+                        got = get_word<true>(slot, sp.call, item_end_gate);
+                    } else {
+                        const bool a = get_word<true>(slot, sp.call, item_end_gate.x);
+                        const bool b = get_word<true>(slot + 8, sp.call, item_end_gate.y);
+                        got = a && b;
+                    }
+                    if (!got) __nanosleep(100);
+                }
+                if (!got) {
+                    waits_ok = false;
+                    item_end_gate = vone(V());
+                }
+            } else if (hgate) {
+                item_end_gate = hgate[row];
+            }
+        }
+
+        // One tile from its stage into registers, ready for the two passes: a[] = the gates that
+        // multiply the state entering each element (shifted by one step for the backward), b[] =
+        // the additive terms; beyond the row's end the identity.
+        auto fetch = [&](int i, V *a, V *b, V &next_gate, int &nvalid) {
+            const int t = tile_of_step(cur, i);
+            nvalid = tile_valid(cur, t);
+            const unsigned char *stg = wsm + i * STAGE_BYTES;
+#pragma unroll
+            for (int c = 0; c < NCH; ++c) {
+                TR::unpack(*reinterpret_cast<const uint4 *>(stg + 0 * TB + (lane * NCH + c) * 16), &a[c * EPC]);
+                TR::unpack(*reinterpret_cast<const uint4 *>(stg + 1 * TB + (lane * NCH + c) * 16), &b[c * EPC]);
+            }
+            if (BACK) {
+                const V g0 = a[0];
+                V up = shfl_down(g0, 1);
+                if (lane == 31) up = next_gate;
+#pragma unroll
+                for (int j = 0; j < K - 1; ++j) a[j] = vconj(a[j + 1]);
+                a[K - 1] = vconj(up);
+                next_gate = shfl_idx(g0, 0);
+            }
+            if (nvalid < TE) {
+                const int jv = nvalid - lane * K;
+                const V gate_end = BACK ? vconj(item_end_gate) : vone(V());
+#pragma unroll
+                for (int j = 0; j < K; ++j) {
+                    if (j >= jv) {
+                        a[j] = vone(V());
+                        b[j] = vzero(V());
+                    } else if (BACK && j + 1 >= jv) {
+                        a[j] = gate_end;
+                    }
+                }
+            }
+        };
+
+        // ---------------- aggregate pass: lane prefixes and the segment's aggregate
+        V segA = vone(V()), segB = vzero(V());      // map from the segment's start to the current tile's start
+        {
+            V next_gate = item_end_gate;
+            for (int i = 0; i < cur.nt; ++i) {
+                bool ok = mbar_wait_bounded(&bars[i], (phase_bits >> i) & 1u, LOAD_WAIT_POLLS);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) {
+                    failed = true;
+                    status_bits |= STATUS_LOAD_TIMEOUT;
+                    break;
+                }
+                phase_bits ^= 1u << i;
+                V a[K], b[K];
+                int nvalid;
+                fetch(i, a, b, next_gate, nvalid);
+                V A, B;
+                if constexpr (PACKED) {
+                    auto J = [](int q) { return REV ? K - 1 - q : q; };
+                    float2 Av = make_float2(a[J(0)], a[J(H)]);
+                    float2 Bv = make_float2(b[J(0)], b[J(H)]);
+#pragma unroll
+                    for (int q = 1; q < H; ++q) {
+                        const float2 av = make_float2(a[J(q)], a[J(H + q)]);
+                        const float2 bv = make_float2(b[J(q)], b[J(H + q)]);
+                        Bv = __ffma2_rn(av, Bv, bv);
+                        Av = __fmul2_rn(Av, av);
+                    }
+                    A = Av.x * Av.y;
+                    B = fmaf(Av.y, Bv.x, Bv.y);
+                } else {
+                    constexpr int JF = REV ? K - 1 : 0;
+                    A = a[JF];
+                    B = b[JF];
+#pragma unroll
+                    for (int q = 1; q < K; ++q) {
+                        const int j = REV ? K - 1 - q : q;
+                        B = vfma(a[j], B, b[j]);
+                        A = vmul(A, a[j]);
+                    }
+                }
+                // inclusive Kogge-Stone over the lanes in processing order; the map that enters the
+                // tile (segA, segB) goes in through the first lane
+                const int ll = REV ? 31 - lane : lane;
+                if (ll == 0) {
+                    B = vfma(A, segB, B);
+                    A = vmul(A, segA);
+                }
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+                    const V Ap = REV ? shfl_down(A, d) : shfl_up(A, d);
+                    const V Bp = REV ? shfl_down(B, d) : shfl_up(B, d);
+                    if (ll >= d) {
+                        B = vfma(A, Bp, B);
+                        A = vmul(A, Ap);
+                    }
+                }
+                // map from the segment's start to this lane's first element
+                V pA = REV ? shfl_down(A, 1) : shfl_up(A, 1);
+                V pB = REV ? shfl_down(B, 1) : shfl_up(B, 1);
+                if (ll == 0) {
+                    pA = segA;
+                    pB = segB;
+                }
+                lane_prefix[(i * 32 + lane) * 2] = pA;
+                lane_prefix[(i * 32 + lane) * 2 + 1] = pB;
+                segA = shfl_idx(A, REV ? 0 : 31);
+                segB = shfl_idx(B, REV ? 0 : 31);
+            }
+        }
+        if (failed) break;
+
+        // ---------------- publish the aggregate, look back
+        if (lane == 0) put_pair<false>(row_rec + static_cast<uint64_t>(s) * LB_RECORD_BYTES, segA, segB, tag);
+        V preA = vone(V()), preB = vzero(V());         // map from the slice's start to the segment's start
+        bool lb_ok = waits_ok;
+        if (s > 0) {
+            const int n0 = s & 31, n1 = (s >> 5) & 31, n2 = s >> 10;
+            V A0 = vone(V()), B0 = vzero(V()), A1 = A0, B1 = B0;
+            // super-blocks 0 .. n2-1, 32 at a time
+            for (int w0 = 0; w0 < n2 && lb_ok; w0 += 32) {
+                V Aw, Bw;
+                const int n = n2 - w0 < 32 ? n2 - w0 : 32;
+                lb_ok = compose_window<V, false>(row_rec + (static_cast<uint64_t>(S) + S1 + w0) * LB_RECORD_BYTES,
+                                                 LB_RECORD_BYTES, n, tag, lane, Aw, Bw);
+                preB = vfma(Aw, preB, Bw);
+                preA = vmul(Aw, preA);
+            }
+            if (n1 > 0 && lb_ok)
+                lb_ok = compose_window<V, false>(row_rec + (static_cast<uint64_t>(S) + (static_cast<uint64_t>(s >> 10) << 5)) * LB_RECORD_BYTES,
+                                                 LB_RECORD_BYTES, n1, tag, lane, A1, B1);
+            if (n0 > 0 && lb_ok)
+                lb_ok = compose_window<V, false>(row_rec + (static_cast<uint64_t>(s >> 5) << 5) * LB_RECORD_BYTES,
+                                                 LB_RECORD_BYTES, n0, tag, lane, A0, B0);
+            // closing duties: the last segment of a block publishes the block, the last block of a
+            // super-block the super-block (only full ones are ever read)
+            if (n0 == 31) {
+                const V Ab = vmul(segA, A0), Bb = vfma(segA, B0, segB);          // this segment after the 31 before it
+                if (lane == 0) put_pair<false>(row_rec + (static_cast<uint64_t>(S) + (s >> 5)) * LB_RECORD_BYTES, Ab, Bb, tag);
+                if (n1 == 31) {
+                    const V Ac = vmul(Ab, A1), Bc = vfma(Ab, B1, Bb);
+                    if (lane == 0)
+                        put_pair<false>(row_rec + (static_cast<uint64_t>(S) + S1 + (s >> 10)) * LB_RECORD_BYTES, Ac, Bc, tag);
+                }
+            }
+            // super-blocks first, then blocks, then segments
+            preB = vfma(A1, preB, B1);
+            preA = vmul(A1, preA);
+            preB = vfma(A0, preB, B0);
+            preA = vmul(A0, preA);
+        }
+        // the slice ends with this segment: its aggregate goes to the ranks that come later
+        if (sharded && s == S - 1 && n_after > 0) {
+            const V Ps = vmul(segA, preA), Ss = vfma(segA, preB, segB);
+            if (lane < n_after) {
+                const int target = REV ? sp.rank - 1 - lane : sp.rank + 1 + lane;
+                bool ok = sp.call <= 2;
+                for (uint32_t poll = 0; poll < LB_WAIT_POLLS && !ok; ++poll) {
+                    ok = static_cast<int32_t>(static_cast<uint32_t>(ld_relaxed_sys_u64(xl + 8 * target)) - (sp.call - 2)) >= 0;
+                    if (!ok) __nanosleep(200);
+                }
+                if (ok) {
+                    unsigned char *slot = sp.xchg[target] + xchg_carry_offset(p.rows) +
+                                          ((static_cast<uint64_t>(parity_slot) * sp.world + sp.rank) * p.rows + row) * LB_RECORD_BYTES;
+                    put_pair<true>(slot, Ps, Ss, sp.call);
+                } else {
+                    lb_ok = false;
+                }
+            }
+            lb_ok = __all_sync(0xffffffffu, lb_ok);
+        }
+        // state entering the slice: the caller's, or the fold of the earlier ranks' aggregates
+        V x_slice = cin ? cin[row] : vzero(V());
+        if (n_before > 0 && lb_ok) {
+            // lane i reads the aggregate of the i-th rank in processing order
+            const int first = REV ? sp.world - 1 : 0;
+            const int64_t step = (REV ? -1 : 1) * static_cast<int64_t>(p.rows) * LB_RECORD_BYTES;
+            const unsigned char *base = xl + xchg_carry_offset(p.rows) +
+                                        ((static_cast<uint64_t>(parity_slot) * sp.world + first) * p.rows + row) * LB_RECORD_BYTES;
+            V Ar, Br;
+            lb_ok = compose_window<V, true>(base, step, n_before, sp.call, lane, Ar, Br);
+            x_slice = vfma(Ar, x_slice, Br);
+        }
+        // forward: the state entering the slice is what the backward needs below its first step
+        if (!REV && s == 0 && sp.carry_save && lane == 0) static_cast<V *>(sp.carry_save)[row] = x_slice;
+        if (!lb_ok) {
+            status_bits |= STATUS_LOOKBACK_TIMEOUT;
+            failed = true;
+            break;
+        }
+        const V x_in = vfma(preA, x_slice, preB);
+
+        // ---------------- scan pass from shared memory; stages are refilled as they drain
+        ItemDesc nxt = describe(resolve(raw_next));
+        const Raw nxt_gate_raw = end_gate_raw(nxt);
+        {
+            V next_gate = item_end_gate;
+            for (int i = 0; i < cur.nt; ++i) {
+                V a[K], b[K];
+                int nvalid;
+                fetch(i, a, b, next_gate, nvalid);
+                const int t = tile_of_step(cur, i);
+                const int64_t toff = static_cast<int64_t>(t) * TE;
+                unsigned char *stg = wsm + i * STAGE_BYTES;
+                V xp[BACK ? K : 1];
+                V x_below = vzero(V());
+                if (BACK) {
+#pragma unroll
+                    for (int c = 0; c < NCH; ++c)
+                        TR::unpack(*reinterpret_cast<const uint4 *>(stg + 2 * TB + (lane * NCH + c) * 16), &xp[c * EPC]);
+                    if (cur.pos0 + toff != 0) {
+                        V hv[EPC];
+                        TR::unpack(*reinterpret_cast<const uint4 *>(stg + NIN * TB), hv);
+                        x_below = hv[EPC - 1];
+                    } else if (hstate) {
+                        x_below = hstate[row];
+                    }
+                }
+                const V pA = lane_prefix[(i * 32 + lane) * 2], pB = lane_prefix[(i * 32 + lane) * 2 + 1];
+                V x = vfma(pA, x_in, pB);
+                if constexpr (PACKED) {
+                    auto J = [](int q) { return REV ? K - 1 - q : q; };
+                    // the state entering the second half of the lane's elements: run the first half's map
+                    float A0h = a[J(0)], B0h = b[J(0)];
+#pragma unroll
+                    for (int q = 1; q < H; ++q) {
+                        B0h = fmaf(a[J(q)], B0h, b[J(q)]);
+                        A0h *= a[J(q)];
+                    }
+                    float2 Xv = make_float2(x, fmaf(A0h, x, B0h));
+#pragma unroll
+                    for (int q = 0; q < H; ++q) {
+                        const float2 av = make_float2(a[J(q)], a[J(H + q)]);
+                        const float2 bv = make_float2(b[J(q)], b[J(H + q)]);
+                        Xv = __ffma2_rn(av, Xv, bv);
+                        b[J(q)] = Xv.x;
+                        b[J(H + q)] = Xv.y;
+                    }
+                } else {
+#pragma unroll
+                    for (int q = 0; q < K; ++q) {
+                        const int j = REV ? K - 1 - q : q;
+                        x = vfma(a[j], x, b[j]);
+                        b[j] = x;
+                    }
+                }
+                if (BACK) {
+                    // d_gates[t] = conj(x[t-1]) * g[t]
+                    V dn = shfl_up(xp[K - 1], 1);
+                    if (lane == 0) dn = x_below;
+#pragma unroll
+                    for (int j = K - 1; j >= 1; --j) a[j] = vmul(vconj(xp[j - 1]), b[j]);
+                    a[0] = vmul(vconj(dn), b[0]);
+                }
+                // results over the inputs of the stage, then out by bulk copies
+                __syncwarp();
+#pragma unroll
+                for (int c = 0; c < NCH; ++c) {
+                    *reinterpret_cast<uint4 *>(stg + 1 * TB + (lane * NCH + c) * 16) = TR::pack(&b[c * EPC]);
+                    if (NOUT > 1) *reinterpret_cast<uint4 *>(stg + 2 * TB + (lane * NCH + c) * 16) = TR::pack(&a[c * EPC]);
+                }
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    const uint32_t bytes = static_cast<uint32_t>(nvalid) * TR::ESIZE;
+                    const int64_t goff = (cur.e_begin + toff) * TR::ESIZE;
+                    bulk_s2g(obase[0] + goff, stg + 1 * TB, bytes);
+                    if (NOUT > 1) bulk_s2g(obase[1] + goff, stg + 2 * TB, bytes);
+                    bulk_commit();
+                    // the store of the stage before this one has read its data: refill that stage
+                    if (i > 0) bulk_wait_read<1>();
+                }
+                __syncwarp();
+                if (i > 0 && nxt.valid && i - 1 < nxt.nt) issue(nxt, i - 1);
+            }
+            if (lane == 0) bulk_wait_read<0>();
+            __syncwarp();
+            if (nxt.valid) {
+                for (int i = cur.nt - 1; i < nxt.nt; ++i) issue(nxt, i);
+            }
+        }
+        cur = nxt;
+        cur_gate_raw = nxt_gate_raw;
+    }
+
+    if (lane == 0) bulk_wait_read<0>();
+    __syncwarp();
+    // a rank that leaves tells the others: its reads of this call's exchange slots are over
+    if (sharded) {
+        uint32_t last = 0;
+        if (lane == 0) {
+            __threadfence();
+            last = (atomicAdd(p.ctrl + CTRL_DONE + 8, 1u) == static_cast<uint32_t>(W - 1)) ? 1u : 0u;
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last) {
+            if (lane < sp.world) st_relaxed_sys_u64(sp.xchg[lane] + 8 * sp.rank, sp.call);
+            if (lane == 0) p.ctrl[CTRL_DONE + 8] = 0;
+            __threadfence_system();
+        }
+    }
+    leave_kernel(p, W, status_bits, lane);
+}
+
+}  // namespace ascan

@@ -19,6 +19,12 @@ uint64_t workspace_bytes(int64_t rows) {
     return static_cast<uint64_t>(kCtrlBytes) + static_cast<uint64_t>(rows) * kCarryRecordBytes;
 }
 
+uint64_t lookback_records_per_row(int64_t segs) {
+    const uint64_t s1 = static_cast<uint64_t>((segs + 31) / 32);
+    const uint64_t s2 = (s1 + 31) / 32;
+    return static_cast<uint64_t>(segs) + s1 + s2;
+}
+
 static int nin_of(int kind) { return kind == ASCAN_KIND_BACKWARD ? 3 : 2; }
 static int nout_of(int kind) {
     return kind == ASCAN_KIND_FORWARD ? 1 : (kind == ASCAN_KIND_BACKWARD ? 2 : 0);
@@ -89,20 +95,61 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     const bool reverse_order = in.kind == ASCAN_KIND_BACKWARD || in.kind == ASCAN_KIND_REDUCE_BACKWARD || in.reverse;
     const bool can_split = use_ws && (!bulk || align_rows == 1);
     // Clearly fewer rows than SMs: a whole CTA per row (the team plan below) would leave SMs
-    // idle, so the look-back plan lets warps of many CTAs scan segments of one row at once.
-    // Every segment but a row's first is streamed twice (aggregate pass, scan pass; the second
-    // read finds the data in L2), which caps this plan near 4 TB/s.
+    // idle.  The look-back plan cuts rows into segments of a few tiles that a warp keeps in
+    // shared memory; segments of one row are scanned concurrently by warps of many CTAs, each
+    // taking its incoming state from the aggregates of the segments before it.  Also the plan
+    // of time-sharded calls, whatever their row count.
     const bool scan_kind = in.kind == ASCAN_KIND_FORWARD || in.kind == ASCAN_KIND_BACKWARD;
-    int lb_tiles = in.tune.lookback_tiles;
-    // below three rows per four SMs (measured on 148 SMs: at 96 rows look-back and teams of 12
-    // warps tie, at 128 rows the teams win by 10-20 %)
-    const int64_t lookback_rows = in.sm_count * 3 / 4;
-    if (lb_tiles < 1) lb_tiles = 1;
-    const bool lookback = can_split && bulk && scan_kind && in.allow_lookback && in.rows < lookback_rows &&
-                          tiles_row >= 2 * lb_tiles && (in.tune.disable_plans & 1) == 0;
-    if (lookback) {
-        seg_tiles = lb_tiles;
-        fine_tiles = lb_tiles;
+    {
+        int lb_tiles = in.tune.lookback_tiles > 0 ? in.tune.lookback_tiles : (in.kind == ASCAN_KIND_BACKWARD ? 3 : 4);
+        if (lb_tiles > 8) lb_tiles = 8;
+        // below three rows per four SMs (measured on 148 SMs: at 96 rows look-back and teams of 12
+        // warps tie, at 128 rows the teams win by 10-20 %)
+        const int64_t lookback_rows = in.sm_count * 3 / 4;
+        const int64_t te3 = 32 * 3 * (16 / esize);
+        const int64_t tiles_row3 = (in.seqlen + te3 - 1) / te3;
+        const bool possible = can_split && bulk && scan_kind && in.rows > 0 && (in.tune.disable_plans & 1) == 0;
+        const bool wanted = in.force_lookback || (in.allow_lookback && in.rows < lookback_rows && tiles_row3 >= 2 * lb_tiles);
+        const int64_t segs = (in.seqlen + lb_tiles * te3 - 1) / (lb_tiles * te3);
+        if (possible && wanted && in.rows * segs < (1ll << 31)) {
+            const int vsize = esize == 8 ? 8 : 4;
+            const int stage = nin_of(in.kind) * 32 * 3 * 16 + (in.kind == ASCAN_KIND_BACKWARD ? 128 : 0);
+            const int wsm = lb_tiles * stage + 128 + lb_tiles * 32 * 2 * vsize;      // lb_warp_smem in lookback.cuh
+            int wpc = kMaxSmemPerCta / wsm;
+            const int cap = in.kind == ASCAN_KIND_BACKWARD ? 14 : 16;
+            if (wpc > cap) wpc = cap;
+            if (in.tune.warps_per_cta > 0 && in.tune.warps_per_cta < wpc) wpc = in.tune.warps_per_cta;
+            if (wpc < 1) return ASCAN_ERR_UNSUPPORTED;
+            pl.kernel = 1;
+            pl.loader = 0;
+            pl.chunks_per_lane = 3;
+            pl.tile_elems = static_cast<int32_t>(te3);
+            pl.stages = lb_tiles;
+            pl.dynamic = 1;
+            pl.team_size = 1;
+            pl.rows_per_item = 1;
+            pl.row_groups = in.rows;
+            pl.seg_elems = lb_tiles * te3;
+            pl.fine_elems = pl.seg_elems;
+            pl.coarse_segs = 0;
+            pl.fine_segs = segs;
+            pl.segs_per_row = segs;
+            pl.items = in.rows * segs;
+            int64_t grid = in.sm_count;
+            if (pl.items < grid * wpc) {
+                int64_t w = (pl.items + grid - 1) / grid;
+                wpc = static_cast<int>(w < 1 ? 1 : w);
+                grid = (pl.items + wpc - 1) / wpc;
+            }
+            pl.warps_per_cta = wpc;
+            pl.grid = static_cast<int32_t>(grid);
+            pl.smem_bytes = static_cast<uint64_t>(wpc) * wsm;
+            pl.workspace_bytes = static_cast<uint64_t>(kCtrlBytes) +
+                                 static_cast<uint64_t>(in.rows) * lookback_records_per_row(segs) * kLookbackRecordBytes;
+            *plan = pl;
+            return ASCAN_OK;
+        }
+        if (in.force_lookback) return ASCAN_ERR_UNSUPPORTED;
     }
     // Fewer rows than warps, but too many for look-back to pay: teams of G warps share an
     // item, so that all warps work although only rows/G... teams can be busy at once.  G is
@@ -110,7 +157,7 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     int team = 1;
     int team_wpc = kMaxWarpsPerCta;      // warps per CTA of a team plan
     const bool team_kind = scan_kind || in.dtype != ASCAN_C64;     // carry-only kinds: real dtypes
-    if (!lookback && can_split && bulk && team_kind && in.allow_team && in.rows > 0 && in.rows < team_rows &&
+    if (can_split && bulk && team_kind && in.allow_team && in.rows > 0 && in.rows < team_rows &&
         (in.tune.disable_plans & 2) == 0) {
         // The forward kinds need fewer registers and less shared memory per warp, so 16 warps
         // fit in a CTA (teams of 2, 4, 8 or 16): with 12 the forward is bound by the time a warp
@@ -152,7 +199,7 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
         }
     }
     const int64_t workers = static_cast<int64_t>(in.sm_count) * team_wpc / team;
-    const int64_t split_min = lookback ? 2 * lb_tiles : (team > 1 ? 2 * fine_tiles : 32);
+    const int64_t split_min = team > 1 ? 2 * fine_tiles : 32;
     if (can_split && tiles_row >= split_min && tiles_row >= 2 * fine_tiles) {
         int64_t fine_region = (static_cast<int64_t>(seg_tiles) * workers + in.rows - 1) / (in.rows > 0 ? in.rows : 1);
         fine_region = (fine_region + fine_tiles - 1) / fine_tiles * fine_tiles;      // tiles, multiple of a fine item
@@ -210,9 +257,7 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     pl.stages = bulk ? stages : 1;
 
     // (the team kernel's backward stage has the same 128-byte halo slot, so the sizes agree)
-    // look-back kernels keep, per tile of a segment and lane, two values of the compute type
-    // (must match lookback_prefix_bytes in stream.cuh)
-    const int wsm = warp_smem(nch, pl.stages, in.kind, bulk) + (lookback ? 8 * 32 * 2 * (esize == 8 ? 8 : 4) : 0);
+    const int wsm = warp_smem(nch, pl.stages, in.kind, bulk);
     int wpc = (kMaxSmemPerCta - (team > 1 ? team_wpc / team * kTeamSmemBytes : 0)) / wsm;
     // the stream kernels are compiled for 16 warps per CTA (14 for the fused backward, which
     // needs more registers); 14 measured best (more warps hide more of a tile's dependent
@@ -255,11 +300,8 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     pl.warps_per_cta = wpc;
     pl.grid = static_cast<int32_t>(grid);
     pl.smem_bytes = static_cast<uint64_t>(wpc) * wsm + (team > 1 ? static_cast<uint64_t>(wpc / team) * kTeamSmemBytes : 0);
-    pl.kernel = (lookback && pl.segs_per_row > 1) ? 1 : (team > 1 ? 2 : 0);
-    pl.workspace_bytes = (!use_ws || !pl.dynamic) ? 0
-                         : (pl.kernel == 1 ? static_cast<uint64_t>(kCtrlBytes) + static_cast<uint64_t>(in.rows) *
-                                                 pl.segs_per_row * kLookbackRecordBytes
-                                           : workspace_bytes(in.rows));
+    pl.kernel = team > 1 ? 2 : 0;
+    pl.workspace_bytes = (!use_ws || !pl.dynamic) ? 0 : workspace_bytes(in.rows);
     *plan = pl;
     return ASCAN_OK;
 }

@@ -21,7 +21,7 @@ constexpr int kCarryRecordBytes = 32;        // per-row carry record behind it
 struct PlanTuning {
     int stages = 2;            // shared-memory stages per warp of the stream and team kernels
     int warps_per_cta = 0;     // 0 = planner's choice; otherwise an upper bound
-    int lookback_tiles = 8;    // tiles per segment of the look-back plan
+    int lookback_tiles = 0;    // tiles per segment of the look-back plan; 0 = 4 (forward) or 3 (fused backward)
     int disable_plans = 0;     // bit 0: no look-back, bit 1: no team, bit 2: static deal (no tickets), bit 3: plain loader
 };
 
@@ -36,13 +36,17 @@ struct PlanInput {
     bool allow_lookback = true;   // false: never choose the look-back plan (smaller workspace)
     bool allow_team = true;       // false: never choose the team plan
     bool three_chunks = false;    // true: always 3 chunks per lane (variants without a 2-chunk kernel)
+    bool force_lookback = false;  // true: the look-back plan whatever the row count (time-sharded calls)
     int sm_count;
     PlanTuning tune;
 };
 
 int dtype_size(int dtype);   // bytes per element, 0 if unknown
 
-constexpr int kLookbackRecordBytes = 64;     // per (row, segment) record of the look-back plan
+constexpr int kLookbackRecordBytes = 32;     // per record of the look-back plan (segments, blocks, super-blocks)
+
+// Records per row of the look-back plan: segments + blocks of 32 + super-blocks of 32 blocks.
+uint64_t lookback_records_per_row(int64_t segs);
 
 // Workspace of the chained plans: control block + one carry record per row.
 uint64_t workspace_bytes(int64_t rows);

@@ -38,17 +38,6 @@
 //     rows (INTERIOR = true) row starts fall inside tiles; the gate of a row's first
 //     processed element is forced to zero there, which resets the running state.
 //
-// Look-back mode (LOOKBACK = true), for matrices with fewer rows than warps
-//   Chaining the segments of a row lets only one warp work on a row at a time.  In this
-//   mode every segment but the first of a row is streamed twice by its warp: a first pass
-//   computes only the segment's aggregate (A, B) and publishes it; the warp then looks
-//   back over the records of the preceding segments -- 32 at a time, one per lane --
-//   composing aggregates until it meets a segment whose outgoing state is already known,
-//   publishes its own outgoing state A*x_in + B at once, and only then streams the
-//   segment again (the second read hits L2) to write the scan.  Segments of one row are
-//   thus scanned concurrently by many warps and CTAs; nothing waits for a whole segment
-//   scan.  Records are per (row, segment); every wait is bounded.
-//
 // Kinds: forward scan (optionally reversed), fused backward (reverse scan over the
 // gates shifted by one step plus the d_gates epilogue; shifted operands come from
 // neighbouring lanes by shuffle, tile halos from one scalar load), and the two
@@ -69,7 +58,6 @@ enum : int { CTRL_STATUS = 0, CTRL_TICKET = 1, CTRL_DONE = 2, CTRL_EPOCH = 3, CT
 constexpr int EPOCH_SHIFT = 15;        // a carry tag is (epoch << 15) | segment number
 constexpr int CTRL_BYTES = 256;        // control block, then one carry record per row
 constexpr int CARRY_RECORD_BYTES = 32;
-constexpr int LOOKBACK_RECORD_BYTES = 64;   // per (row, segment): aggregate A, aggregate B, outgoing state
 
 struct StreamParams {
     const void *in0;         // gates
@@ -155,13 +143,6 @@ __host__ __device__ constexpr int stream_warp_smem(int nch, int stages, int kind
     return nstg * stream_stage_bytes(nch, kind) + outbufs * stream_nout(kind) * tb + 128;
 }
 
-// Look-back plan: the aggregate pass leaves, per tile and lane, the affine map from the
-// segment's start to the lane's first element; the scan pass applies it to the segment's
-// incoming state and goes straight to the recurrence (no lane aggregates, no shuffle
-// combine a second time).  Segments of up to LB_PREFIX_TILES tiles use it.
-constexpr int LB_PREFIX_TILES = 8;
-__host__ __device__ constexpr int lookback_prefix_bytes(int vsize) { return LB_PREFIX_TILES * 32 * 2 * vsize; }
-
 constexpr uint32_t LOAD_WAIT_POLLS = 1u << 22;
 constexpr uint32_t CARRY_WAIT_POLLS = 1u << 20;
 
@@ -186,7 +167,6 @@ struct ItemDesc {
     int64_t n;         // elements in the item
     int32_t s_log;     // segment index in processing order
     int32_t nt;        // tiles in the item
-    int32_t phase;     // look-back mode: 0 = aggregate pass, 1 = scan pass (always 1 otherwise)
     bool valid;
 };
 
@@ -200,8 +180,7 @@ struct ItemDesc {
 // gate pre-activations z and the gate is sigmoid(z), computed in fp32 as the tile is read.
 // The fused backward returns d_z[t] = x[t-1] * g[t] * s(1 - s) in place of d_gates, which
 // removes the caller's sigmoid pass and its backward pass over the (B, C, T) tensors.
-template <class TR, int NCH, int KIND, bool REVERSE, bool BULK, bool INTERIOR, bool LOOKBACK, bool TOKR = false,
-          int ACT = 0>
+template <class TR, int NCH, int KIND, bool REVERSE, bool BULK, bool INTERIOR, bool TOKR = false, int ACT = 0>
 __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ? 448 : 512), 1) stream_kernel(const StreamParams p) {
     using V = typename TR::V;
     using Raw = typename TR::Raw;
@@ -218,7 +197,7 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
     constexpr bool TOK_IN_REAL = TOKR && KIND == K_SCAN;
     constexpr bool TOK_OUT_REAL = TOKR && KIND == K_BWD;
     const int NSTG = BULK ? p.stages : 1;
-    const int WARP_SMEM = stream_warp_smem(NCH, p.stages, KIND, BULK) + (LOOKBACK ? lookback_prefix_bytes(sizeof(V)) : 0);
+    const int WARP_SMEM = stream_warp_smem(NCH, p.stages, KIND, BULK);
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31;
@@ -229,7 +208,6 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
     constexpr int STAGE_BYTES = stream_stage_bytes(NCH, KIND);
     unsigned char *out_base = wsm + NSTG * STAGE_BYTES;
     uint64_t *bars = reinterpret_cast<uint64_t *>(out_base + OUTBUFS * NOUT * TB);
-    V *lane_prefix = reinterpret_cast<V *>(reinterpret_cast<unsigned char *>(bars) + 128);   // LOOKBACK only
 
     const int64_t w = static_cast<int64_t>(blockIdx.x) * wpc + wib;
     const int64_t W = static_cast<int64_t>(gridDim.x) * wpc;
@@ -273,7 +251,7 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
     auto describe = [&](int64_t q) -> ItemDesc {
         ItemDesc d;
         d.valid = q < p.items;
-        d.e_begin = 0; d.row0 = 0; d.pos0 = 0; d.s_log = 0; d.n = 0; d.nt = 0; d.phase = 1;
+        d.e_begin = 0; d.row0 = 0; d.pos0 = 0; d.s_log = 0; d.n = 0; d.nt = 0;
         if (!d.valid) return d;
         if (!split) {
             const int64_t r0 = q * p.rows_per_item;
@@ -306,7 +284,6 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
             d.n = left < len ? left : len;
         }
         d.nt = static_cast<int32_t>((d.n + TE - 1) / TE);
-        if (LOOKBACK && d.s_log > 0) d.phase = 0;
         return d;
     };
 
@@ -350,12 +327,7 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
     ItemDesc nxt = cur;
     auto need_next = [&]() {
         if (!nxt_ready) {
-            if (LOOKBACK && cur.valid && cur.phase == 0) {
-                nxt = cur;             // the same segment again, this time to write the scan
-                nxt.phase = 1;
-            } else {
-                nxt = describe(cur.valid ? resolve(raw_next) : p.items);
-            }
+            nxt = describe(cur.valid ? resolve(raw_next) : p.items);
             nxt_ready = true;
         }
     };
@@ -418,7 +390,7 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
         h.gate_kind = 0;
         h.halo = vone(V());
         if (!d.valid) return h;
-        if (!LOOKBACK && split && d.s_log > 0) {
+        if (split && d.s_log > 0) {
             const unsigned char *rec = p.records + d.row0 * CARRY_RECORD_BYTES;
             h.x = fetch_tagged(rec, 0, TWO_WORDS);
             if (REDUCE) h.x2 = fetch_tagged(rec, 1, TWO_WORDS);
@@ -435,7 +407,6 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
         return h;
     };
     ItemHeader head = fetch_header(cur);
-    V lookback_x_in = vzero(V());   // look-back mode: incoming state of the segment being processed
 
     while (cur.valid && !failed) {
         // ---------------- item prologue: incoming state, halo gate, running position
@@ -447,17 +418,7 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
             if (head.gate_kind == 1) item_end_gate = sigmoid_fast<TR::ESIZE == 4>(item_end_gate);
         }
         V next_gate = item_end_gate;
-        const bool agg_pass = LOOKBACK && cur.phase == 0;   // stream for the aggregate only
-        // the scan pass of a segment whose aggregate pass left the lanes' prefixes behind
-        const bool keep_prefix = LOOKBACK && cur.s_log > 0 && cur.nt <= LB_PREFIX_TILES;
-        const bool use_prefix = keep_prefix && !agg_pass;
-        if (LOOKBACK && cur.s_log > 0) {
-            if (agg_pass) {
-                x2_carry = vone(V());          // zero state and unit response: (B, A) of the segment
-            } else {
-                x_carry = lookback_x_in;       // found by the look-back after the aggregate pass
-            }
-        } else if (split && cur.s_log > 0) {
+        if (split && cur.s_log > 0) {
             // state published by the warp that processed the previous segment of this row
             const unsigned char *rec = p.records + cur.row0 * CARRY_RECORD_BYTES;
             const uint32_t want = epoch | static_cast<uint32_t>(cur.s_log);
@@ -556,7 +517,7 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
             }
             V xp[KIND == K_BWD ? K : 1];
             V x_below = vzero(V());   // state just below the tile, from the halo chunk
-            if (KIND == K_BWD && !agg_pass) {
+            if (KIND == K_BWD) {
 #pragma unroll
                 for (int c = 0; c < NCH; ++c) {
                     const uint4 qx = *reinterpret_cast<const uint4 *>(stg + 2 * TB + (lane * NCH + c) * 16);
@@ -707,10 +668,7 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
             V A0h = vone(V()), B0h = vzero(V());
             V x = vzero(V());    // state entering this lane
             V x2 = vzero(V());
-            if (use_prefix) {
-                const V pa = lane_prefix[(i * 32 + lane) * 2], pb = lane_prefix[(i * 32 + lane) * 2 + 1];
-                x = vfma(pa, lookback_x_in, pb);
-            } else {
+            {
             V A, B;
             V B2 = vzero(V());
             if constexpr (PACKED) {
@@ -742,7 +700,7 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
             }
             // the warp's incoming state enters through the first lane in processing order
             const int ll = REV ? 31 - lane : lane;
-            const bool unit_channel = REDUCE || agg_pass;   // also carry the response to a unit state
+            constexpr bool unit_channel = REDUCE;            // also carry the response to a unit state
             if (ll == 0) {
                 B = vfma(A, x_carry, B);
                 if (unit_channel) B2 = vfma(A, x2_carry, B2);
@@ -763,21 +721,17 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
             // state entering this lane = inclusive result of the previous lane
             x = REV ? shfl_down(B, 1) : shfl_up(B, 1);
             if (ll == 0) x = x_carry;
-            if ((REDUCE && INTERIOR) || (agg_pass && keep_prefix)) {
+            if (REDUCE && INTERIOR) {
                 x2 = REV ? shfl_down(B2, 1) : shfl_up(B2, 1);
                 if (ll == 0) x2 = x2_carry;
-            }
-            if (agg_pass && keep_prefix) {
-                lane_prefix[(i * 32 + lane) * 2] = x2;
-                lane_prefix[(i * 32 + lane) * 2 + 1] = x;
             }
             x_carry = shfl_idx(B, REV ? 0 : 31);
             if (unit_channel) x2_carry = shfl_idx(B2, REV ? 0 : 31);
             }
 
-            if (!REDUCE && !agg_pass) {
+            if (!REDUCE) {
                 // ---- pass 2: the recurrence itself from the lane's incoming state
-                if (PACKED && !use_prefix) {
+                if (PACKED) {
                   if constexpr (PACKED) {
                     auto J = [](int q) { return REV ? K - 1 - q : q; };
                     float2 Xv = make_float2(x, fmaf(A0h, x, B0h));   // states entering the two halves
@@ -922,74 +876,7 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
         if (failed) break;
 
         // ---------------- item epilogue: hand the outgoing state on, move to the next item
-        if (LOOKBACK) {
-            unsigned char *rec = p.records + (cur.row0 * p.segs_per_row + cur.s_log) * LOOKBACK_RECORD_BYTES;
-            const uint32_t tag = epoch | static_cast<uint32_t>(cur.s_log + 1);
-            if (agg_pass) {
-                // ---- publish the aggregate, look back for the incoming state, publish the outgoing state
-                const V segA = x2_carry, segB = x_carry;
-                if (lane == 0) {
-                    publish_tagged(rec, 0, segA, tag);
-                    publish_tagged(rec, 1, segB, tag);
-                }
-                V accA = vone(V()), accB = vzero(V());      // composition of the segments walked so far
-                int k = cur.s_log - 1;                       // nearest preceding segment
-                bool found = false;
-                uint32_t polls = 0;
-                while (!found) {
-                    // lane i examines segment k - i; segment -1 stands for the row's initial state
-                    const int kk = k - lane;
-                    int state = 0;                           // 0 nothing yet, 1 aggregate, 2 outgoing state
-                    V rA = vone(V()), rB = vzero(V()), rX = vzero(V());
-                    if (kk < 0) {
-                        state = 2;
-                        if (kk == -1 && cin) rX = cin[cur.row0];
-                    } else {
-                        const unsigned char *pr =
-                            p.records + (cur.row0 * p.segs_per_row + kk) * LOOKBACK_RECORD_BYTES;
-                        const uint32_t want = epoch | static_cast<uint32_t>(kk + 1);
-                        if (read_tagged(pr, 2, want, rX)) {
-                            state = 2;
-                        } else {
-                            const bool okA = read_tagged(pr, 0, want, rA);
-                            const bool okB = read_tagged(pr, 1, want, rB);
-                            if (okA && okB) state = 1;
-                        }
-                    }
-                    const uint32_t has_x = __ballot_sync(0xffffffffu, state == 2);
-                    const uint32_t has_any = __ballot_sync(0xffffffffu, state != 0);
-                    const int px = has_x ? __ffs(has_x) - 1 : 32;        // nearest known outgoing state
-                    const uint32_t need = px >= 32 ? 0xffffffffu : ((1u << px) - 1u);
-                    if ((has_any & need) != need) {
-                        // a nearer segment has published nothing yet: poll again, with a bound
-                        if (++polls > CARRY_WAIT_POLLS) {
-                            status_bits |= STATUS_LOOKBACK_TIMEOUT;
-                            break;
-                        }
-                        __nanosleep(100);
-                        continue;
-                    }
-                    // compose the aggregates of lanes 0 .. px-1 (lane 0 is applied last)
-                    for (int i = 0; i < px && i < 32; ++i) {
-                        const V Ai = shfl_idx(rA, i), Bi = shfl_idx(rB, i);
-                        accB = vfma(accA, Bi, accB);
-                        accA = vmul(accA, Ai);
-                    }
-                    if (px < 32) {
-                        const V xs = shfl_idx(rX, px);
-                        lookback_x_in = vfma(accA, xs, accB);
-                        found = true;
-                    } else {
-                        k -= 32;
-                    }
-                }
-                if (!found) lookback_x_in = vzero(V());
-                if (lane == 0) publish_tagged(rec, 2, vfma(segA, lookback_x_in, segB), tag);
-            } else if (cur.s_log == 0 && p.segs_per_row > 1) {
-                // the first segment of a row is scanned straight away; its end state is known now
-                if (lane == 0) publish_tagged(rec, 2, x_carry, tag);
-            }
-        } else if (split && cur.s_log + 1 < p.segs_per_row) {
+        if (split && cur.s_log + 1 < p.segs_per_row) {
             // (fault injection for the tests: the hand-over of row 0's first segment is dropped,
             // so exactly one reader runs into its bound and reports it)
             const bool drop = p.test_drop_carry && cur.row0 == 0 && cur.s_log == 0;
@@ -1008,9 +895,8 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
             }
         }
         need_next();
-        const bool same_ticket = LOOKBACK && cur.phase == 0;   // the scan pass of the same segment follows
         cur = nxt;
-        if (!same_ticket) raw_next = cur.valid ? draw() : 0u;
+        raw_next = cur.valid ? draw() : 0u;
         nxt_ready = false;
         if (prod_in_next) {
             prod_in_next = false;      // the producer's item is now the current one

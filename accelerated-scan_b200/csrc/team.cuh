@@ -136,7 +136,7 @@ __global__ void __launch_bounds__((KIND == K_BWD || KIND == K_REDUCE_BWD) ? 384 
     auto describe = [&](int64_t q) -> ItemDesc {
         ItemDesc d;
         d.valid = q < p.items;
-        d.e_begin = 0; d.row0 = 0; d.pos0 = 0; d.s_log = 0; d.n = 0; d.nt = 0; d.phase = 1;
+        d.e_begin = 0; d.row0 = 0; d.pos0 = 0; d.s_log = 0; d.n = 0; d.nt = 0;
         if (!d.valid) return d;
         if (!split) {
             d.row0 = q;

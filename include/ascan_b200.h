@@ -64,10 +64,10 @@ typedef enum {
  * of warp.cuh:282-380.  Pure host arithmetic, usable without a GPU when
  * sm_count > 0 is passed. */
 typedef struct {
-    int32_t kernel;            /* 0 = stream: one warp per item, segments of a row chained; 1 = look-back (very few rows: segments of a row scanned concurrently); 2 = team (fewer than four rows per warp: several warps share an item) */
+    int32_t kernel;            /* 0 = stream: one warp per item, segments of a row chained; 1 = look-back (very few rows, or rows sharded along time: short segments kept in shared memory and scanned concurrently, incoming states from segment aggregates); 2 = team (fewer than four rows per warp: several warps share an item) */
     int32_t loader;            /* 0 = bulk-async copies into shared-memory stages, 1 = plain element loads (unaligned data) */
     int32_t chunks_per_lane;   /* 16-byte chunks each lane owns per tile                  */
-    int32_t stages;            /* shared-memory stages per warp                            */
+    int32_t stages;            /* shared-memory stages per warp (look-back: tiles per segment) */
     int32_t warps_per_cta;
     int32_t grid;              /* persistent CTAs                                          */
     int32_t tile_elems;        /* elements per warp tile                                   */
@@ -204,9 +204,62 @@ int ascan_fold_carries(const void *gathered, int64_t rows, int world, int rank,
                        void *state_out, void *halo_out, void *stream);
 
 /*
+ * Time-sharded scan: every rank (one GPU each) holds a contiguous time slice of ALL rows
+ * (rank order = time order) and calls the same function on its slice.  Each rank streams its
+ * slice once; the state entering the slice is folded from the slice aggregates that the other
+ * ranks store, with plain 64-bit peer stores, into this rank's exchange buffer, so the ranks run
+ * at the same time and no collective is involved.  No counterpart in the reference (it has no
+ * multi-device path).
+ *   exchange   `world` device pointers: exchange[j] is rank j's exchange buffer as mapped in
+ *              THIS process (exchange[rank] is the local one): peer-accessible memory of
+ *              ascan_exchange_bytes(rows, world) bytes, 16-byte aligned, zero-filled once
+ *              before its first use.  One buffer set per direction: the forward calls of a
+ *              group of ranks share one set, the backward calls another.  world == 1 ignores it.
+ *   call       number of this call on its buffer set: 1, 2, 3, ... and the same on every rank.
+ *              Ranks may drift apart by at most one call; a rank that gets further ahead waits
+ *              (bounded) for the slower ones.
+ *   carry_save (forward, nullable) receives, per row, the state entering this rank's slice
+ *              (compute type); pass it as halo_state_left of the backward.
+ *   ws         required: ascan_workspace_bytes_time_sharded(...) bytes, 256-byte aligned,
+ *              zero-filled once; not shared with launches that can overlap.
+ * carry_in of the whole sequence is not supported (the sequence starts from zero).  Needs
+ * 16-byte aligned pointers and seqlen * element size divisible by 16; otherwise
+ * ASCAN_ERR_UNSUPPORTED.  Kernels of different ranks wait for one another's aggregates: run
+ * each rank on a GPU of its own.
+ */
+size_t ascan_exchange_bytes(int64_t rows, int world);
+size_t ascan_workspace_bytes_time_sharded(int64_t rows, int64_t seqlen, int dtype, int kind);
+int ascan_forward_time_sharded(const void *gates, const void *tokens, void *out,
+                               int64_t rows, int64_t seqlen, int dtype,
+                               int rank, int world, uint32_t call, void *const *exchange,
+                               void *carry_save, void *ws, size_t ws_bytes, void *stream);
+int ascan_backward_time_sharded(const void *gates, const void *states, const void *grad_out,
+                                void *d_gates, void *d_tokens,
+                                int64_t rows, int64_t seqlen, int dtype,
+                                int rank, int world, uint32_t call, void *const *exchange,
+                                const void *halo_state_left,
+                                void *ws, size_t ws_bytes, void *stream);
+
+/*
+ * Exchange buffers for ranks that are separate processes.  ascan_peer_alloc allocates
+ * `bytes` of zero-filled device memory on the current device (cudaMalloc: these four are the
+ * only functions of the library that allocate or free) and fills `handle64` (64 bytes) with
+ * an inter-process handle; the handle travels to the other ranks by any host channel, and
+ * ascan_peer_open maps that rank's buffer into this process with peer access enabled.
+ * ascan_peer_close unmaps, ascan_peer_free releases the local buffer.  Ranks inside one
+ * process pass their device pointers directly and need none of this.  No counterpart in
+ * the reference.
+ */
+int ascan_peer_alloc(size_t bytes, void **ptr, void *handle64);
+int ascan_peer_open(const void *handle64, void **ptr);
+int ascan_peer_close(void *ptr);
+int ascan_peer_free(void *ptr);
+
+/*
  * Scratch bytes a call of `kind` with these sizes can use: a control block
- * (status word, work ticket) plus one carry record per row, or per (row, segment)
- * when the look-back plan applies (clearly fewer rows than SMs).  With that much scratch
+ * (status word, work ticket) plus one carry record per row, or 32 bytes per segment,
+ * block of 32 segments and super-block when the look-back plan applies (clearly fewer
+ * rows than SMs).  With that much scratch
  * the kernels balance work over the SMs dynamically and split long rows across
  * warps and CTAs; with less they step down to the chained plan (256 + 32*rows
  * bytes), and with none (NULL) to a static deal of whole rows: correct, slower.

@@ -75,7 +75,7 @@ def test_failure_surfaces_at_the_next_call_without_debug_mode(cuda_device, chain
     torch.cuda.synchronize(cuda_device)                   # the failed launch has finished
     with pytest.raises(RuntimeError, match="bounded device-side wait"):
         _native.forward(g, x, out)
-    _native.check_status(cuda_device)                     # clears the device-side word as well
+    _native.check_status(cuda_device)                     # reported once: both copies of the status are clear
     _native.forward(g, x, out)
     _native.check_status(cuda_device)
     assert rel_err(to_np(out), want) <= 1e-5

@@ -67,10 +67,14 @@ def test_planner_invariants(T, dtype, kind):
             assert pl["segs_per_row"] == 1 and pl["kernel"] == 0 and pl["workspace_bytes"] == 0
             assert pl["items"] <= 2 * pl["grid"] * pl["warps_per_cta"]
         elif pl["kernel"] == 1:
-            # look-back plan: fewer rows than 3/4 of the SMs, per-(row, segment) records, equal small segments
+            # look-back plan: fewer rows than 3/4 of the SMs; equal short segments (one shared-memory stage
+            # per tile); 32-byte records per segment, block of 32 segments and super-block of 32 blocks
             assert rows < 111 and kind in (0, 1) and pl["segs_per_row"] > 1
-            assert pl["workspace_bytes"] == 256 + 64 * rows * pl["segs_per_row"]
-            assert pl["seg_elems"] == pl["fine_elems"]
+            segs = pl["segs_per_row"]
+            blocks = (segs + 31) // 32
+            assert pl["workspace_bytes"] == 256 + 32 * rows * (segs + blocks + (blocks + 31) // 32)
+            assert pl["seg_elems"] == pl["fine_elems"] == pl["stages"] * pl["tile_elems"]
+            assert pl["stages"] == (3 if kind == 1 else 4) and pl["chunks_per_lane"] == 3
             chained = _native.plan(rows, T, dtype, kind, sm_count=148, lookback=False, team=False)
             assert chained["kernel"] == 0 and chained["workspace_bytes"] in (0, 256 + 32 * rows)
         else:
@@ -91,7 +95,8 @@ def test_planner_invariants(T, dtype, kind):
         if pl["segs_per_row"] > 1:
             # split rows: one row per item, segments are whole tiles
             assert pl["rows_per_item"] == 1 and pl["seg_elems"] % pl["tile_elems"] == 0
-            assert pl["fine_elems"] % pl["tile_elems"] == 0 and pl["segs_per_row"] < 32768
+            assert pl["fine_elems"] % pl["tile_elems"] == 0
+            assert pl["segs_per_row"] < 32768 or pl["kernel"] == 1      # chained carries tag segments in 15 bits
             # only the last piece of a row (in memory order) may be short, none is empty
             if kind in (1, 3):
                 assert pl["fine_segs"] * pl["fine_elems"] + (pl["coarse_segs"] - 1) * pl["seg_elems"] < T or pl["coarse_segs"] == 0
