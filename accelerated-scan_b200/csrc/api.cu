@@ -163,6 +163,10 @@ static int plan_for(int64_t rows, int64_t seqlen, int dtype, int kind, bool alig
 }
 
 // Copies the plan's decomposition and the workspace pointers into the kernel parameters.
+#ifdef LB_DEBUG_TIMING
+static void *g_debug_buffer = nullptr;
+extern "C" void ascan_debug_buffer(void *p) { g_debug_buffer = p; }
+#endif
 static void fill_common(StreamParams &p, const ascan_plan &pl, int64_t rows, int64_t seqlen, void *ws, size_t ws_bytes) {
     p.rows = rows;
     p.T = seqlen;
@@ -181,6 +185,9 @@ static void fill_common(StreamParams &p, const ascan_plan &pl, int64_t rows, int
     p.test_drop_carry = g_opt_drop_carry.load(std::memory_order_relaxed);
     p.epoch_mask = (1u << g_opt_epoch_bits.load(std::memory_order_relaxed)) - 1u;
     p.scratch_bytes = (pl.dynamic && ws_bytes > static_cast<size_t>(CTRL_BYTES)) ? ws_bytes - CTRL_BYTES : 0;
+#ifdef LB_DEBUG_TIMING
+    if (pl.kernel == 1) p.carry_out = g_debug_buffer;
+#endif
 }
 
 // Plan for the fused variants, which exist only in the chained stream plan with the bulk

@@ -40,7 +40,7 @@
 namespace ascan {
 
 constexpr int LB_RECORD_BYTES = 32;          // one affine pair of the compute type in tagged 64-bit words
-constexpr int LB_MAX_TILES = 8;              // tiles per segment (= shared-memory stages per warp), at most
+constexpr int LB_MAX_TILES = 8;              // tiles per segment, at most (a warp holds two segments: 2 stages per tile)
 constexpr int MAX_WORLD = 16;                // ranks of a time-sharded scan, at most
 constexpr uint32_t LB_WAIT_POLLS = 1u << 20;      // about a second
 
@@ -66,8 +66,10 @@ struct ShardParams {
 __host__ __device__ constexpr int lb_stage_bytes(int nch, int kind) {
     return stream_nin(kind) * 32 * nch * 16 + (kind == K_BWD ? 128 : 0);
 }
-__host__ __device__ constexpr int lb_warp_smem(int nch, int nt, int kind, int vsize) {
-    return nt * lb_stage_bytes(nch, kind) + 128 + nt * 32 * 2 * vsize;
+// Two resident segments of `nt` tiles per warp, their mbarriers, and 16 bytes per stage and lane
+// of prefix maps.
+__host__ __device__ constexpr int lb_warp_smem(int nch, int nt, int kind) {
+    return 2 * nt * lb_stage_bytes(nch, kind) + 128 + 2 * nt * 32 * 16;
 }
 // Workspace of the look-back plan: control block, then the records of the three levels.
 __host__ __device__ constexpr uint64_t lb_level_count(int64_t n) { return static_cast<uint64_t>((n + 31) / 32); }
@@ -157,10 +159,72 @@ __device__ __forceinline__ bool compose_window(const unsigned char *base, int64_
     return true;
 }
 
+// Reads up to three windows of records at once (lane i reads record i of each) and polls only
+// for those still missing, so a look-back whose records are all there costs one round trip.
+// Window w: n[w] records from base[w]; result (A[w], B[w]) as in compose_window.
+template <class V>
+__device__ __forceinline__ bool compose_three(const unsigned char *const base[3], const int n[3], uint32_t tag, int lane,
+                                              V A[3], V B[3]) {
+    V a[3], b[3];
+    bool ok[3];
+#pragma unroll
+    for (int w = 0; w < 3; ++w) {
+        a[w] = vone(V());
+        b[w] = vzero(V());
+        ok[w] = lane >= n[w];
+    }
+    bool all = false;
+    for (uint32_t poll = 0; poll < LB_WAIT_POLLS; ++poll) {
+#pragma unroll
+        for (int w = 0; w < 3; ++w)
+            if (!ok[w]) ok[w] = get_pair<false>(base[w] + lane * LB_RECORD_BYTES, tag, a[w], b[w]);
+        all = __all_sync(0xffffffffu, ok[0] && ok[1] && ok[2]);
+        if (all) break;
+        if (poll > 4) __nanosleep(poll > 64 ? 200 : 40);
+    }
+#pragma unroll
+    for (int w = 0; w < 3; ++w) {
+        if (n[w] > 0 && all) {
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const V Ap = shfl_up(a[w], d), Bp = shfl_up(b[w], d);
+                if (lane >= d) {
+                    b[w] = vfma(a[w], Bp, b[w]);
+                    a[w] = vmul(a[w], Ap);
+                }
+            }
+            A[w] = shfl_idx(a[w], 31);
+            B[w] = shfl_idx(b[w], 31);
+        } else {
+            A[w] = vone(V());
+            B[w] = vzero(V());
+        }
+    }
+    return all;
+}
+
+// What a warp keeps about an item between its aggregate pass and its scan pass.
+template <class V>
+struct PendingItem {
+    ItemDesc d;
+    V segA, segB;          // the segment's aggregate
+    V end_gate;            // backward: gate of the step right after the segment
+    bool waits_ok;
+};
+
 // KIND: K_SCAN (REVERSE selects the direction) or K_BWD.  Bulk loader, one segment per item.
+//
+// A warp holds TWO segments in shared memory (2 * NT stages) and works on them in the order
+//     aggregate(k+1), look-back(k), scan(k), aggregate(k+2), look-back(k+1), scan(k+1), ...
+// so the look-back of an item starts a whole aggregate pass after the item's own aggregate was
+// published: the aggregates it reads, all of items drawn earlier, are normally there already.
+// The number of item k+2 is drawn after look-back(k); from that draw to the publication of the
+// item's aggregate the warp waits for nothing but memory, so a drawn item is never held back
+// by its owner waiting in a look-back (such waits would chain up across warps).
 template <class TR, int NCH, int KIND, bool REVERSE>
-__global__ void __launch_bounds__(KIND == K_BWD ? 448 : 512, 1) lookback_kernel(const StreamParams p, const ShardParams sp) {
+__global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, const ShardParams sp) {
     using V = typename TR::V;
+    using Raw = typename TR::Raw;
     constexpr int EPC = TR::EPC;
     constexpr int K = NCH * EPC;
     constexpr int TE = 32 * K;
@@ -172,16 +236,18 @@ __global__ void __launch_bounds__(KIND == K_BWD ? 448 : 512, 1) lookback_kernel(
     constexpr int STAGE_BYTES = lb_stage_bytes(NCH, KIND);
     constexpr bool PACKED = sizeof(V) == 4 && (K % 2 == 0);
     constexpr int H = K / 2;
-    const int NT = p.stages;                                  // tiles per segment
-    const int WARP_SMEM = lb_warp_smem(NCH, NT, KIND, sizeof(V));
+    const int NT = p.stages;                                  // tiles per segment; 2 * NT stages per warp
+    const int WARP_SMEM = lb_warp_smem(NCH, NT, KIND);
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31;
     const int wib = threadIdx.x >> 5;
     const int wpc = blockDim.x >> 5;
     unsigned char *wsm = smem_raw + static_cast<size_t>(wib) * WARP_SMEM;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(wsm + NT * STAGE_BYTES);
-    V *lane_prefix = reinterpret_cast<V *>(wsm + NT * STAGE_BYTES + 128);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(wsm + 2 * NT * STAGE_BYTES);
+    // per stage and lane: the affine map from the segment's start to the lane's first element and,
+    // for the real types, the map over the first half of the lane's elements (4 floats in all)
+    float4 *lane_prefix = reinterpret_cast<float4 *>(wsm + 2 * NT * STAGE_BYTES + 128);
 
     const int64_t W = static_cast<int64_t>(gridDim.x) * wpc;
     const int64_t T = p.T;
@@ -264,231 +330,282 @@ __global__ void __launch_bounds__(KIND == K_BWD ? 448 : 512, 1) lookback_kernel(
         const int64_t left = d.n - static_cast<int64_t>(t) * TE;
         return left < TE ? static_cast<int>(left) : TE;
     };
-    // step i of an item lives in stage i.  Lane 0 arms the stage's mbarrier, then one lane per
-    // stream issues its copy (and one more the 16 bytes of saved states just below the tile).
-    auto issue = [&](const ItemDesc &d, int i) {
+    // step i of an item in slot `slot` lives in stage slot * NT + i.  Lane 0 arms the stage's
+    // mbarrier, then one lane per stream issues its copy (and one more the 16 bytes of saved
+    // states just below the tile).
+    auto issue = [&](const ItemDesc &d, int slot, int i) {
         const int t = tile_of_step(d, i);
+        const int stage = slot * NT + i;
         const uint32_t bytes = static_cast<uint32_t>(tile_valid(d, t)) * TR::ESIZE;
         const int64_t goff = (d.e_begin + static_cast<int64_t>(t) * TE) * TR::ESIZE;
         const bool halo = BACK && goff > 0;
-        unsigned char *dst = wsm + i * STAGE_BYTES;
-        if (lane == 0) mbar_expect_tx(&bars[i], bytes * NIN + (halo ? 16u : 0u));
+        unsigned char *dst = wsm + stage * STAGE_BYTES;
+        if (lane == 0) mbar_expect_tx(&bars[stage], bytes * NIN + (halo ? 16u : 0u));
         __syncwarp();
-        if (lane < NIN) bulk_g2s(dst + lane * TB, gbase[lane] + goff, bytes, &bars[i]);
-        if (lane == NIN && halo) bulk_g2s(dst + NIN * TB, gbase[2] + goff - 16, 16, &bars[i]);
+        if (lane < NIN) bulk_g2s(dst + lane * TB, gbase[lane] + goff, bytes, &bars[stage]);
+        if (lane == NIN && halo) bulk_g2s(dst + NIN * TB, gbase[2] + goff - 16, 16, &bars[stage]);
     };
 
     if (lane == 0) {
-        for (int s = 0; s < NT; ++s) mbar_init(&bars[s], 1);
+        for (int s = 0; s < 2 * NT; ++s) mbar_init(&bars[s], 1);
         mbar_init_fence();
     }
     __syncwarp();
 
-    // backward: the gate of the step right after a segment, loaded when the item is drawn and
-    // used an item later (the load's latency never shows)
-    using Raw = typename TR::Raw;
+    uint32_t phase_bits = 0;       // bit s: parity to wait for on stage s
+    bool failed = false;
+
+    // backward: the gate of the step right after a segment, loaded when the item is drawn (the
+    // load's latency hides behind the scan pass that runs meanwhile)
     auto end_gate_raw = [&](const ItemDesc &d) -> Raw {
         Raw r = 0;
         if (BACK && d.valid && d.pos0 + d.n < T) r = TR::load_raw(p.in0, d.e_begin + d.n);
         return r;
     };
-    ItemDesc cur = describe(resolve(draw()));
-    if (cur.valid) {
-        for (int i = 0; i < cur.nt; ++i) issue(cur, i);
-    }
-    Raw cur_gate_raw = end_gate_raw(cur);
-    uint32_t phase_bits = 0;       // bit i: parity to wait for on stage i
-    bool failed = false;
-
-    while (cur.valid && !failed) {
-        const uint32_t raw_next = draw();          // resolved when the scan pass starts
-        const int64_t row = cur.row0;
-        const int s = cur.s_log;
-        unsigned char *row_rec = records + static_cast<uint64_t>(row) * per_row * LB_RECORD_BYTES;
-
-        // A wait that expires ends this warp's work: the status bit is set, the warp leaves after
-        // the aggregate pass (when none of its copies is in flight any more) and the launch's
-        // result is invalid.  Every warp gives up at its first expired wait, so a launch whose
-        // partner never shows up ends after about one bound, not one bound per item.
-        bool waits_ok = true;
-        // ---- what the segment needs from outside its own range (backward): the gate of the
-        // step right after it
-        V item_end_gate = vone(V());
-        if (BACK) {
-            if (cur.pos0 + cur.n < T) {
-                item_end_gate = TR::decode(cur_gate_raw);
-            } else if (sharded && sp.rank + 1 < sp.world) {
-                // first gate of the next rank's slice, stored into this rank's exchange buffer
-                const unsigned char *slot = xl + xchg_halo_offset() + (static_cast<uint64_t>(parity_slot) * p.rows + row) * 16;
-                bool got = false;
-                for (uint32_t poll = 0; poll < LB_WAIT_POLLS && !got; ++poll) {
-                    if constexpr (sizeof(V) == 4) {
-                        got = get_word<true>(slot, sp.call, item_end_gate);
-                    } else {
-                        const bool a = get_word<true>(slot, sp.call, item_end_gate.x);
-                        const bool b = get_word<true>(slot + 8, sp.call, item_end_gate.y);
-                        got = a && b;
-                    }
-                    if (!got) __nanosleep(100);
-                }
-                if (!got) {
-                    waits_ok = false;
-                    item_end_gate = vone(V());
-                }
-            } else if (hgate) {
-                item_end_gate = hgate[row];
-            }
-        }
-
-        // One tile from its stage into registers, ready for the two passes: a[] = the gates that
-        // multiply the state entering each element (shifted by one step for the backward), b[] =
-        // the additive terms; beyond the row's end the identity.
-        auto fetch = [&](int i, V *a, V *b, V &next_gate, int &nvalid) {
-            const int t = tile_of_step(cur, i);
-            nvalid = tile_valid(cur, t);
-            const unsigned char *stg = wsm + i * STAGE_BYTES;
-#pragma unroll
-            for (int c = 0; c < NCH; ++c) {
-                TR::unpack(*reinterpret_cast<const uint4 *>(stg + 0 * TB + (lane * NCH + c) * 16), &a[c * EPC]);
-                TR::unpack(*reinterpret_cast<const uint4 *>(stg + 1 * TB + (lane * NCH + c) * 16), &b[c * EPC]);
-            }
-            if (BACK) {
-                const V g0 = a[0];
-                V up = shfl_down(g0, 1);
-                if (lane == 31) up = next_gate;
-#pragma unroll
-                for (int j = 0; j < K - 1; ++j) a[j] = vconj(a[j + 1]);
-                a[K - 1] = vconj(up);
-                next_gate = shfl_idx(g0, 0);
-            }
-            if (nvalid < TE) {
-                const int jv = nvalid - lane * K;
-                const V gate_end = BACK ? vconj(item_end_gate) : vone(V());
-#pragma unroll
-                for (int j = 0; j < K; ++j) {
-                    if (j >= jv) {
-                        a[j] = vone(V());
-                        b[j] = vzero(V());
-                    } else if (BACK && j + 1 >= jv) {
-                        a[j] = gate_end;
-                    }
-                }
-            }
-        };
-
-        // ---------------- aggregate pass: lane prefixes and the segment's aggregate
-        V segA = vone(V()), segB = vzero(V());      // map from the segment's start to the current tile's start
-        {
-            V next_gate = item_end_gate;
-            for (int i = 0; i < cur.nt; ++i) {
-                bool ok = mbar_wait_bounded(&bars[i], (phase_bits >> i) & 1u, LOAD_WAIT_POLLS);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) {
-                    failed = true;
-                    status_bits |= STATUS_LOAD_TIMEOUT;
-                    break;
-                }
-                phase_bits ^= 1u << i;
-                V a[K], b[K];
-                int nvalid;
-                fetch(i, a, b, next_gate, nvalid);
-                V A, B;
-                if constexpr (PACKED) {
-                    auto J = [](int q) { return REV ? K - 1 - q : q; };
-                    float2 Av = make_float2(a[J(0)], a[J(H)]);
-                    float2 Bv = make_float2(b[J(0)], b[J(H)]);
-#pragma unroll
-                    for (int q = 1; q < H; ++q) {
-                        const float2 av = make_float2(a[J(q)], a[J(H + q)]);
-                        const float2 bv = make_float2(b[J(q)], b[J(H + q)]);
-                        Bv = __ffma2_rn(av, Bv, bv);
-                        Av = __fmul2_rn(Av, av);
-                    }
-                    A = Av.x * Av.y;
-                    B = fmaf(Av.y, Bv.x, Bv.y);
+    // ... and decoded, or taken from the halos, when the item's aggregate pass starts
+    auto end_gate = [&](const ItemDesc &d, Raw raw, bool &ok) -> V {
+        V g = vone(V());
+        if (!BACK) return g;
+        if (d.pos0 + d.n < T) return TR::decode(raw);
+        if (sharded && sp.rank + 1 < sp.world) {
+            // first gate of the next rank's slice, stored into this rank's exchange buffer
+            const unsigned char *slot = xl + xchg_halo_offset() + (static_cast<uint64_t>(parity_slot) * p.rows + d.row0) * 16;
+            bool got = false;
+            for (uint32_t poll = 0; poll < LB_WAIT_POLLS && !got; ++poll) {
+                if constexpr (sizeof(V) == 4) {
+                    got = get_word<true>(slot, sp.call, g);
                 } else {
-                    constexpr int JF = REV ? K - 1 : 0;
-                    A = a[JF];
-                    B = b[JF];
+                    const bool a = get_word<true>(slot, sp.call, g.x);
+                    const bool b = get_word<true>(slot + 8, sp.call, g.y);
+                    got = a && b;
+                }
+                if (!got) __nanosleep(100);
+            }
+            if (!got) {
+                ok = false;
+                g = vone(V());
+            }
+            return g;
+        }
+        if (hgate) g = hgate[d.row0];
+        return g;
+    };
+
+    // One tile from its stage into registers, ready for the two passes: a[] = the gates that
+    // multiply the state entering each element (shifted by one step for the backward), b[] = the
+    // additive terms; beyond the row's end the identity.
+    auto fetch = [&](const PendingItem<V> &it, int slot, int i, V *a, V *b, V &next_gate, int &nvalid) {
+        const int t = tile_of_step(it.d, i);
+        nvalid = tile_valid(it.d, t);
+        const unsigned char *stg = wsm + (slot * NT + i) * STAGE_BYTES;
 #pragma unroll
-                    for (int q = 1; q < K; ++q) {
-                        const int j = REV ? K - 1 - q : q;
-                        B = vfma(a[j], B, b[j]);
-                        A = vmul(A, a[j]);
-                    }
-                }
-                // inclusive Kogge-Stone over the lanes in processing order; the map that enters the
-                // tile (segA, segB) goes in through the first lane
-                const int ll = REV ? 31 - lane : lane;
-                if (ll == 0) {
-                    B = vfma(A, segB, B);
-                    A = vmul(A, segA);
-                }
+        for (int c = 0; c < NCH; ++c) {
+            TR::unpack(*reinterpret_cast<const uint4 *>(stg + 0 * TB + (lane * NCH + c) * 16), &a[c * EPC]);
+            TR::unpack(*reinterpret_cast<const uint4 *>(stg + 1 * TB + (lane * NCH + c) * 16), &b[c * EPC]);
+        }
+        if (BACK) {
+            const V g0 = a[0];
+            V up = shfl_down(g0, 1);
+            if (lane == 31) up = next_gate;
 #pragma unroll
-                for (int d = 1; d < 32; d <<= 1) {
-                    const V Ap = REV ? shfl_down(A, d) : shfl_up(A, d);
-                    const V Bp = REV ? shfl_down(B, d) : shfl_up(B, d);
-                    if (ll >= d) {
-                        B = vfma(A, Bp, B);
-                        A = vmul(A, Ap);
-                    }
+            for (int j = 0; j < K - 1; ++j) a[j] = vconj(a[j + 1]);
+            a[K - 1] = vconj(up);
+            next_gate = shfl_idx(g0, 0);
+        }
+        if (nvalid < TE) {
+            const int jv = nvalid - lane * K;
+            const V gate_end = BACK ? vconj(it.end_gate) : vone(V());
+#pragma unroll
+            for (int j = 0; j < K; ++j) {
+                if (j >= jv) {
+                    a[j] = vone(V());
+                    b[j] = vzero(V());
+                } else if (BACK && j + 1 >= jv) {
+                    a[j] = gate_end;
                 }
-                // map from the segment's start to this lane's first element
-                V pA = REV ? shfl_down(A, 1) : shfl_up(A, 1);
-                V pB = REV ? shfl_down(B, 1) : shfl_up(B, 1);
-                if (ll == 0) {
-                    pA = segA;
-                    pB = segB;
-                }
-                lane_prefix[(i * 32 + lane) * 2] = pA;
-                lane_prefix[(i * 32 + lane) * 2 + 1] = pB;
-                segA = shfl_idx(A, REV ? 0 : 31);
-                segB = shfl_idx(B, REV ? 0 : 31);
             }
         }
-        if (failed) break;
+    };
 
-        // ---------------- publish the aggregate, look back
-        if (lane == 0) put_pair<false>(row_rec + static_cast<uint64_t>(s) * LB_RECORD_BYTES, segA, segB, tag);
-        V preA = vone(V()), preB = vzero(V());         // map from the slice's start to the segment's start
-        bool lb_ok = waits_ok;
-        if (s > 0) {
-            const int n0 = s & 31, n1 = (s >> 5) & 31, n2 = s >> 10;
-            V A0 = vone(V()), B0 = vzero(V()), A1 = A0, B1 = B0;
-            // super-blocks 0 .. n2-1, 32 at a time
-            for (int w0 = 0; w0 < n2 && lb_ok; w0 += 32) {
-                V Aw, Bw;
-                const int n = n2 - w0 < 32 ? n2 - w0 : 32;
-                lb_ok = compose_window<V, false>(row_rec + (static_cast<uint64_t>(S) + S1 + w0) * LB_RECORD_BYTES,
-                                                 LB_RECORD_BYTES, n, tag, lane, Aw, Bw);
-                preB = vfma(Aw, preB, Bw);
-                preA = vmul(Aw, preA);
+    // ---------------- aggregate pass of the item in `slot`: lane prefixes, the segment's
+    // aggregate, publication
+    auto aggregate = [&](PendingItem<V> &it, int slot, Raw gate_raw) {
+        it.waits_ok = true;
+        it.end_gate = end_gate(it.d, gate_raw, it.waits_ok);
+        V segA = vone(V()), segB = vzero(V());      // map from the segment's start to the current tile's start
+        V next_gate = it.end_gate;
+        for (int i = 0; i < it.d.nt; ++i) {
+            const int stage = slot * NT + i;
+            bool ok = mbar_wait_bounded(&bars[stage], (phase_bits >> stage) & 1u, LOAD_WAIT_POLLS);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                failed = true;
+                status_bits |= STATUS_LOAD_TIMEOUT;
+                return;
             }
-            if (n1 > 0 && lb_ok)
-                lb_ok = compose_window<V, false>(row_rec + (static_cast<uint64_t>(S) + (static_cast<uint64_t>(s >> 10) << 5)) * LB_RECORD_BYTES,
-                                                 LB_RECORD_BYTES, n1, tag, lane, A1, B1);
-            if (n0 > 0 && lb_ok)
-                lb_ok = compose_window<V, false>(row_rec + (static_cast<uint64_t>(s >> 5) << 5) * LB_RECORD_BYTES,
-                                                 LB_RECORD_BYTES, n0, tag, lane, A0, B0);
-            // closing duties: the last segment of a block publishes the block, the last block of a
-            // super-block the super-block (only full ones are ever read)
-            if (n0 == 31) {
-                const V Ab = vmul(segA, A0), Bb = vfma(segA, B0, segB);          // this segment after the 31 before it
-                if (lane == 0) put_pair<false>(row_rec + (static_cast<uint64_t>(S) + (s >> 5)) * LB_RECORD_BYTES, Ab, Bb, tag);
-                if (n1 == 31) {
-                    const V Ac = vmul(Ab, A1), Bc = vfma(Ab, B1, Bb);
-                    if (lane == 0)
-                        put_pair<false>(row_rec + (static_cast<uint64_t>(S) + S1 + (s >> 10)) * LB_RECORD_BYTES, Ac, Bc, tag);
+            phase_bits ^= 1u << stage;
+            V a[K], b[K];
+            int nvalid;
+            fetch(it, slot, i, a, b, next_gate, nvalid);
+            V A, B;
+            V A0h = vone(V()), B0h = vzero(V());     // real types: the map over the first half of the lane's elements
+            if constexpr (PACKED) {
+                auto J = [](int q) { return REV ? K - 1 - q : q; };
+                float2 Av = make_float2(a[J(0)], a[J(H)]);
+                float2 Bv = make_float2(b[J(0)], b[J(H)]);
+#pragma unroll
+                for (int q = 1; q < H; ++q) {
+                    const float2 av = make_float2(a[J(q)], a[J(H + q)]);
+                    const float2 bv = make_float2(b[J(q)], b[J(H + q)]);
+                    Bv = __ffma2_rn(av, Bv, bv);
+                    Av = __fmul2_rn(Av, av);
+                }
+                A0h = Av.x;
+                B0h = Bv.x;
+                A = Av.x * Av.y;
+                B = fmaf(Av.y, Bv.x, Bv.y);
+            } else {
+                constexpr int JF = REV ? K - 1 : 0;
+                A = a[JF];
+                B = b[JF];
+#pragma unroll
+                for (int q = 1; q < K; ++q) {
+                    const int j = REV ? K - 1 - q : q;
+                    B = vfma(a[j], B, b[j]);
+                    A = vmul(A, a[j]);
                 }
             }
-            // super-blocks first, then blocks, then segments
-            preB = vfma(A1, preB, B1);
-            preA = vmul(A1, preA);
-            preB = vfma(A0, preB, B0);
-            preA = vmul(A0, preA);
+            // inclusive Kogge-Stone over the lanes in processing order; the map that enters the
+            // tile (segA, segB) goes in through the first lane
+            const int ll = REV ? 31 - lane : lane;
+            if (ll == 0) {
+                B = vfma(A, segB, B);
+                A = vmul(A, segA);
+            }
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const V Ap = REV ? shfl_down(A, d) : shfl_up(A, d);
+                const V Bp = REV ? shfl_down(B, d) : shfl_up(B, d);
+                if (ll >= d) {
+                    B = vfma(A, Bp, B);
+                    A = vmul(A, Ap);
+                }
+            }
+            // map from the segment's start to this lane's first element
+            V pA = REV ? shfl_down(A, 1) : shfl_up(A, 1);
+            V pB = REV ? shfl_down(B, 1) : shfl_up(B, 1);
+            if (ll == 0) {
+                pA = segA;
+                pB = segB;
+            }
+            if constexpr (sizeof(V) == 4) {
+                lane_prefix[stage * 32 + lane] = make_float4(pA, pB, A0h, B0h);
+            } else {
+                lane_prefix[stage * 32 + lane] = make_float4(pA.x, pA.y, pB.x, pB.y);
+            }
+            segA = shfl_idx(A, REV ? 0 : 31);
+            segB = shfl_idx(B, REV ? 0 : 31);
+        }
+        it.segA = segA;
+        it.segB = segB;
+        unsigned char *row_rec = records + static_cast<uint64_t>(it.d.row0) * per_row * LB_RECORD_BYTES;
+        const int s = it.d.s_log;
+        if (lane == 0) put_pair<false>(row_rec + static_cast<uint64_t>(s) * LB_RECORD_BYTES, segA, segB, tag);
+        // Closing duties.  The last segment of a block publishes the block's aggregate (this
+        // segment after the 31 before it), the last block of a super-block the super-block's.
+        // They wait only for aggregates of items drawn earlier, which nobody holds back, and the
+        // warp holds no unpublished item while it waits; the records are there long before the
+        // look-backs that read them.  Only full blocks and super-blocks are ever read.
+        if ((s & 31) == 31) {
+            V A0, B0;
+            bool ok = compose_window<V, false>(row_rec + static_cast<uint64_t>(s - 31) * LB_RECORD_BYTES, LB_RECORD_BYTES, 31,
+                                               tag, lane, A0, B0);
+            const V Ab = vmul(segA, A0), Bb = vfma(segA, B0, segB);
+            if (ok && lane == 0) put_pair<false>(row_rec + (static_cast<uint64_t>(S) + (s >> 5)) * LB_RECORD_BYTES, Ab, Bb, tag);
+            if (ok && ((s >> 5) & 31) == 31) {
+                V A1, B1;
+                ok = compose_window<V, false>(row_rec + (static_cast<uint64_t>(S) + (s >> 5) - 31) * LB_RECORD_BYTES,
+                                              LB_RECORD_BYTES, 31, tag, lane, A1, B1);
+                if (ok && lane == 0)
+                    put_pair<false>(row_rec + (static_cast<uint64_t>(S) + S1 + (s >> 10)) * LB_RECORD_BYTES, vmul(Ab, A1),
+                                    vfma(Ab, B1, Bb), tag);
+            }
+            if (!ok) it.waits_ok = false;
+        }
+    };
+
+    PendingItem<V> cur, nxt;
+    cur.d = describe(resolve(draw()));
+    cur.segA = vone(V()); cur.segB = vzero(V()); cur.end_gate = vone(V()); cur.waits_ok = true;
+    nxt = cur;
+    int cur_slot = 0;
+    if (cur.d.valid) {
+        for (int i = 0; i < cur.d.nt; ++i) issue(cur.d, 0, i);
+        const Raw g_raw = end_gate_raw(cur.d);
+        nxt.d = describe(resolve(draw()));
+        if (nxt.d.valid) {
+            for (int i = 0; i < nxt.d.nt; ++i) issue(nxt.d, 1, i);
+        }
+        aggregate(cur, 0, g_raw);
+    }
+    Raw nxt_gate_raw = end_gate_raw(nxt.d);
+
+#ifdef LB_DEBUG_TIMING
+    unsigned long long dbg[6] = {0, 0, 0, 0, 0, 0};
+    auto now = []() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; };
+    unsigned long long t_mark = now();
+#define LB_MARK(k) { unsigned long long t_ = now(); dbg[k] += t_ - t_mark; t_mark = t_; }
+#else
+#define LB_MARK(k)
+#endif
+    while (cur.d.valid && !failed) {
+        const int nxt_slot = cur_slot ^ 1;
+        // ---------------- aggregate pass of the item after this one
+        if (nxt.d.valid) aggregate(nxt, nxt_slot, nxt_gate_raw);
+        if (failed) break;
+        LB_MARK(1)
+
+        // ---------------- look back for this item
+        const int64_t row = cur.d.row0;
+        const int s = cur.d.s_log;
+        unsigned char *row_rec = records + static_cast<uint64_t>(row) * per_row * LB_RECORD_BYTES;
+        const V segA = cur.segA, segB = cur.segB;
+        // A wait that expires ends this warp's work: the status bit is set and the warp leaves
+        // (none of its copies is in flight at this point: both resident segments have been
+        // aggregated).  Every warp gives up at its first expired wait, so a launch whose partner
+        // never shows up ends after about one bound, not one bound per item.
+        bool lb_ok = cur.waits_ok && nxt.waits_ok;
+        V preA = vone(V()), preB = vzero(V());         // map from the slice's start to the segment's start
+        if (s > 0 && lb_ok) {
+            // Segments, blocks and super-blocks are read at once (one round trip when they are there).
+            const int n0 = s & 31, n1 = (s >> 5) & 31, n2 = s >> 10;
+            const unsigned char *base[3] = {
+                row_rec + (static_cast<uint64_t>(s >> 5) << 5) * LB_RECORD_BYTES,
+                row_rec + (static_cast<uint64_t>(S) + (static_cast<uint64_t>(s >> 10) << 5)) * LB_RECORD_BYTES,
+                row_rec + (static_cast<uint64_t>(S) + S1) * LB_RECORD_BYTES};
+            const int n[3] = {n0, n1, n2 < 32 ? n2 : 32};
+            V Aw[3], Bw[3];
+            lb_ok = compose_three<V>(base, n, tag, lane, Aw, Bw);
+            // further super-blocks of very long rows, 32 at a time, in order
+            V A2 = Aw[2], B2 = Bw[2];
+            for (int w0 = 32; w0 < n2 && lb_ok; w0 += 32) {
+                V Ax, Bx;
+                const int nn = n2 - w0 < 32 ? n2 - w0 : 32;
+                lb_ok = compose_window<V, false>(row_rec + (static_cast<uint64_t>(S) + S1 + w0) * LB_RECORD_BYTES,
+                                                 LB_RECORD_BYTES, nn, tag, lane, Ax, Bx);
+                B2 = vfma(Ax, B2, Bx);
+                A2 = vmul(Ax, A2);
+            }
+            // the map from the slice's start: super-blocks, then blocks, then segments
+            preA = A2;
+            preB = B2;
+            preB = vfma(Aw[1], preB, Bw[1]);
+            preA = vmul(Aw[1], preA);
+            preB = vfma(Aw[0], preB, Bw[0]);
+            preA = vmul(Aw[0], preA);
         }
         // the slice ends with this segment: its aggregate goes to the ranks that come later
-        if (sharded && s == S - 1 && n_after > 0) {
+        if (sharded && s == S - 1 && n_after > 0 && lb_ok) {
             const V Ps = vmul(segA, preA), Ss = vfma(segA, preB, segB);
             if (lane < n_after) {
                 const int target = REV ? sp.rank - 1 - lane : sp.rank + 1 + lane;
@@ -527,26 +644,40 @@ __global__ void __launch_bounds__(KIND == K_BWD ? 448 : 512, 1) lookback_kernel(
             break;
         }
         const V x_in = vfma(preA, x_slice, preB);
+        LB_MARK(2)
 
         // ---------------- scan pass from shared memory; stages are refilled as they drain
-        ItemDesc nxt = describe(resolve(raw_next));
-        const Raw nxt_gate_raw = end_gate_raw(nxt);
+        // The number of the item after the next is drawn only now (see the head of the kernel).
+        const uint32_t raw_after = draw();
+        PendingItem<V> aft = cur;
+        aft.d.valid = false;
+        Raw aft_gate_raw = 0;
+        bool aft_known = false;
+        auto learn_after = [&]() {
+            if (!aft_known) {
+                aft.d = describe(nxt.d.valid ? resolve(raw_after) : p.items);
+                aft_gate_raw = end_gate_raw(aft.d);
+                aft_known = true;
+            }
+        };
         {
-            V next_gate = item_end_gate;
-            for (int i = 0; i < cur.nt; ++i) {
+            V next_gate = cur.end_gate;
+            const int nt = cur.d.nt;
+            for (int i = 0; i < nt; ++i) {
                 V a[K], b[K];
                 int nvalid;
-                fetch(i, a, b, next_gate, nvalid);
-                const int t = tile_of_step(cur, i);
+                fetch(cur, cur_slot, i, a, b, next_gate, nvalid);
+                const int t = tile_of_step(cur.d, i);
                 const int64_t toff = static_cast<int64_t>(t) * TE;
-                unsigned char *stg = wsm + i * STAGE_BYTES;
+                const int stage = cur_slot * NT + i;
+                unsigned char *stg = wsm + stage * STAGE_BYTES;
                 V xp[BACK ? K : 1];
                 V x_below = vzero(V());
                 if (BACK) {
 #pragma unroll
                     for (int c = 0; c < NCH; ++c)
                         TR::unpack(*reinterpret_cast<const uint4 *>(stg + 2 * TB + (lane * NCH + c) * 16), &xp[c * EPC]);
-                    if (cur.pos0 + toff != 0) {
+                    if (cur.d.pos0 + toff != 0) {
                         V hv[EPC];
                         TR::unpack(*reinterpret_cast<const uint4 *>(stg + NIN * TB), hv);
                         x_below = hv[EPC - 1];
@@ -554,18 +685,11 @@ __global__ void __launch_bounds__(KIND == K_BWD ? 448 : 512, 1) lookback_kernel(
                         x_below = hstate[row];
                     }
                 }
-                const V pA = lane_prefix[(i * 32 + lane) * 2], pB = lane_prefix[(i * 32 + lane) * 2 + 1];
-                V x = vfma(pA, x_in, pB);
+                const float4 pf = lane_prefix[stage * 32 + lane];
                 if constexpr (PACKED) {
                     auto J = [](int q) { return REV ? K - 1 - q : q; };
-                    // the state entering the second half of the lane's elements: run the first half's map
-                    float A0h = a[J(0)], B0h = b[J(0)];
-#pragma unroll
-                    for (int q = 1; q < H; ++q) {
-                        B0h = fmaf(a[J(q)], B0h, b[J(q)]);
-                        A0h *= a[J(q)];
-                    }
-                    float2 Xv = make_float2(x, fmaf(A0h, x, B0h));
+                    const float x = fmaf(pf.x, x_in, pf.y);
+                    float2 Xv = make_float2(x, fmaf(pf.z, x, pf.w));       // states entering the two halves
 #pragma unroll
                     for (int q = 0; q < H; ++q) {
                         const float2 av = make_float2(a[J(q)], a[J(H + q)]);
@@ -575,6 +699,12 @@ __global__ void __launch_bounds__(KIND == K_BWD ? 448 : 512, 1) lookback_kernel(
                         b[J(H + q)] = Xv.y;
                     }
                 } else {
+                    V x;
+                    if constexpr (sizeof(V) == 4) {
+                        x = vfma(pf.x, x_in, pf.y);
+                    } else {
+                        x = vfma(make_float2(pf.x, pf.y), x_in, make_float2(pf.z, pf.w));
+                    }
 #pragma unroll
                     for (int q = 0; q < K; ++q) {
                         const int j = REV ? K - 1 - q : q;
@@ -601,7 +731,7 @@ __global__ void __launch_bounds__(KIND == K_BWD ? 448 : 512, 1) lookback_kernel(
                 __syncwarp();
                 if (lane == 0) {
                     const uint32_t bytes = static_cast<uint32_t>(nvalid) * TR::ESIZE;
-                    const int64_t goff = (cur.e_begin + toff) * TR::ESIZE;
+                    const int64_t goff = (cur.d.e_begin + toff) * TR::ESIZE;
                     bulk_s2g(obase[0] + goff, stg + 1 * TB, bytes);
                     if (NOUT > 1) bulk_s2g(obase[1] + goff, stg + 2 * TB, bytes);
                     bulk_commit();
@@ -609,17 +739,34 @@ __global__ void __launch_bounds__(KIND == K_BWD ? 448 : 512, 1) lookback_kernel(
                     if (i > 0) bulk_wait_read<1>();
                 }
                 __syncwarp();
-                if (i > 0 && nxt.valid && i - 1 < nxt.nt) issue(nxt, i - 1);
+                if (i > 0) {
+                    learn_after();
+                    if (aft.d.valid && i - 1 < aft.d.nt) issue(aft.d, cur_slot, i - 1);
+                }
             }
+            learn_after();
+            LB_MARK(3)
             if (lane == 0) bulk_wait_read<0>();
             __syncwarp();
-            if (nxt.valid) {
-                for (int i = cur.nt - 1; i < nxt.nt; ++i) issue(nxt, i);
+            LB_MARK(4)
+            if (aft.d.valid) {
+                for (int i = nt - 1; i < aft.d.nt; ++i) issue(aft.d, cur_slot, i);
             }
         }
         cur = nxt;
-        cur_gate_raw = nxt_gate_raw;
+        nxt = aft;
+        nxt_gate_raw = aft_gate_raw;
+        cur_slot = nxt_slot;
+#ifdef LB_DEBUG_TIMING
+        dbg[5] += 1;
+#endif
     }
+#ifdef LB_DEBUG_TIMING
+    if (p.carry_out && lane == 0) {
+        unsigned long long *o = static_cast<unsigned long long *>(p.carry_out) + (static_cast<int64_t>(blockIdx.x) * wpc + wib) * 8;
+        for (int k = 0; k < 6; ++k) o[k] = dbg[k];
+    }
+#endif
 
     if (lane == 0) bulk_wait_read<0>();
     __syncwarp();

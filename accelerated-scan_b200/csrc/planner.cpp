@@ -101,7 +101,7 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     // of time-sharded calls, whatever their row count.
     const bool scan_kind = in.kind == ASCAN_KIND_FORWARD || in.kind == ASCAN_KIND_BACKWARD;
     {
-        int lb_tiles = in.tune.lookback_tiles > 0 ? in.tune.lookback_tiles : (in.kind == ASCAN_KIND_BACKWARD ? 3 : 4);
+        int lb_tiles = in.tune.lookback_tiles > 0 ? in.tune.lookback_tiles : 2;
         if (lb_tiles > 8) lb_tiles = 8;
         // below three rows per four SMs (measured on 148 SMs: at 96 rows look-back and teams of 12
         // warps tie, at 128 rows the teams win by 10-20 %)
@@ -112,11 +112,11 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
         const bool wanted = in.force_lookback || (in.allow_lookback && in.rows < lookback_rows && tiles_row3 >= 2 * lb_tiles);
         const int64_t segs = (in.seqlen + lb_tiles * te3 - 1) / (lb_tiles * te3);
         if (possible && wanted && in.rows * segs < (1ll << 31)) {
-            const int vsize = esize == 8 ? 8 : 4;
+            // two resident segments per warp (lb_warp_smem in lookback.cuh)
             const int stage = nin_of(in.kind) * 32 * 3 * 16 + (in.kind == ASCAN_KIND_BACKWARD ? 128 : 0);
-            const int wsm = lb_tiles * stage + 128 + lb_tiles * 32 * 2 * vsize;      // lb_warp_smem in lookback.cuh
+            const int wsm = 2 * lb_tiles * stage + 128 + 2 * lb_tiles * 32 * 16;
             int wpc = kMaxSmemPerCta / wsm;
-            const int cap = in.kind == ASCAN_KIND_BACKWARD ? 14 : 16;
+            const int cap = 16;
             if (wpc > cap) wpc = cap;
             if (in.tune.warps_per_cta > 0 && in.tune.warps_per_cta < wpc) wpc = in.tune.warps_per_cta;
             if (wpc < 1) return ASCAN_ERR_UNSUPPORTED;

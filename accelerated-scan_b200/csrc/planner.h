@@ -21,7 +21,7 @@ constexpr int kCarryRecordBytes = 32;        // per-row carry record behind it
 struct PlanTuning {
     int stages = 2;            // shared-memory stages per warp of the stream and team kernels
     int warps_per_cta = 0;     // 0 = planner's choice; otherwise an upper bound
-    int lookback_tiles = 0;    // tiles per segment of the look-back plan; 0 = 4 (forward) or 3 (fused backward)
+    int lookback_tiles = 0;    // tiles per segment of the look-back plan; 0 = the default (2)
     int disable_plans = 0;     // bit 0: no look-back, bit 1: no team, bit 2: static deal (no tickets), bit 3: plain loader
 };
 
