@@ -16,8 +16,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "accelerated_scan", "libascan_b200.so")
 SOURCES = ["api.cu", "planner.cpp", "inst_f32.cu", "inst_bf16.cu", "inst_f16.cu", "inst_c64.cu"]
-HEADERS = ["common.cuh", "stream.cuh", "team.cuh", "dispatch.cuh", "launch.h", "planner.h",
-           os.path.join("..", "..", "include", "ascan_b200.h")]
+HEADERS = sorted(f for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))) + [
+    os.path.join("..", "..", "include", "ascan_b200.h")]
 OBJ_DIR = os.path.join(HERE, "build", "obj")
 
 

@@ -260,7 +260,10 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
     const V *hgate = static_cast<const V *>(p.halo_gate);
     const V *hstate = static_cast<const V *>(p.halo_state);
 
-    const uint32_t tag = *reinterpret_cast<volatile uint32_t *>(p.ctrl + CTRL_EPOCH) + 1u;   // never zero
+    // Tag of this launch's records: the launch epoch above fifteen one-bits.  Never zero, and never
+    // equal to a carry tag of the chained plans (epoch above a segment number below 32767), which
+    // may have left words in the same workspace.
+    const uint32_t tag = (*reinterpret_cast<volatile uint32_t *>(p.ctrl + CTRL_EPOCH) << EPOCH_SHIFT) | 0x7fffu;
     const uint64_t S1 = lb_level_count(S), S2 = lb_level_count(static_cast<int64_t>(S1));
     const uint64_t per_row = static_cast<uint64_t>(S) + S1 + S2;
     unsigned char *records = p.records;
