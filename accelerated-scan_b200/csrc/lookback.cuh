@@ -66,10 +66,14 @@ struct ShardParams {
 __host__ __device__ constexpr int lb_stage_bytes(int nch, int kind) {
     return stream_nin(kind) * 32 * nch * 16 + (kind == K_BWD ? 128 : 0);
 }
-// Two resident segments of `nt` tiles per warp, their mbarriers, and 16 bytes per stage and lane
-// of prefix maps.
+// The forward kinds send their results through a staging tile of their own, so that a stage can
+// be refilled as soon as its tile is in registers; the fused backward writes its two results over
+// the stage's inputs (a staging area would cost it two warps per CTA).
+__host__ __device__ constexpr int lb_staging_bytes(int nch, int kind) { return kind == K_BWD ? 0 : 32 * nch * 16; }
+// Two resident segments of `nt` tiles per warp, the staging tile, the mbarriers, and 16 bytes per
+// stage and lane of prefix maps.
 __host__ __device__ constexpr int lb_warp_smem(int nch, int nt, int kind) {
-    return 2 * nt * lb_stage_bytes(nch, kind) + 128 + 2 * nt * 32 * 16;
+    return 2 * nt * lb_stage_bytes(nch, kind) + lb_staging_bytes(nch, kind) + 128 + 2 * nt * 32 * 16;
 }
 // Workspace of the look-back plan: control block, then the records of the three levels.
 __host__ __device__ constexpr uint64_t lb_level_count(int64_t n) { return static_cast<uint64_t>((n + 31) / 32); }
@@ -162,9 +166,26 @@ __device__ __forceinline__ bool compose_window(const unsigned char *base, int64_
 // Reads up to three windows of records at once (lane i reads record i of each) and polls only
 // for those still missing, so a look-back whose records are all there costs one round trip.
 // Window w: n[w] records from base[w]; result (A[w], B[w]) as in compose_window.
+// The words of a real-valued look-back (three windows of {A, B}), loaded ahead of time.
+struct RecordWords {
+    uint64_t w[6];
+};
+__device__ __forceinline__ RecordWords load_record_words(const unsigned char *const base[3], const int n[3], int lane) {
+    RecordWords r;
+#pragma unroll
+    for (int w = 0; w < 3; ++w) {
+        r.w[2 * w] = r.w[2 * w + 1] = 0;
+        if (lane < n[w]) {
+            r.w[2 * w] = ld_relaxed_u64(base[w] + lane * LB_RECORD_BYTES);
+            r.w[2 * w + 1] = ld_relaxed_u64(base[w] + lane * LB_RECORD_BYTES + 8);
+        }
+    }
+    return r;
+}
+
 template <class V>
 __device__ __forceinline__ bool compose_three(const unsigned char *const base[3], const int n[3], uint32_t tag, int lane,
-                                              V A[3], V B[3]) {
+                                              V A[3], V B[3], const RecordWords *ahead = nullptr) {
     V a[3], b[3];
     bool ok[3];
 #pragma unroll
@@ -172,6 +193,20 @@ __device__ __forceinline__ bool compose_three(const unsigned char *const base[3]
         a[w] = vone(V());
         b[w] = vzero(V());
         ok[w] = lane >= n[w];
+    }
+    if constexpr (sizeof(V) == 4) {
+        // words loaded before the aggregate pass of the next item: normally all of them are valid
+        if (ahead) {
+#pragma unroll
+            for (int w = 0; w < 3; ++w) {
+                if (!ok[w] && static_cast<uint32_t>(ahead->w[2 * w] >> 32) == tag &&
+                    static_cast<uint32_t>(ahead->w[2 * w + 1] >> 32) == tag) {
+                    a[w] = __uint_as_float(static_cast<uint32_t>(ahead->w[2 * w]));
+                    b[w] = __uint_as_float(static_cast<uint32_t>(ahead->w[2 * w + 1]));
+                    ok[w] = true;
+                }
+            }
+        }
     }
     bool all = false;
     for (uint32_t poll = 0; poll < LB_WAIT_POLLS; ++poll) {
@@ -244,10 +279,13 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
     const int wib = threadIdx.x >> 5;
     const int wpc = blockDim.x >> 5;
     unsigned char *wsm = smem_raw + static_cast<size_t>(wib) * WARP_SMEM;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(wsm + 2 * NT * STAGE_BYTES);
+    constexpr bool STAGED = !BACK;                            // results leave through a staging tile
+    constexpr int STAGING_BYTES = lb_staging_bytes(NCH, KIND);
+    unsigned char *staging = wsm + 2 * NT * STAGE_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(wsm + 2 * NT * STAGE_BYTES + STAGING_BYTES);
     // per stage and lane: the affine map from the segment's start to the lane's first element and,
     // for the real types, the map over the first half of the lane's elements (4 floats in all)
-    float4 *lane_prefix = reinterpret_cast<float4 *>(wsm + 2 * NT * STAGE_BYTES + 128);
+    float4 *lane_prefix = reinterpret_cast<float4 *>(wsm + 2 * NT * STAGE_BYTES + STAGING_BYTES + 128);
 
     const int64_t W = static_cast<int64_t>(gridDim.x) * wpc;
     const int64_t T = p.T;
@@ -563,15 +601,28 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
 #endif
     while (cur.d.valid && !failed) {
         const int nxt_slot = cur_slot ^ 1;
+        const int64_t row = cur.d.row0;
+        const int s = cur.d.s_log;
+        unsigned char *row_rec = records + static_cast<uint64_t>(row) * per_row * LB_RECORD_BYTES;
+        // the records this item's look-back will read: segments of its block, blocks of its
+        // super-block, super-blocks before it
+        const int n0 = s & 31, n1 = (s >> 5) & 31, n2 = s >> 10;
+        const unsigned char *lb_base[3] = {
+            row_rec + (static_cast<uint64_t>(s >> 5) << 5) * LB_RECORD_BYTES,
+            row_rec + (static_cast<uint64_t>(S) + (static_cast<uint64_t>(s >> 10) << 5)) * LB_RECORD_BYTES,
+            row_rec + (static_cast<uint64_t>(S) + S1) * LB_RECORD_BYTES};
+        const int lb_n[3] = {n0, n1, n2 < 32 ? n2 : 32};
+        // real types: load them now, use them after the aggregate pass below (they were published
+        // an iteration ago, so this hides the round trip; what is missing is polled for later)
+        RecordWords ahead;
+        if constexpr (sizeof(V) == 4) ahead = load_record_words(lb_base, lb_n, lane);
+
         // ---------------- aggregate pass of the item after this one
         if (nxt.d.valid) aggregate(nxt, nxt_slot, nxt_gate_raw);
         if (failed) break;
         LB_MARK(1)
 
         // ---------------- look back for this item
-        const int64_t row = cur.d.row0;
-        const int s = cur.d.s_log;
-        unsigned char *row_rec = records + static_cast<uint64_t>(row) * per_row * LB_RECORD_BYTES;
         const V segA = cur.segA, segB = cur.segB;
         // A wait that expires ends this warp's work: the status bit is set and the warp leaves
         // (none of its copies is in flight at this point: both resident segments have been
@@ -580,15 +631,9 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
         bool lb_ok = cur.waits_ok && nxt.waits_ok;
         V preA = vone(V()), preB = vzero(V());         // map from the slice's start to the segment's start
         if (s > 0 && lb_ok) {
-            // Segments, blocks and super-blocks are read at once (one round trip when they are there).
-            const int n0 = s & 31, n1 = (s >> 5) & 31, n2 = s >> 10;
-            const unsigned char *base[3] = {
-                row_rec + (static_cast<uint64_t>(s >> 5) << 5) * LB_RECORD_BYTES,
-                row_rec + (static_cast<uint64_t>(S) + (static_cast<uint64_t>(s >> 10) << 5)) * LB_RECORD_BYTES,
-                row_rec + (static_cast<uint64_t>(S) + S1) * LB_RECORD_BYTES};
-            const int n[3] = {n0, n1, n2 < 32 ? n2 : 32};
+            // Segments, blocks and super-blocks at once.
             V Aw[3], Bw[3];
-            lb_ok = compose_three<V>(base, n, tag, lane, Aw, Bw);
+            lb_ok = compose_three<V>(lb_base, lb_n, tag, lane, Aw, Bw, sizeof(V) == 4 ? &ahead : nullptr);
             // further super-blocks of very long rows, 32 at a time, in order
             V A2 = Aw[2], B2 = Bw[2];
             for (int w0 = 32; w0 < n2 && lb_ok; w0 += 32) {
@@ -650,7 +695,10 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
         LB_MARK(2)
 
         // ---------------- scan pass from shared memory; stages are refilled as they drain
-        // The number of the item after the next is drawn only now (see the head of the kernel).
+        // The number of the item after the next is drawn only now, after the look-back: from this
+        // draw to the publication of that item's aggregate the warp waits for nothing but memory,
+        // so a drawn item is never held back by its owner waiting in a look-back.  (Drawn before
+        // the look-back, such waits chained up across warps and cost 40 % of the throughput.)
         const uint32_t raw_after = draw();
         PendingItem<V> aft = cur;
         aft.d.valid = false;
@@ -689,6 +737,18 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
                     }
                 }
                 const float4 pf = lane_prefix[stage * 32 + lane];
+                if constexpr (STAGED) {
+                    // the tile is in registers: its stage can take the matching tile of the item
+                    // after the next (whose number arrives during the first tile; the first stage
+                    // is refilled together with the second)
+                    __syncwarp();
+                    fence_async_smem();
+                    if (i >= 1) {
+                        learn_after();
+                        if (i == 1 && aft.d.valid) issue(aft.d, cur_slot, 0);
+                        if (aft.d.valid && i < aft.d.nt) issue(aft.d, cur_slot, i);
+                    }
+                }
                 if constexpr (PACKED) {
                     auto J = [](int q) { return REV ? K - 1 - q : q; };
                     const float x = fmaf(pf.x, x_in, pf.y);
@@ -723,37 +783,62 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
                     for (int j = K - 1; j >= 1; --j) a[j] = vmul(vconj(xp[j - 1]), b[j]);
                     a[0] = vmul(vconj(dn), b[0]);
                 }
-                // results over the inputs of the stage, then out by bulk copies
-                __syncwarp();
+                if constexpr (STAGED) {
+                    // results into the staging tile (once the store before has read it), then out
+                    if (lane == 0) bulk_wait_read<0>();
+                    __syncwarp();
 #pragma unroll
-                for (int c = 0; c < NCH; ++c) {
-                    *reinterpret_cast<uint4 *>(stg + 1 * TB + (lane * NCH + c) * 16) = TR::pack(&b[c * EPC]);
-                    if (NOUT > 1) *reinterpret_cast<uint4 *>(stg + 2 * TB + (lane * NCH + c) * 16) = TR::pack(&a[c * EPC]);
-                }
-                fence_async_smem();
-                __syncwarp();
-                if (lane == 0) {
-                    const uint32_t bytes = static_cast<uint32_t>(nvalid) * TR::ESIZE;
-                    const int64_t goff = (cur.d.e_begin + toff) * TR::ESIZE;
-                    bulk_s2g(obase[0] + goff, stg + 1 * TB, bytes);
-                    if (NOUT > 1) bulk_s2g(obase[1] + goff, stg + 2 * TB, bytes);
-                    bulk_commit();
-                    // the store of the stage before this one has read its data: refill that stage
-                    if (i > 0) bulk_wait_read<1>();
-                }
-                __syncwarp();
-                if (i > 0) {
-                    learn_after();
-                    if (aft.d.valid && i - 1 < aft.d.nt) issue(aft.d, cur_slot, i - 1);
+                    for (int c = 0; c < NCH; ++c)
+                        *reinterpret_cast<uint4 *>(staging + (lane * NCH + c) * 16) = TR::pack(&b[c * EPC]);
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        bulk_s2g(obase[0] + (cur.d.e_begin + toff) * TR::ESIZE, staging, static_cast<uint32_t>(nvalid) * TR::ESIZE);
+                        bulk_commit();
+                    }
+                } else {
+                    // results over the inputs of the stage, then out by bulk copies
+                    __syncwarp();
+#pragma unroll
+                    for (int c = 0; c < NCH; ++c) {
+                        *reinterpret_cast<uint4 *>(stg + 1 * TB + (lane * NCH + c) * 16) = TR::pack(&b[c * EPC]);
+                        if (NOUT > 1) *reinterpret_cast<uint4 *>(stg + 2 * TB + (lane * NCH + c) * 16) = TR::pack(&a[c * EPC]);
+                    }
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        const uint32_t bytes = static_cast<uint32_t>(nvalid) * TR::ESIZE;
+                        const int64_t goff = (cur.d.e_begin + toff) * TR::ESIZE;
+                        bulk_s2g(obase[0] + goff, stg + 1 * TB, bytes);
+                        if (NOUT > 1) bulk_s2g(obase[1] + goff, stg + 2 * TB, bytes);
+                        bulk_commit();
+                        // the store of the stage before this one has read its data: refill that stage
+                        if (i > 0) bulk_wait_read<1>();
+                    }
+                    __syncwarp();
+                    if (i > 0) {
+                        learn_after();
+                        if (aft.d.valid && i - 1 < aft.d.nt) issue(aft.d, cur_slot, i - 1);
+                    }
                 }
             }
             learn_after();
             LB_MARK(3)
-            if (lane == 0) bulk_wait_read<0>();
-            __syncwarp();
-            LB_MARK(4)
-            if (aft.d.valid) {
-                for (int i = nt - 1; i < aft.d.nt; ++i) issue(aft.d, cur_slot, i);
+            if constexpr (STAGED) {
+                // stages the loop did not refill: the only one of a one-tile item, and those the
+                // item after the next has beyond this item's tiles
+                if (aft.d.valid) {
+                    if (nt == 1) issue(aft.d, cur_slot, 0);
+                    for (int i = nt > 1 ? nt : 1; i < aft.d.nt; ++i) issue(aft.d, cur_slot, i);
+                }
+                LB_MARK(4)
+            } else {
+                if (lane == 0) bulk_wait_read<0>();
+                __syncwarp();
+                LB_MARK(4)
+                if (aft.d.valid) {
+                    for (int i = nt - 1; i < aft.d.nt; ++i) issue(aft.d, cur_slot, i);
+                }
             }
         }
         cur = nxt;

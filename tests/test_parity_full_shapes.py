@@ -102,6 +102,6 @@ def test_length_sweep_shapes_bf16(cuda_device, L):
     """(8, 1536, L) bf16: at 12288 rows the short rows take the kernels that group rows per item."""
     from accelerated_scan import _native
 
-    if L <= 1024:
+    if L <= 256:
         assert _native.plan(8 * 1536, L, _native.BF16, _native.KIND_FORWARD)["rows_per_item"] > 1
     _check(cuda_device, (8, 1536, L), torch.bfloat16, "near_one", 200 + L, "native")
