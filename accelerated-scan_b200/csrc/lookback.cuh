@@ -468,6 +468,40 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
         }
     };
 
+    // The map from the slice's start to the start of segment `s` of a row, from the records of
+    // the segments of its block, the blocks of its super-block and the super-blocks before it
+    // (fixed order: super-blocks, then blocks, then segments).  false when a wait expires.
+    auto local_prefix = [&](unsigned char *row_rec, int s, V &preA, V &preB, const RecordWords *ahead) -> bool {
+        preA = vone(V());
+        preB = vzero(V());
+        if (s == 0) return true;
+        const int n2 = s >> 10;
+        const unsigned char *base[3] = {
+            row_rec + (static_cast<uint64_t>(s >> 5) << 5) * LB_RECORD_BYTES,
+            row_rec + (static_cast<uint64_t>(S) + (static_cast<uint64_t>(s >> 10) << 5)) * LB_RECORD_BYTES,
+            row_rec + (static_cast<uint64_t>(S) + S1) * LB_RECORD_BYTES};
+        const int n[3] = {s & 31, (s >> 5) & 31, n2 < 32 ? n2 : 32};
+        V Aw[3], Bw[3];
+        bool ok = compose_three<V>(base, n, tag, lane, Aw, Bw, ahead);
+        // further super-blocks of very long rows, 32 at a time, in order
+        V A2 = Aw[2], B2 = Bw[2];
+        for (int w0 = 32; w0 < n2 && ok; w0 += 32) {
+            V Ax, Bx;
+            const int nn = n2 - w0 < 32 ? n2 - w0 : 32;
+            ok = compose_window<V, false>(row_rec + (static_cast<uint64_t>(S) + S1 + w0) * LB_RECORD_BYTES, LB_RECORD_BYTES, nn,
+                                          tag, lane, Ax, Bx);
+            B2 = vfma(Ax, B2, Bx);
+            A2 = vmul(Ax, A2);
+        }
+        preA = A2;
+        preB = B2;
+        preB = vfma(Aw[1], preB, Bw[1]);
+        preA = vmul(Aw[1], preA);
+        preB = vfma(Aw[0], preB, Bw[0]);
+        preA = vmul(Aw[0], preA);
+        return ok;
+    };
+
     // ---------------- aggregate pass of the item in `slot`: lane prefixes, the segment's
     // aggregate, publication
     auto aggregate = [&](PendingItem<V> &it, int slot, Raw gate_raw) {
@@ -573,6 +607,28 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
             }
             if (!ok) it.waits_ok = false;
         }
+        // The slice of the row ends with this segment: the slice's aggregate goes to the ranks that
+        // come later in processing order, as early as possible (they all wait for it).
+        if (sharded && s == S - 1 && n_after > 0 && it.waits_ok) {
+            V preA, preB;
+            bool ok = local_prefix(row_rec, s, preA, preB, nullptr);
+            const V Ps = vmul(segA, preA), Ss = vfma(segA, preB, segB);
+            if (ok && lane < n_after) {
+                const int target = REV ? sp.rank - 1 - lane : sp.rank + 1 + lane;
+                // the slot was last used two calls ago: the receiver must have finished that call
+                ok = sp.call <= 2;
+                for (uint32_t poll = 0; poll < LB_WAIT_POLLS && !ok; ++poll) {
+                    ok = static_cast<int32_t>(static_cast<uint32_t>(ld_relaxed_sys_u64(xl + 8 * target)) - (sp.call - 2)) >= 0;
+                    if (!ok) __nanosleep(200);
+                }
+                if (ok) {
+                    unsigned char *slot_rec = sp.xchg[target] + xchg_carry_offset(p.rows) +
+                                              ((static_cast<uint64_t>(parity_slot) * sp.world + sp.rank) * p.rows + it.d.row0) * LB_RECORD_BYTES;
+                    put_pair<true>(slot_rec, Ps, Ss, sp.call);
+                }
+            }
+            if (!__all_sync(0xffffffffu, ok)) it.waits_ok = false;
+        }
     };
 
     PendingItem<V> cur, nxt;
@@ -623,55 +679,13 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
         LB_MARK(1)
 
         // ---------------- look back for this item
-        const V segA = cur.segA, segB = cur.segB;
         // A wait that expires ends this warp's work: the status bit is set and the warp leaves
         // (none of its copies is in flight at this point: both resident segments have been
         // aggregated).  Every warp gives up at its first expired wait, so a launch whose partner
         // never shows up ends after about one bound, not one bound per item.
         bool lb_ok = cur.waits_ok && nxt.waits_ok;
         V preA = vone(V()), preB = vzero(V());         // map from the slice's start to the segment's start
-        if (s > 0 && lb_ok) {
-            // Segments, blocks and super-blocks at once.
-            V Aw[3], Bw[3];
-            lb_ok = compose_three<V>(lb_base, lb_n, tag, lane, Aw, Bw, sizeof(V) == 4 ? &ahead : nullptr);
-            // further super-blocks of very long rows, 32 at a time, in order
-            V A2 = Aw[2], B2 = Bw[2];
-            for (int w0 = 32; w0 < n2 && lb_ok; w0 += 32) {
-                V Ax, Bx;
-                const int nn = n2 - w0 < 32 ? n2 - w0 : 32;
-                lb_ok = compose_window<V, false>(row_rec + (static_cast<uint64_t>(S) + S1 + w0) * LB_RECORD_BYTES,
-                                                 LB_RECORD_BYTES, nn, tag, lane, Ax, Bx);
-                B2 = vfma(Ax, B2, Bx);
-                A2 = vmul(Ax, A2);
-            }
-            // the map from the slice's start: super-blocks, then blocks, then segments
-            preA = A2;
-            preB = B2;
-            preB = vfma(Aw[1], preB, Bw[1]);
-            preA = vmul(Aw[1], preA);
-            preB = vfma(Aw[0], preB, Bw[0]);
-            preA = vmul(Aw[0], preA);
-        }
-        // the slice ends with this segment: its aggregate goes to the ranks that come later
-        if (sharded && s == S - 1 && n_after > 0 && lb_ok) {
-            const V Ps = vmul(segA, preA), Ss = vfma(segA, preB, segB);
-            if (lane < n_after) {
-                const int target = REV ? sp.rank - 1 - lane : sp.rank + 1 + lane;
-                bool ok = sp.call <= 2;
-                for (uint32_t poll = 0; poll < LB_WAIT_POLLS && !ok; ++poll) {
-                    ok = static_cast<int32_t>(static_cast<uint32_t>(ld_relaxed_sys_u64(xl + 8 * target)) - (sp.call - 2)) >= 0;
-                    if (!ok) __nanosleep(200);
-                }
-                if (ok) {
-                    unsigned char *slot = sp.xchg[target] + xchg_carry_offset(p.rows) +
-                                          ((static_cast<uint64_t>(parity_slot) * sp.world + sp.rank) * p.rows + row) * LB_RECORD_BYTES;
-                    put_pair<true>(slot, Ps, Ss, sp.call);
-                } else {
-                    lb_ok = false;
-                }
-            }
-            lb_ok = __all_sync(0xffffffffu, lb_ok);
-        }
+        if (lb_ok) lb_ok = local_prefix(row_rec, s, preA, preB, sizeof(V) == 4 ? &ahead : nullptr);
         // state entering the slice: the caller's, or the fold of the earlier ranks' aggregates
         V x_slice = cin ? cin[row] : vzero(V());
         if (n_before > 0 && lb_ok) {

@@ -96,7 +96,7 @@ def parse_args():
     ap.add_argument("--no-also", action="store_true")
     ap.add_argument("--e2e-slabs", type=int, default=16)
     ap.add_argument("--e2e-streams", type=int, default=4)
-    ap.add_argument("--time-sharded-steps", type=int, default=5)
+    ap.add_argument("--time-sharded-steps", type=int, default=20)
     # other shapes for profiling runs (the contract's workload is the default (8, 1536, L));
     # use with --no-sweep --no-also, which are written for the default shape
     ap.add_argument("--batch", type=int, default=8)
@@ -721,43 +721,45 @@ def run_time_sharded(args, torch, dist, dev, world, rank):
 
     from accelerated_scan import _native
 
-    for _ in range(3):
-        step()
-    barrier()
+    def timed(fn, K):
+        """Device time of K back-to-back steps in the steady state.  The single-pass path has no
+        collective: ranks leave a host barrier up to a millisecond apart, and the first step after
+        it waits for the slowest one.  Two untimed steps after the barrier align the ranks through
+        the data they exchange; the events then bracket K steps on every rank (max over ranks)."""
+        for _ in range(3):
+            fn()
+        barrier()
+        for _ in range(2):
+            fn()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(K):
+            out = fn()
+        b.record()
+        barrier()
+        ms = a.elapsed_time(b) / K
+        if world > 1:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, out
+
     K = args.time_sharded_steps
     n0 = _native.launch_count
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(K):
-        states, dg, dx = step()
-    b.record()
-    barrier()
-    launches_per_step = (_native.launch_count - n0) // K
-    ms = a.elapsed_time(b) / K
-    if world > 1:
-        t = torch.tensor([ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+    ms, (states, dg, dx) = timed(step, K)
+    n1 = _native.launch_count
+    launches_per_step = (n1 - n0) // (K + 5)
     n = Bt * Ct * Tt
     gbs = 8 * 4 * n / (ms * 1e-3) / 1e9
     # the three-step scheme (carry-only reduction, all_gather, seeded scan) beside it: the
     # fallback path, and a second implementation the single-pass results are compared with
     three = None
     if world > 1 and single_pass:
-        for _ in range(2):
-            ref_states, ref_dg, ref_dx = step_three()
-        barrier()
-        a.record()
-        for _ in range(K):
-            ref_states, ref_dg, ref_dx = step_three()
-        b.record()
-        barrier()
-        t = torch.tensor([a.elapsed_time(b) / K], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms3, (ref_states, ref_dg, ref_dx) = timed(step_three, K)
         rel = lambda p, q: float((p - q).abs().max() / q.abs().max().clamp_min(1e-30))
         agree = torch.tensor([rel(states, ref_states), rel(dg, ref_dg), rel(dx, ref_dx)], device=dev, dtype=torch.float64)
         dist.all_reduce(agree, op=dist.ReduceOp.MAX)
-        three = {"ms_per_step": round(float(t.item()), 4), "value": round(8 * 4 * n / (float(t.item()) * 1e-3) / 1e9, 1),
+        three = {"ms_per_step": round(ms3, 4), "value": round(8 * 4 * n / (ms3 * 1e-3) / 1e9, 1),
                  "max_rel_diff_vs_single_pass": [float(f"{v:.3e}") for v in agree.tolist()]}
         del ref_states, ref_dg, ref_dx
 
@@ -788,6 +790,8 @@ def run_time_sharded(args, torch, dist, dev, world, rank):
             "path": "plain kernels" if world == 1 else ("single pass" if single_pass else "three steps"),
             "exchange": "none" if world == 1 else sharded.describe_exchange(single_pass),
             "three_step_path": three,
+            "timing": "steady state: after a barrier, 2 untimed steps align the ranks, then CUDA events around `steps` "
+                      "back-to-back steps, max over ranks",
             "launches_per_step": launches_per_step,
             "pct_of_measured_peak_per_gpu": round(100 * gbs / world / measured_peak()[0], 2), "parity": parity}
 
