@@ -33,7 +33,7 @@ class Plan(ctypes.Structure):
         ("kernel", ctypes.c_int32), ("loader", ctypes.c_int32), ("chunks_per_lane", ctypes.c_int32),
         ("stages", ctypes.c_int32), ("warps_per_cta", ctypes.c_int32), ("grid", ctypes.c_int32),
         ("tile_elems", ctypes.c_int32), ("dynamic", ctypes.c_int32),
-        ("team_size", ctypes.c_int32), ("reserved", ctypes.c_int32),
+        ("team_size", ctypes.c_int32), ("row_grid", ctypes.c_int32),
         ("rows_per_item", ctypes.c_int64), ("row_groups", ctypes.c_int64), ("seg_elems", ctypes.c_int64),
         ("fine_elems", ctypes.c_int64), ("coarse_segs", ctypes.c_int64), ("fine_segs", ctypes.c_int64),
         ("segs_per_row", ctypes.c_int64), ("items", ctypes.c_int64),
@@ -118,7 +118,8 @@ EXPORTS = (
     "ascan_backward_time_sharded", "ascan_peer_alloc", "ascan_peer_open", "ascan_peer_close", "ascan_peer_free",
 )
 
-OPT_STAGES, OPT_WARPS_PER_CTA, OPT_LOOKBACK_TILES, OPT_DISABLE_PLANS, OPT_TEST_DROP_CARRY, OPT_TEST_EPOCH_BITS = range(6)
+(OPT_STAGES, OPT_WARPS_PER_CTA, OPT_LOOKBACK_TILES, OPT_DISABLE_PLANS, OPT_TEST_DROP_CARRY, OPT_TEST_EPOCH_BITS,
+ OPT_ITEMS_PER_WARP) = range(7)
 
 
 def strerror(code: int) -> str:
@@ -254,10 +255,11 @@ def _finish(rc, what, ws, stream):
 
 
 def plan(rows: int, seqlen: int, dtype: int, kind: int, aligned: bool = True, workspace: bool = True,
-         sm_count: int = 148, reverse: bool = False, lookback: bool = True, team: bool = True) -> dict:
+         sm_count: int = 148, reverse: bool = False, lookback: bool = True, team: bool = True,
+         seeded: bool = False) -> dict:
     pl = Plan()
     flags = (int(bool(aligned)) | (int(bool(workspace)) << 1) | (int(bool(reverse)) << 2) | (int(not lookback) << 3)
-             | (int(not team) << 4))
+             | (int(not team) << 4) | (int(bool(seeded)) << 5))
     check(lib.ascan_plan_describe(rows, seqlen, dtype, kind, flags, sm_count, ctypes.byref(pl)),
           "ascan_plan_describe")
     return pl.as_dict()

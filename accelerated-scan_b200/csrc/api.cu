@@ -37,7 +37,7 @@ static int cached_sm_count(int *out) {
 
 // ---- options (ascan_set_option): process-wide, read on every call, never from the environment
 static std::atomic<int> g_opt_stages{2}, g_opt_wpc{0}, g_opt_lookback_tiles{0}, g_opt_disable_plans{0};
-static std::atomic<int> g_opt_drop_carry{0}, g_opt_epoch_bits{17};
+static std::atomic<int> g_opt_drop_carry{0}, g_opt_epoch_bits{17}, g_opt_items_per_warp{4};
 static std::atomic<uint32_t> g_opt_generation{0};
 
 static PlanTuning current_tuning() {
@@ -46,6 +46,7 @@ static PlanTuning current_tuning() {
     t.warps_per_cta = g_opt_wpc.load(std::memory_order_relaxed);
     t.lookback_tiles = g_opt_lookback_tiles.load(std::memory_order_relaxed);
     t.disable_plans = g_opt_disable_plans.load(std::memory_order_relaxed);
+    t.items_per_warp = g_opt_items_per_warp.load(std::memory_order_relaxed);
     return t;
 }
 
@@ -76,7 +77,8 @@ static int make_plan_cached(const PlanInput &in, ascan_plan *pl) {
     k.kind = in.kind;
     k.sm_count = in.sm_count;
     k.flags = (in.reverse ? 1u : 0u) | (in.aligned ? 2u : 0u) | (in.workspace ? 4u : 0u) | (in.allow_lookback ? 8u : 0u) |
-              (in.allow_team ? 16u : 0u) | (in.three_chunks ? 32u : 0u) | (in.force_lookback ? 64u : 0u);
+              (in.allow_team ? 16u : 0u) | (in.three_chunks ? 32u : 0u) | (in.force_lookback ? 64u : 0u) |
+              (in.allow_grid ? 128u : 0u);
     k.generation = g_opt_generation.load(std::memory_order_relaxed);
     for (int i = 0; i < memo.used; ++i) {
         if (memo.key[i] == k) {
@@ -137,9 +139,10 @@ __global__ void fold_carries_kernel(const V *gathered, int64_t rows, int world, 
 static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 static int plan_for(int64_t rows, int64_t seqlen, int dtype, int kind, bool aligned, const void *ws, size_t ws_bytes,
-                    ascan_plan *pl, bool reverse = false) {
+                    ascan_plan *pl, bool reverse = false, bool seeded = false) {
     PlanInput in;
     in.reverse = reverse;
+    in.allow_grid = !seeded;
     in.rows = rows;
     in.seqlen = seqlen;
     in.dtype = dtype;
@@ -163,10 +166,6 @@ static int plan_for(int64_t rows, int64_t seqlen, int dtype, int kind, bool alig
 }
 
 // Copies the plan's decomposition and the workspace pointers into the kernel parameters.
-#ifdef LB_DEBUG_TIMING
-static void *g_debug_buffer = nullptr;
-extern "C" void ascan_debug_buffer(void *p) { g_debug_buffer = p; }
-#endif
 static void fill_common(StreamParams &p, const ascan_plan &pl, int64_t rows, int64_t seqlen, void *ws, size_t ws_bytes) {
     p.rows = rows;
     p.T = seqlen;
@@ -185,9 +184,6 @@ static void fill_common(StreamParams &p, const ascan_plan &pl, int64_t rows, int
     p.test_drop_carry = g_opt_drop_carry.load(std::memory_order_relaxed);
     p.epoch_mask = (1u << g_opt_epoch_bits.load(std::memory_order_relaxed)) - 1u;
     p.scratch_bytes = (pl.dynamic && ws_bytes > static_cast<size_t>(CTRL_BYTES)) ? ws_bytes - CTRL_BYTES : 0;
-#ifdef LB_DEBUG_TIMING
-    if (pl.kernel == 1) p.carry_out = g_debug_buffer;
-#endif
 }
 
 // Plan for the fused variants, which exist only in the chained stream plan with the bulk
@@ -248,7 +244,7 @@ int ascan_forward(const void *gates, const void *tokens, void *out, int64_t rows
     if (!gates || !tokens || !out) return ASCAN_ERR_INVALID_ARG;
     ascan_plan pl;
     const bool al = aligned16(gates) && aligned16(tokens) && aligned16(out);
-    int rc = plan_for(rows, seqlen, dtype, ASCAN_KIND_FORWARD, al, ws, ws_bytes, &pl, reverse != 0);
+    int rc = plan_for(rows, seqlen, dtype, ASCAN_KIND_FORWARD, al, ws, ws_bytes, &pl, reverse != 0, carry_in != nullptr);
     if (rc != ASCAN_OK) return rc;
     StreamParams p = {};
     p.in0 = gates;
@@ -269,7 +265,8 @@ int ascan_backward(const void *gates, const void *states, const void *grad_out, 
     ascan_plan pl;
     const bool al = aligned16(gates) && aligned16(states) && aligned16(grad_out) && aligned16(d_gates) &&
                     aligned16(d_tokens);
-    int rc = plan_for(rows, seqlen, dtype, ASCAN_KIND_BACKWARD, al, ws, ws_bytes, &pl);
+    int rc = plan_for(rows, seqlen, dtype, ASCAN_KIND_BACKWARD, al, ws, ws_bytes, &pl, false,
+                      carry_in || halo_gate_right || halo_state_left);
     if (rc != ASCAN_OK) return rc;
     StreamParams p = {};
     p.in0 = gates;
@@ -351,6 +348,7 @@ int ascan_plan_describe(int64_t rows, int64_t seqlen, int dtype, int kind, int f
     in.sm_count = sm_count;
     in.allow_lookback = (flags & 8) == 0;
     in.allow_team = (flags & 16) == 0;
+    in.allow_grid = (flags & 32) == 0;
     if (sm_count <= 0) {
         int rc = cached_sm_count(&in.sm_count);
         if (rc != ASCAN_OK) return rc;
@@ -374,8 +372,12 @@ int ascan_set_option(int option, int value) {
             g_opt_lookback_tiles.store(value);
             break;
         case ASCAN_OPT_DISABLE_PLANS:
-            if (value < 0 || value > 15) return ASCAN_ERR_INVALID_ARG;
+            if (value < 0 || value > 31) return ASCAN_ERR_INVALID_ARG;
             g_opt_disable_plans.store(value);
+            break;
+        case ASCAN_OPT_ITEMS_PER_WARP:
+            if (value < 1 || value > 64) return ASCAN_ERR_INVALID_ARG;
+            g_opt_items_per_warp.store(value);
             break;
         case ASCAN_OPT_TEST_DROP_CARRY: g_opt_drop_carry.store(value ? 1 : 0); break;
         case ASCAN_OPT_TEST_EPOCH_BITS:
@@ -394,6 +396,7 @@ int ascan_get_option(int option) {
         case ASCAN_OPT_WARPS_PER_CTA: return g_opt_wpc.load();
         case ASCAN_OPT_LOOKBACK_TILES: return g_opt_lookback_tiles.load();
         case ASCAN_OPT_DISABLE_PLANS: return g_opt_disable_plans.load();
+        case ASCAN_OPT_ITEMS_PER_WARP: return g_opt_items_per_warp.load();
         case ASCAN_OPT_TEST_DROP_CARRY: return g_opt_drop_carry.load();
         case ASCAN_OPT_TEST_EPOCH_BITS: return g_opt_epoch_bits.load();
         default: return -1;

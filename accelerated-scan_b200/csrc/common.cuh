@@ -264,6 +264,26 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity
     return false;
 }
 
+// The same with a suspend-time hint: a thread whose phase is not complete sleeps in hardware
+// for up to `hint_ns` per try instead of spinning through issue slots the other warps of the
+// SM could use.  For waits that are expected to last a microsecond or so.
+__device__ __forceinline__ bool mbar_wait_bounded_suspended(uint64_t *bar, uint32_t parity, uint32_t limit, uint32_t hint_ns) {
+    for (uint32_t i = 0; i < limit; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(ok)
+            : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
 // Bulk asynchronous copy global -> shared (no multicast), completion on an mbarrier.
 // Both addresses 16-byte aligned, size a multiple of 16 bytes.
 __device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src_gmem, uint32_t bytes, uint64_t *bar) {

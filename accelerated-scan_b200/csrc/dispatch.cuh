@@ -75,7 +75,14 @@ static int launch_nch(const StreamParams &p, const ascan_plan &pl, cudaStream_t 
     switch (pl.chunks_per_lane) {
         case 3: return launch_loader<TR, 3, KIND, REVERSE>(p, pl, stream);
         case 2:
-            // two chunks per lane: planned for the fused backward of the 16-bit dtypes only
+            // two chunks per lane: rows on the tile grid (short power-of-two rows, scan kinds) ...
+            if constexpr (KIND == K_SCAN || KIND == K_BWD) {
+                if (pl.row_grid) {
+                    if (pl.kernel != 0 || pl.loader != 0) return ASCAN_ERR_UNSUPPORTED;
+                    return launch_kernel(stream_kernel<TR, 2, KIND, REVERSE, true, false, false, 0, true>, p, pl, stream);
+                }
+            }
+            // ... and the fused backward of the 16-bit dtypes
             if constexpr (KIND == K_BWD && TR::EPC == 8) {
                 if (pl.kernel == 0) return launch_loader<TR, 2, KIND, REVERSE>(p, pl, stream);
             }

@@ -511,7 +511,7 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
         V next_gate = it.end_gate;
         for (int i = 0; i < it.d.nt; ++i) {
             const int stage = slot * NT + i;
-            bool ok = mbar_wait_bounded(&bars[stage], (phase_bits >> stage) & 1u, LOAD_WAIT_POLLS);
+            bool ok = mbar_wait_bounded_suspended(&bars[stage], (phase_bits >> stage) & 1u, LOAD_WAIT_POLLS, 2000);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
                 failed = true;
@@ -647,14 +647,6 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
     }
     Raw nxt_gate_raw = end_gate_raw(nxt.d);
 
-#ifdef LB_DEBUG_TIMING
-    unsigned long long dbg[6] = {0, 0, 0, 0, 0, 0};
-    auto now = []() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; };
-    unsigned long long t_mark = now();
-#define LB_MARK(k) { unsigned long long t_ = now(); dbg[k] += t_ - t_mark; t_mark = t_; }
-#else
-#define LB_MARK(k)
-#endif
     while (cur.d.valid && !failed) {
         const int nxt_slot = cur_slot ^ 1;
         const int64_t row = cur.d.row0;
@@ -676,7 +668,6 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
         // ---------------- aggregate pass of the item after this one
         if (nxt.d.valid) aggregate(nxt, nxt_slot, nxt_gate_raw);
         if (failed) break;
-        LB_MARK(1)
 
         // ---------------- look back for this item
         // A wait that expires ends this warp's work: the status bit is set and the warp leaves
@@ -706,7 +697,6 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
             break;
         }
         const V x_in = vfma(preA, x_slice, preB);
-        LB_MARK(2)
 
         // ---------------- scan pass from shared memory; stages are refilled as they drain
         // The number of the item after the next is drawn only now, after the look-back: from this
@@ -837,7 +827,6 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
                 }
             }
             learn_after();
-            LB_MARK(3)
             if constexpr (STAGED) {
                 // stages the loop did not refill: the only one of a one-tile item, and those the
                 // item after the next has beyond this item's tiles
@@ -845,11 +834,9 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
                     if (nt == 1) issue(aft.d, cur_slot, 0);
                     for (int i = nt > 1 ? nt : 1; i < aft.d.nt; ++i) issue(aft.d, cur_slot, i);
                 }
-                LB_MARK(4)
             } else {
                 if (lane == 0) bulk_wait_read<0>();
                 __syncwarp();
-                LB_MARK(4)
                 if (aft.d.valid) {
                     for (int i = nt - 1; i < aft.d.nt; ++i) issue(aft.d, cur_slot, i);
                 }
@@ -859,16 +846,7 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
         nxt = aft;
         nxt_gate_raw = aft_gate_raw;
         cur_slot = nxt_slot;
-#ifdef LB_DEBUG_TIMING
-        dbg[5] += 1;
-#endif
     }
-#ifdef LB_DEBUG_TIMING
-    if (p.carry_out && lane == 0) {
-        unsigned long long *o = static_cast<unsigned long long *>(p.carry_out) + (static_cast<int64_t>(blockIdx.x) * wpc + wib) * 8;
-        for (int k = 0; k < 6; ++k) o[k] = dbg[k];
-    }
-#endif
 
     if (lane == 0) bulk_wait_read<0>();
     __syncwarp();

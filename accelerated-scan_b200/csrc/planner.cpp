@@ -60,9 +60,21 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     // long enough to be split (whole short rows run better one warp each); from 8000 rows on
     // the stream plan is ahead again.
     const int64_t team_rows = 4 * stream_warps;
-    const int nch = (in.kind == ASCAN_KIND_BACKWARD && esize == 2 && in.rows >= team_rows && !in.three_chunks)
+    // Short rows on the tile grid: with two chunks per lane (512 16-bit, 256 fp32, 128 complex64
+    // elements per tile) every power-of-two row length from one lane's elements up to the tile
+    // divides the tile, so items can group whole rows without any per-element row-boundary
+    // arithmetic (GRID kernels; measured at 12288 rows of bf16: 128 steps 14.3 -> 10.2 us forward,
+    // 18.4 -> 12.3 us backward; 256 steps 20.5 -> 14.3 / 30.7 -> 18.4 us).  Rows longer than a tile
+    // keep three chunks per lane: the two-chunk forward kernel pays its per-tile costs on a third
+    // fewer bytes (bf16, 2048 to 16384 steps: 14-19 % slower).  Not where teams apply.
+    const int64_t k2 = 2 * (16 / esize), te2 = 32 * k2, te3 = 32 * 3 * (16 / esize);
+    const bool scan_kind_early = in.kind == ASCAN_KIND_FORWARD || in.kind == ASCAN_KIND_BACKWARD;
+    const bool row_grid = in.allow_grid && scan_kind_early && in.aligned && !in.three_chunks && in.rows >= team_rows &&
+                      in.seqlen % k2 == 0 && te2 % in.seqlen == 0 && (in.tune.disable_plans & (8 | 16)) == 0;
+    const int nch = (row_grid || (in.kind == ASCAN_KIND_BACKWARD && esize == 2 && in.rows >= team_rows && !in.three_chunks))
                         ? 2
                         : 3;
+    pl.row_grid = row_grid ? 1 : 0;
     const int64_t te = 32 * nch * (16 / esize);
     // tickets and split-row item numbers are 32-bit
     const bool use_ws = in.workspace && (in.tune.disable_plans & 4) == 0 && in.rows < (1ll << 30) &&
@@ -90,6 +102,7 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     // Short rows are grouped into items of about four per warp, at most `seg_tiles` tiles.
     int seg_tiles = 16;
     int fine_tiles = 4;
+    if (row_grid) seg_tiles = 32;
     const int64_t max_warps = static_cast<int64_t>(in.sm_count) * kMaxWarpsPerCta;
     const int64_t tiles_row = (in.seqlen + te - 1) / te;
     const bool reverse_order = in.kind == ASCAN_KIND_BACKWARD || in.kind == ASCAN_KIND_REDUCE_BACKWARD || in.reverse;
@@ -201,7 +214,7 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     }
     const int64_t workers = static_cast<int64_t>(in.sm_count) * team_wpc / team;
     const int64_t split_min = team > 1 ? 2 * fine_tiles : 32;
-    if (can_split && tiles_row >= split_min && tiles_row >= 2 * fine_tiles) {
+    if (can_split && !row_grid && tiles_row >= split_min && tiles_row >= 2 * fine_tiles) {
         int64_t fine_region = (static_cast<int64_t>(seg_tiles) * workers + in.rows - 1) / (in.rows > 0 ? in.rows : 1);
         fine_region = (fine_region + fine_tiles - 1) / fine_tiles * fine_tiles;      // tiles, multiple of a fine item
         if (fine_region > tiles_row) fine_region = tiles_row;
@@ -236,12 +249,21 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
         pl.segs_per_row = pl.coarse_segs + pl.fine_segs;
     } else {
         const int64_t total_tiles = (in.rows * in.seqlen + te - 1) / te;
-        int64_t fit = total_tiles / (4 * max_warps);
+        // about four items per warp; a row-grid problem of at most 16 tiles per warp is dealt as one
+        // item per warp (a launch of some 10 us gains nothing from balancing, and saves the tickets)
+        int ipw = in.tune.items_per_warp > 0 ? in.tune.items_per_warp : 4;
+        if (row_grid && total_tiles <= 16 * max_warps) ipw = 1;
+        int64_t fit = total_tiles / (ipw * max_warps);
         if (fit < 1) fit = 1;
         if (fit < seg_tiles) seg_tiles = static_cast<int>(fit);
         int64_t rpi = (seg_tiles * te) / in.seqlen;
         if (rpi < 1) rpi = 1;
         if (bulk) rpi = (rpi + align_rows - 1) / align_rows * align_rows;
+        if (row_grid && te > in.seqlen) {
+            // whole tiles per item: a multiple of the rows of one tile
+            const int64_t per_tile = te / in.seqlen;
+            rpi = (rpi + per_tile - 1) / per_tile * per_tile;
+        }
         pl.rows_per_item = rpi;
         pl.row_groups = (in.rows + rpi - 1) / rpi;
         pl.seg_elems = in.seqlen;
@@ -270,7 +292,7 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     else if (wpc > 14) wpc = 14;
     if (wpc < 1) return ASCAN_ERR_UNSUPPORTED;
     // kernels for items that group rows keep more state per thread: compiled for 12 warps
-    if (pl.rows_per_item > 1 && wpc > kMaxWarpsPerCta) wpc = kMaxWarpsPerCta;
+    if (pl.rows_per_item > 1 && !row_grid && wpc > kMaxWarpsPerCta) wpc = kMaxWarpsPerCta;
 
     // One persistent CTA per SM.  With fewer items than warps, spread the items over
     // all SMs before filling the warps of a CTA.
@@ -302,7 +324,8 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     pl.grid = static_cast<int32_t>(grid);
     pl.smem_bytes = static_cast<uint64_t>(wpc) * wsm + (team > 1 ? static_cast<uint64_t>(wpc / team) * kTeamSmemBytes : 0);
     pl.kernel = team > 1 ? 2 : 0;
-    pl.workspace_bytes = (!use_ws || !pl.dynamic) ? 0 : workspace_bytes(in.rows);
+    // carry records are only needed when rows are split; the control block (ticket, status) always
+    pl.workspace_bytes = (!use_ws || !pl.dynamic) ? 0 : (pl.segs_per_row > 1 ? workspace_bytes(in.rows) : kCtrlBytes);
     *plan = pl;
     return ASCAN_OK;
 }

@@ -22,7 +22,8 @@ struct PlanTuning {
     int stages = 2;            // shared-memory stages per warp of the stream and team kernels
     int warps_per_cta = 0;     // 0 = planner's choice; otherwise an upper bound
     int lookback_tiles = 0;    // tiles per segment of the look-back plan; 0 = the default (2)
-    int disable_plans = 0;     // bit 0: no look-back, bit 1: no team, bit 2: static deal (no tickets), bit 3: plain loader
+    int items_per_warp = 4;    // items per warp that grouped short rows aim for (at most two: dealt statically)
+    int disable_plans = 0;     // bit 0: no look-back, bit 1: no team, bit 2: static deal (no tickets), bit 3: plain loader, bit 4: no row grid
 };
 
 struct PlanInput {
@@ -37,6 +38,7 @@ struct PlanInput {
     bool allow_team = true;       // false: never choose the team plan
     bool three_chunks = false;    // true: always 3 chunks per lane (variants without a 2-chunk kernel)
     bool force_lookback = false;  // true: the look-back plan whatever the row count (time-sharded calls)
+    bool allow_grid = true;       // false: the call has seeds (carry_in, halos), which the row-grid kernels do not take
     int sm_count;
     PlanTuning tune;
 };

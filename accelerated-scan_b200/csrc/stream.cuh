@@ -180,7 +180,16 @@ struct ItemDesc {
 // gate pre-activations z and the gate is sigmoid(z), computed in fp32 as the tile is read.
 // The fused backward returns d_z[t] = x[t-1] * g[t] * s(1 - s) in place of d_gates, which
 // removes the caller's sigmoid pass and its backward pass over the (B, C, T) tensors.
-template <class TR, int NCH, int KIND, bool REVERSE, bool BULK, bool INTERIOR, bool TOKR = false, int ACT = 0>
+//
+// GRID (K_SCAN and K_BWD without seeds, INTERIOR = false): items group whole rows, and the rows
+// fall on the grid of tiles and lanes -- the row length is a multiple of the elements of a lane
+// and either divides the tile or is a multiple of it -- so a row can only start at the first
+// element of a lane and which lanes those are is known once per kernel.  The gate that would
+// carry a state into a row (its first element, forward; the step after its last element,
+// backward) is set to zero there; everything else is the one-row-per-item code, packed
+// arithmetic included.  This is the plan of the short power-of-two rows.
+template <class TR, int NCH, int KIND, bool REVERSE, bool BULK, bool INTERIOR, bool TOKR = false, int ACT = 0,
+          bool GRID = false>
 __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ? 448 : 512), 1) stream_kernel(const StreamParams p) {
     using V = typename TR::V;
     using Raw = typename TR::Raw;
@@ -212,6 +221,10 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
     const int64_t w = static_cast<int64_t>(blockIdx.x) * wpc + wib;
     const int64_t W = static_cast<int64_t>(gridDim.x) * wpc;
     const int64_t T = p.T;
+    static_assert(!GRID || (!INTERIOR && (KIND == K_SCAN || KIND == K_BWD)), "GRID: scan kinds, rows on the tile grid");
+    // GRID: lanes per row when several rows share a tile (else a row takes whole tiles)
+    const int grid_lpr = (GRID && T < TE) ? static_cast<int>(T / K) : 32;
+    const bool grid_lane_first = GRID && (lane % grid_lpr == 0), grid_lane_last = GRID && (lane % grid_lpr == grid_lpr - 1);
     const bool dynamic = (p.ctrl != nullptr);
     const bool split = p.segs_per_row > 1;
     const unsigned char *gbase[3] = {static_cast<const unsigned char *>(p.in0), static_cast<const unsigned char *>(p.in1),
@@ -555,6 +568,9 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
             }
 
             const int jv = nvalid - lane * K;   // elements j >= jv lie beyond the item
+            // GRID: does a row start at this lane's first element / end at its last one in this tile
+            const bool row_first = grid_lane_first && (T <= TE || ts_mod == 0);
+            const bool row_last = grid_lane_last && (T <= TE || ts_mod + TE == T);
             V b2[(REDUCE && INTERIOR) ? K : 1];
             uint32_t start_mask_lo = 0, start_mask_hi = 0;   // INTERIOR backward: elements that open a row
             bool has_boundary = false;
@@ -592,6 +608,14 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
                             // the last step of the row takes the gate of the step after the row
                             a[j] = gate_end;
                         }
+                    }
+                }
+                if constexpr (GRID) {
+                    // nothing is carried into a row: zero the gate of its first processed element
+                    if (!REV) {
+                        if (row_first) a[0] = vzero(V());
+                    } else {
+                        if (row_last) a[K - 1] = vzero(V());
                     }
                 }
             } else {
@@ -757,6 +781,7 @@ __global__ void __launch_bounds__(INTERIOR ? 384 : ((KIND == K_BWD && NCH > 2) ?
                     // element below (neighbouring lane by shuffle, tile halo for lane 0)
                     V dn = shfl_up(xp[K - 1], 1);
                     if (lane == 0) dn = halo_in_row ? (BULK ? x_below : TR::decode(x_halo_raw)) : x_halo_row;
+                    if (GRID && row_first) dn = vzero(V());       // a row starts here: the state before it is zero
                     if constexpr (ACT == 1) {
                         // after the shift a[j-1] is the gate s of element j: chain rule through
                         // the sigmoid, d_z = d_gate * s * (1 - s); downwards, so that each gate

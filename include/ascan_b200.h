@@ -73,7 +73,7 @@ typedef struct {
     int32_t tile_elems;        /* elements per warp tile                                   */
     int32_t dynamic;           /* 1 = items drawn from a ticket counter in the workspace   */
     int32_t team_size;         /* warps that share an item (1 unless kernel == 2)          */
-    int32_t reserved;
+    int32_t row_grid;          /* 1 = short rows on the grid of tiles and lanes: items group whole rows, no per-element row-boundary work */
     int64_t rows_per_item;     /* rows grouped into one item when rows are not split       */
     int64_t row_groups;        /* ceil(rows / rows_per_item)                               */
     int64_t seg_elems;         /* steps per coarse segment when rows are split             */
@@ -270,7 +270,7 @@ size_t ascan_workspace_bytes(int64_t rows, int64_t seqlen, int dtype, int kind);
  * The plan the library would use.  flags: bit 0 = every pointer is 16-byte
  * aligned, bit 1 = a workspace of ascan_workspace_bytes() is supplied, bit 2 =
  * forward kind with reverse != 0, bit 3 = never choose the look-back plan, bit 4 = never
- * choose the team plan;
+ * choose the team plan, bit 5 = the call has seeds (carry_in or halos: no row-grid kernels);
  * sm_count <= 0 queries the current device.  Host only.
  */
 int ascan_plan_describe(int64_t rows, int64_t seqlen, int dtype, int kind,
@@ -305,9 +305,10 @@ typedef enum {
     ASCAN_OPT_STAGES = 0,          /* shared-memory stages per warp, 1..8 (default 2)          */
     ASCAN_OPT_WARPS_PER_CTA = 1,   /* upper bound on warps per CTA, 0 = planner's choice       */
     ASCAN_OPT_LOOKBACK_TILES = 2,  /* tiles per segment of the look-back plan                  */
-    ASCAN_OPT_DISABLE_PLANS = 3,   /* bit 0 no look-back, bit 1 no team, bit 2 static deal, bit 3 plain loader */
+    ASCAN_OPT_DISABLE_PLANS = 3,   /* bit 0 no look-back, bit 1 no team, bit 2 static deal, bit 3 plain loader, bit 4 no row grid */
     ASCAN_OPT_TEST_DROP_CARRY = 4, /* 1: drop one carry hand-over per launch (a wait expires)  */
-    ASCAN_OPT_TEST_EPOCH_BITS = 5  /* width of the launch epoch, 1..17 (default 17)            */
+    ASCAN_OPT_TEST_EPOCH_BITS = 5, /* width of the launch epoch, 1..17 (default 17)            */
+    ASCAN_OPT_ITEMS_PER_WARP = 6   /* items per warp that grouped short rows aim for (default 4) */
 } ascan_option;
 int ascan_set_option(int option, int value);
 int ascan_get_option(int option);          /* -1 for an unknown option */
