@@ -97,6 +97,8 @@ def parse_args():
     ap.add_argument("--e2e-slabs", type=int, default=16)
     ap.add_argument("--e2e-streams", type=int, default=4)
     ap.add_argument("--time-sharded-steps", type=int, default=20)
+    ap.add_argument("--slice-of", type=int, default=8,
+                    help="also time, on one GPU, the kernels one rank of an N-GPU time-sharded scan runs (0 = skip)")
     # other shapes for profiling runs (the contract's workload is the default (8, 1536, L));
     # use with --no-sweep --no-also, which are written for the default shape
     ap.add_argument("--batch", type=int, default=8)
@@ -459,6 +461,11 @@ def run_b200(args):
         torch.cuda.empty_cache()
         time_sharded = run_time_sharded(args, torch, dist, dev, world, rank)
 
+    # ---- the kernels of one rank of the time-sharded scan, alone on this GPU
+    slice_kernels = None
+    if args.slice_of > 1 and not args.no_time_sharded and args.seqlen == 65536 and rank == 0:
+        slice_kernels = run_slice_kernels(args, torch, _native, dev, args.slice_of)
+
     # ---- end to end through the drop-in autograd API with pinned host buffers
     e2e = None
     if not args.no_e2e:
@@ -471,6 +478,8 @@ def run_b200(args):
         parity["also"] = {"ok": all(r["parity"]["ok"] for r in also if "parity" in r)}
     if time_sharded:
         parity["time_sharded"] = time_sharded.pop("parity")
+    if slice_kernels:
+        parity["slice_kernels"] = slice_kernels.pop("parity")
     parity["ok"] = all(v["ok"] for v in parity.values() if isinstance(v, dict))
 
     if world > 1:
@@ -505,6 +514,7 @@ def run_b200(args):
         },
         "pct_of_nominal_8TBs": round(100 * value / world / 8000.0, 2),
         "time_sharded": time_sharded,
+        "time_sharded_slice_kernels": slice_kernels,
         "sweep": sweep,
         "also": also,
     }
@@ -677,6 +687,51 @@ def run_sweep(args, torch, _native, dev, dtype, esize, gates, tokens, grad_out, 
     return {"shape": f"({B},{C},L) {args.dtype}",
             "l2": "256 MB flush buffer rewritten, then another 256 MB read (drains the flush's dirty lines), before every timed launch",
             "timing": "median of 7 single launches, CUDA events", "points": points}
+
+
+def run_slice_kernels(args, torch, _native, dev, n_ranks):
+    """The two kernels one rank of an `n_ranks`-GPU time-sharded scan of (2, 512, 1048576) fp32 runs,
+    alone on one GPU: the single-pass look-back kernels on a (2, 512, 1048576 / n_ranks) slice,
+    without partners (the exchange is what `time_sharded` adds at N GPUs).  Their rate bounds the
+    scaling of the time-sharded scan: N ranks take at least this long per step."""
+    Bt, Ct, Tl = 2, 512, 1048576 // n_ranks
+    gen = torch.Generator(device=dev).manual_seed(78)
+    g = 0.999 + 0.001 * torch.rand(Bt, Ct, Tl, device=dev, generator=gen)
+    x = torch.rand(Bt, Ct, Tl, device=dev, generator=gen)
+    go = torch.randn(Bt, Ct, Tl, device=dev, generator=gen)
+    o, dg, dx = torch.empty_like(x), torch.empty_like(x), torch.empty_like(x)
+    call = [0]
+
+    def fwd():
+        call[0] += 1
+        _native.forward_time_sharded(g, x, o, 0, 1, call[0], [], None)
+
+    def bwd():
+        _native.backward_time_sharded(g, o, go, dg, dx, 0, 1, call[0], [], None)
+
+    for _ in range(3):
+        fwd()
+        bwd()
+    torch.cuda.synchronize()
+    K = 10
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+    for k in range(K):
+        ev[k][0].record()
+        fwd()
+        ev[k][1].record()
+        bwd()
+        ev[k][2].record()
+    torch.cuda.synchronize()
+    tf = sum(e[0].elapsed_time(e[1]) for e in ev) / K
+    tb = sum(e[1].elapsed_time(e[2]) for e in ev) / K
+    n = Bt * Ct * Tl
+    peak, _ = measured_peak()
+    both = 8 * 4 * n / ((tf + tb) * 1e-3) / 1e9
+    return {"workload": f"look-back kernels on one rank's slice (2,512,{Tl}) fp32 of a {n_ranks}-GPU time-sharded scan, no partners",
+            "fwd_ms": round(tf, 5), "bwd_ms": round(tb, 5), "fwd_GBps": round(12 * n / tf / 1e6, 1),
+            "bwd_GBps": round(20 * n / tb / 1e6, 1), "value": round(both, 1), "unit": UNIT,
+            "frac_of_measured_peak": round(both / peak, 4),
+            "parity": parity_check(torch, "fp32", g, x, go, o, dg, dx, subset_rows(Bt, Ct, per_side=4))}
 
 
 def run_time_sharded(args, torch, dist, dev, world, rank):
