@@ -84,7 +84,7 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference-gpu"])
     ap.add_argument("--seqlen", type=int, default=65536)
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"])
     ap.add_argument("--e2e-steps", type=int, default=2)
@@ -912,9 +912,76 @@ def run_e2e(args, torch, dist, warp, dev, world, dtype, esize):
              "api": f"accelerated_scan.warp.scan + autograd backward, {slabs} row slabs pipelined on {len(streams)} streams"}, launches)
 
 
+def run_reference_gpu(args):
+    """The reference's own CUDA kernel (accelerated_scan/warp.py + warp.cuh, unmodified, staged in
+    baseline/_ref/ and JIT-built here by torch's extension machinery) on this GPU: fp32 only -- its
+    16-bit path strides its aligned tuples wrongly and reads out of bounds (warp.cuh:27-29,236-248),
+    so it is never run -- at (8, 1536, 65536), the longest sequence its ladder takes (warp.cuh:379),
+    driven as the reference's benchmark drives it (tests/bench.py:72-82) but with the outputs
+    allocated once.  Prints one JSON line; a failed build is reported, not raised."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    line = {"impl": "reference-gpu", "metric": METRIC, "unit": UNIT, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"({B},{C},{args.seqlen}) fp32 forward + fused backward by the reference's warp kernel"}}
+    path = os.path.join(ROOT, "baseline", "_ref", "warp.py")
+    if not os.path.exists(path):
+        line["unavailable"] = "baseline/_ref/warp.py is absent (staged by __graft_entry__.build() where the reference is mounted)"
+        print(json.dumps(line), flush=True)
+        return
+    import importlib.util
+
+    import torch
+
+    try:
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)                       # the JIT build is verbose on stdout
+        try:
+            spec = importlib.util.spec_from_file_location("reference_warp", path)
+            mod = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(mod)
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved, 1)
+            os.close(saved)
+    except Exception as exc:                # noqa: BLE001 - the error text is the result
+        line["unavailable"] = f"JIT build of the reference kernel failed: {type(exc).__name__}: {str(exc)[-400:]}"
+        print(json.dumps(line), flush=True)
+        return
+    dev = torch.device("cuda", 0)
+    T = args.seqlen
+    gen = torch.Generator(device=dev).manual_seed(1234)
+    gates = 0.999 + 0.001 * torch.rand(B, C, T, device=dev, generator=gen)
+    tokens = torch.rand(B, C, T, device=dev, generator=gen)
+    grad_out = torch.randn(B, C, T, device=dev, generator=gen)
+    out, dg, dx = torch.empty_like(tokens), torch.empty_like(tokens), torch.empty_like(tokens)
+    for _ in range(max(3, args.warmup)):
+        mod.warpscan_forward(gates, tokens, out, False)
+        mod.warpscan_backward(gates, out, grad_out, dg, dx)
+    torch.cuda.synchronize()
+    K = args.steps
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+    for k in range(K):
+        ev[k][0].record()
+        mod.warpscan_forward(gates, tokens, out, False)
+        ev[k][1].record()
+        mod.warpscan_backward(gates, out, grad_out, dg, dx)
+        ev[k][2].record()
+    torch.cuda.synchronize()
+    tf = sum(e[0].elapsed_time(e[1]) for e in ev) / K
+    tb = sum(e[1].elapsed_time(e[2]) for e in ev) / K
+    n = B * C * T
+    line.update({"value": round(32 * n / ((tf + tb) * 1e-3) / 1e9, 1), "fwd_ms": round(tf, 4), "bwd_ms": round(tb, 4),
+                 "fwd_GBps": round(12 * n / tf / 1e6, 1), "bwd_GBps": round(20 * n / tb / 1e6, 1), "steps": K,
+                 "parity": parity_check(torch, "fp32", gates, tokens, grad_out, out, dg, dx, subset_rows(B, C))})
+    print(json.dumps(line), flush=True)
+
+
 def main():
     args = parse_args()
-    if args.impl == "reference":
+    if args.impl == "reference-gpu":
+        run_reference_gpu(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_b200(args)

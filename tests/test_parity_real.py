@@ -175,13 +175,36 @@ def test_unaligned_views_use_plain_loader(cuda_device):
     assert rel_err(to_np(dg), want_dg) <= FP32_REL
 
 
-def test_deterministic(cuda_device):
-    warp = _warp()
-    gates, tokens, _ = real_inputs(5, (2, 64, 8192), grad=False)
-    g, x = gates.to(cuda_device), tokens.to(cuda_device)
-    a = warp.scan_forward(g, x)
-    b = warp.scan_forward(g, x)
-    assert torch.equal(a, b)
+# one shape per launch plan: (rows, seqlen, plan kernel, row_grid)
+DETERMINISM_CASES = [
+    (7200, 13000, 0, 0),     # chained stream plan, rows split into segments
+    (1024, 16384, 2, 0),     # team plan
+    (16, 1 << 18, 1, 0),     # look-back plan: segments of a row scanned concurrently by many CTAs
+    (12288, 256, 0, 1),      # short rows on the tile grid
+]
+
+
+@pytest.mark.parametrize("rows,seqlen,kernel,row_grid", DETERMINISM_CASES)
+def test_deterministic(cuda_device, rows, seqlen, kernel, row_grid):
+    """Every plan is bitwise reproducible from run to run, forward and backward: the order in
+    which partial results are combined is fixed by the plan (the look-back plan reads the
+    aggregates of fixed sets of segments, never "whatever is there"), not by timing.  The
+    reference's kernels are deterministic too (one block per row, warp.cuh:49-223)."""
+    from accelerated_scan import _native
+
+    pl = _native.plan(rows, seqlen, _native.F32, _native.KIND_FORWARD)
+    assert pl["kernel"] == kernel and pl["row_grid"] == row_grid, pl
+    gates, tokens, grad_out = real_inputs(5, (1, rows, seqlen), law="near_one")
+    g, x, go = gates.to(cuda_device), tokens.to(cuda_device), grad_out.to(cuda_device)
+    runs = []
+    for _ in range(3):
+        out, dg, dx = torch.empty_like(x), torch.empty_like(x), torch.empty_like(x)
+        _native.forward(g, x, out)
+        _native.backward(g, out, go, dg, dx)
+        runs.append((out, dg, dx))
+    for other in runs[1:]:
+        for a, b in zip(runs[0], other):
+            assert torch.equal(a, b)
 
 
 def test_status_word_clean(cuda_device):
