@@ -368,7 +368,7 @@ int ascan_set_option(int option, int value) {
             g_opt_wpc.store(value);
             break;
         case ASCAN_OPT_LOOKBACK_TILES:
-            if (value < 0 || value > 2) return ASCAN_ERR_INVALID_ARG;
+            if (value < 0 || value > 8) return ASCAN_ERR_INVALID_ARG;
             g_opt_lookback_tiles.store(value);
             break;
         case ASCAN_OPT_DISABLE_PLANS:

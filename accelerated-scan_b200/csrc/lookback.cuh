@@ -40,7 +40,7 @@
 namespace ascan {
 
 constexpr int LB_RECORD_BYTES = 32;          // one affine pair of the compute type in tagged 64-bit words
-constexpr int LB_MAX_TILES = 2;              // tiles per segment, at most (a warp holds two segments and works on a segment's tiles side by side)
+constexpr int LB_MAX_TILES = 8;              // tiles per segment, at most (a warp holds two segments: 2 stages per tile)
 constexpr int MAX_WORLD = 16;                // ranks of a time-sharded scan, at most
 constexpr uint32_t LB_WAIT_POLLS = 1u << 20;      // about a second
 
@@ -66,10 +66,14 @@ struct ShardParams {
 __host__ __device__ constexpr int lb_stage_bytes(int nch, int kind) {
     return stream_nin(kind) * 32 * nch * 16 + (kind == K_BWD ? 128 : 0);
 }
-// Two resident segments of `nt` (1 or 2) tiles per warp, the mbarriers, and 16 bytes per stage and
-// lane of prefix maps.  Results are written over the inputs of their stage and leave from there.
+// The forward kinds send their results through a staging tile of their own, so that a stage can
+// be refilled as soon as its tile is in registers; the fused backward writes its two results over
+// the stage's inputs (a staging area would cost it two warps per CTA).
+__host__ __device__ constexpr int lb_staging_bytes(int nch, int kind) { return kind == K_BWD ? 0 : 32 * nch * 16; }
+// Two resident segments of `nt` tiles per warp, the staging tile, the mbarriers, and 16 bytes per
+// stage and lane of prefix maps.
 __host__ __device__ constexpr int lb_warp_smem(int nch, int nt, int kind) {
-    return 2 * nt * lb_stage_bytes(nch, kind) + 128 + 2 * nt * 32 * 16;
+    return 2 * nt * lb_stage_bytes(nch, kind) + lb_staging_bytes(nch, kind) + 128 + 2 * nt * 32 * 16;
 }
 // Workspace of the look-back plan: control block, then the records of the three levels.
 __host__ __device__ constexpr uint64_t lb_level_count(int64_t n) { return static_cast<uint64_t>((n + 31) / 32); }
@@ -253,7 +257,7 @@ struct PendingItem {
 // item's aggregate the warp waits for nothing but memory, so a drawn item is never held back
 // by its owner waiting in a look-back (such waits would chain up across warps).
 template <class TR, int NCH, int KIND, bool REVERSE>
-__global__ void __launch_bounds__(KIND == K_BWD ? 352 : 448, 1) lookback_kernel(const StreamParams p, const ShardParams sp) {
+__global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, const ShardParams sp) {
     using V = typename TR::V;
     using Raw = typename TR::Raw;
     constexpr int EPC = TR::EPC;
@@ -275,10 +279,13 @@ __global__ void __launch_bounds__(KIND == K_BWD ? 352 : 448, 1) lookback_kernel(
     const int wib = threadIdx.x >> 5;
     const int wpc = blockDim.x >> 5;
     unsigned char *wsm = smem_raw + static_cast<size_t>(wib) * WARP_SMEM;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(wsm + 2 * NT * STAGE_BYTES);
+    constexpr bool STAGED = !BACK;                            // results leave through a staging tile
+    constexpr int STAGING_BYTES = lb_staging_bytes(NCH, KIND);
+    unsigned char *staging = wsm + 2 * NT * STAGE_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(wsm + 2 * NT * STAGE_BYTES + STAGING_BYTES);
     // per stage and lane: the affine map from the segment's start to the lane's first element and,
     // for the real types, the map over the first half of the lane's elements (4 floats in all)
-    float4 *lane_prefix = reinterpret_cast<float4 *>(wsm + 2 * NT * STAGE_BYTES + 128);
+    float4 *lane_prefix = reinterpret_cast<float4 *>(wsm + 2 * NT * STAGE_BYTES + STAGING_BYTES + 128);
 
     const int64_t W = static_cast<int64_t>(gridDim.x) * wpc;
     const int64_t T = p.T;
@@ -497,110 +504,83 @@ __global__ void __launch_bounds__(KIND == K_BWD ? 352 : 448, 1) lookback_kernel(
 
     // ---------------- aggregate pass of the item in `slot`: lane prefixes, the segment's
     // aggregate, publication
-    // Lane aggregate of one tile in registers: the map over the lane's K elements in processing
-    // order, and (real types) the map over the first half of them.
-    auto lane_aggregate = [&](const V *a, const V *b, V &A, V &B, V &Ah, V &Bh) {
-        if constexpr (PACKED) {
-            auto J = [](int q) { return REV ? K - 1 - q : q; };
-            float2 Av = make_float2(a[J(0)], a[J(H)]);
-            float2 Bv = make_float2(b[J(0)], b[J(H)]);
-#pragma unroll
-            for (int q = 1; q < H; ++q) {
-                const float2 av = make_float2(a[J(q)], a[J(H + q)]);
-                const float2 bv = make_float2(b[J(q)], b[J(H + q)]);
-                Bv = __ffma2_rn(av, Bv, bv);
-                Av = __fmul2_rn(Av, av);
-            }
-            Ah = Av.x;
-            Bh = Bv.x;
-            A = Av.x * Av.y;
-            B = fmaf(Av.y, Bv.x, Bv.y);
-        } else {
-            constexpr int JF = REV ? K - 1 : 0;
-            A = a[JF];
-            B = b[JF];
-#pragma unroll
-            for (int q = 1; q < K; ++q) {
-                const int j = REV ? K - 1 - q : q;
-                B = vfma(a[j], B, b[j]);
-                A = vmul(A, a[j]);
-            }
-            Ah = vone(V());
-            Bh = vzero(V());
-        }
-    };
-    auto store_prefix = [&](int stage, V pA, V pB, V Ah, V Bh) {
-        if constexpr (sizeof(V) == 4) {
-            lane_prefix[stage * 32 + lane] = make_float4(pA, pB, Ah, Bh);
-        } else {
-            lane_prefix[stage * 32 + lane] = make_float4(pA.x, pA.y, pB.x, pB.y);
-        }
-    };
-
-    // ---------------- aggregate pass of the item in `slot`: lane prefixes, the segment's
-    // aggregate, publication.  A segment has at most two tiles; they are worked on side by
-    // side (the two chains of shuffles and multiply-adds are independent, which hides half of
-    // their latency), each from an identity entry, and joined afterwards.
     auto aggregate = [&](PendingItem<V> &it, int slot, Raw gate_raw) {
         it.waits_ok = true;
         it.end_gate = end_gate(it.d, gate_raw, it.waits_ok);
-        const bool two = it.d.nt > 1;
-        const int stage0 = slot * NT;
-        bool ok = mbar_wait_bounded_suspended(&bars[stage0], (phase_bits >> stage0) & 1u, LOAD_WAIT_POLLS, 2000);
-        if (two) ok = mbar_wait_bounded_suspended(&bars[stage0 + 1], (phase_bits >> (stage0 + 1)) & 1u, LOAD_WAIT_POLLS, 2000) && ok;
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) {
-            failed = true;
-            status_bits |= STATUS_LOAD_TIMEOUT;
-            return;
-        }
-        phase_bits ^= (two ? 3u : 1u) << stage0;
+        V segA = vone(V()), segB = vzero(V());      // map from the segment's start to the current tile's start
         V next_gate = it.end_gate;
-        V a0[K], b0[K], a1[K], b1[K];
-        int nv0, nv1;
-        fetch(it, slot, 0, a0, b0, next_gate, nv0);
-        if (two) {
-            fetch(it, slot, 1, a1, b1, next_gate, nv1);
-        } else {
-#pragma unroll
-            for (int j = 0; j < K; ++j) {
-                a1[j] = vone(V());
-                b1[j] = vzero(V());
+        for (int i = 0; i < it.d.nt; ++i) {
+            const int stage = slot * NT + i;
+            bool ok = mbar_wait_bounded_suspended(&bars[stage], (phase_bits >> stage) & 1u, LOAD_WAIT_POLLS, 2000);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                failed = true;
+                status_bits |= STATUS_LOAD_TIMEOUT;
+                return;
             }
-        }
-        V A0, B0, A0h, B0h, A1, B1, A1h, B1h;
-        lane_aggregate(a0, b0, A0, B0, A0h, B0h);
-        lane_aggregate(a1, b1, A1, B1, A1h, B1h);
-        // inclusive Kogge-Stone over the lanes in processing order, both tiles at once
-        const int ll = REV ? 31 - lane : lane;
+            phase_bits ^= 1u << stage;
+            V a[K], b[K];
+            int nvalid;
+            fetch(it, slot, i, a, b, next_gate, nvalid);
+            V A, B;
+            V A0h = vone(V()), B0h = vzero(V());     // real types: the map over the first half of the lane's elements
+            if constexpr (PACKED) {
+                auto J = [](int q) { return REV ? K - 1 - q : q; };
+                float2 Av = make_float2(a[J(0)], a[J(H)]);
+                float2 Bv = make_float2(b[J(0)], b[J(H)]);
 #pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
-            const V Ap0 = REV ? shfl_down(A0, d) : shfl_up(A0, d);
-            const V Bp0 = REV ? shfl_down(B0, d) : shfl_up(B0, d);
-            const V Ap1 = REV ? shfl_down(A1, d) : shfl_up(A1, d);
-            const V Bp1 = REV ? shfl_down(B1, d) : shfl_up(B1, d);
-            if (ll >= d) {
-                B0 = vfma(A0, Bp0, B0);
-                A0 = vmul(A0, Ap0);
-                B1 = vfma(A1, Bp1, B1);
-                A1 = vmul(A1, Ap1);
+                for (int q = 1; q < H; ++q) {
+                    const float2 av = make_float2(a[J(q)], a[J(H + q)]);
+                    const float2 bv = make_float2(b[J(q)], b[J(H + q)]);
+                    Bv = __ffma2_rn(av, Bv, bv);
+                    Av = __fmul2_rn(Av, av);
+                }
+                A0h = Av.x;
+                B0h = Bv.x;
+                A = Av.x * Av.y;
+                B = fmaf(Av.y, Bv.x, Bv.y);
+            } else {
+                constexpr int JF = REV ? K - 1 : 0;
+                A = a[JF];
+                B = b[JF];
+#pragma unroll
+                for (int q = 1; q < K; ++q) {
+                    const int j = REV ? K - 1 - q : q;
+                    B = vfma(a[j], B, b[j]);
+                    A = vmul(A, a[j]);
+                }
             }
+            // inclusive Kogge-Stone over the lanes in processing order; the map that enters the
+            // tile (segA, segB) goes in through the first lane
+            const int ll = REV ? 31 - lane : lane;
+            if (ll == 0) {
+                B = vfma(A, segB, B);
+                A = vmul(A, segA);
+            }
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const V Ap = REV ? shfl_down(A, d) : shfl_up(A, d);
+                const V Bp = REV ? shfl_down(B, d) : shfl_up(B, d);
+                if (ll >= d) {
+                    B = vfma(A, Bp, B);
+                    A = vmul(A, Ap);
+                }
+            }
+            // map from the segment's start to this lane's first element
+            V pA = REV ? shfl_down(A, 1) : shfl_up(A, 1);
+            V pB = REV ? shfl_down(B, 1) : shfl_up(B, 1);
+            if (ll == 0) {
+                pA = segA;
+                pB = segB;
+            }
+            if constexpr (sizeof(V) == 4) {
+                lane_prefix[stage * 32 + lane] = make_float4(pA, pB, A0h, B0h);
+            } else {
+                lane_prefix[stage * 32 + lane] = make_float4(pA.x, pA.y, pB.x, pB.y);
+            }
+            segA = shfl_idx(A, REV ? 0 : 31);
+            segB = shfl_idx(B, REV ? 0 : 31);
         }
-        // maps from the tile's start to this lane's first element, and the tiles' totals
-        V pA0 = REV ? shfl_down(A0, 1) : shfl_up(A0, 1);
-        V pB0 = REV ? shfl_down(B0, 1) : shfl_up(B0, 1);
-        V pA1 = REV ? shfl_down(A1, 1) : shfl_up(A1, 1);
-        V pB1 = REV ? shfl_down(B1, 1) : shfl_up(B1, 1);
-        if (ll == 0) {
-            pA0 = pA1 = vone(V());
-            pB0 = pB1 = vzero(V());
-        }
-        const V TA0 = shfl_idx(A0, REV ? 0 : 31), TB0 = shfl_idx(B0, REV ? 0 : 31);
-        const V TA1 = shfl_idx(A1, REV ? 0 : 31), TB1 = shfl_idx(B1, REV ? 0 : 31);
-        // the second tile starts where the first ends
-        store_prefix(stage0, pA0, pB0, A0h, B0h);
-        if (two) store_prefix(stage0 + 1, vmul(pA1, TA0), vfma(pA1, TB0, pB1), A1h, B1h);
-        const V segA = vmul(TA1, TA0), segB = vfma(TA1, TB0, TB1);
         it.segA = segA;
         it.segB = segB;
         unsigned char *row_rec = records + static_cast<uint64_t>(it.d.row0) * per_row * LB_RECORD_BYTES;
@@ -736,129 +716,130 @@ __global__ void __launch_bounds__(KIND == K_BWD ? 352 : 448, 1) lookback_kernel(
             }
         };
         {
-            // both tiles of the segment side by side (independent recurrences)
-            const bool two = cur.d.nt > 1;
-            const int stage0 = cur_slot * NT;
             V next_gate = cur.end_gate;
-            V a0[K], b0[K], a1[K], b1[K];
-            int nv0, nv1 = 0;
-            fetch(cur, cur_slot, 0, a0, b0, next_gate, nv0);
-            if (two) {
-                fetch(cur, cur_slot, 1, a1, b1, next_gate, nv1);
-            } else {
+            const int nt = cur.d.nt;
+            for (int i = 0; i < nt; ++i) {
+                V a[K], b[K];
+                int nvalid;
+                fetch(cur, cur_slot, i, a, b, next_gate, nvalid);
+                const int t = tile_of_step(cur.d, i);
+                const int64_t toff = static_cast<int64_t>(t) * TE;
+                const int stage = cur_slot * NT + i;
+                unsigned char *stg = wsm + stage * STAGE_BYTES;
+                V xp[BACK ? K : 1];
+                V x_below = vzero(V());
+                if (BACK) {
 #pragma unroll
-                for (int j = 0; j < K; ++j) {
-                    a1[j] = vone(V());
-                    b1[j] = vzero(V());
-                }
-            }
-            const int t0 = tile_of_step(cur.d, 0), t1 = tile_of_step(cur.d, 1);
-            const int64_t toff0 = static_cast<int64_t>(t0) * TE, toff1 = static_cast<int64_t>(t1) * TE;
-            unsigned char *stg0 = wsm + stage0 * STAGE_BYTES, *stg1 = stg0 + STAGE_BYTES;
-            V xp0[BACK ? K : 1], xp1[BACK ? K : 1];
-            V below0 = vzero(V()), below1 = vzero(V());
-            if (BACK) {
-#pragma unroll
-                for (int c = 0; c < NCH; ++c) {
-                    TR::unpack(*reinterpret_cast<const uint4 *>(stg0 + 2 * TB + (lane * NCH + c) * 16), &xp0[c * EPC]);
-                    if (two) TR::unpack(*reinterpret_cast<const uint4 *>(stg1 + 2 * TB + (lane * NCH + c) * 16), &xp1[c * EPC]);
-                }
-                V hv[EPC];
-                if (cur.d.pos0 + toff0 != 0) {
-                    TR::unpack(*reinterpret_cast<const uint4 *>(stg0 + NIN * TB), hv);
-                    below0 = hv[EPC - 1];
-                } else if (hstate) {
-                    below0 = hstate[row];
-                }
-                if (two) {
-                    if (cur.d.pos0 + toff1 != 0) {
-                        TR::unpack(*reinterpret_cast<const uint4 *>(stg1 + NIN * TB), hv);
-                        below1 = hv[EPC - 1];
+                    for (int c = 0; c < NCH; ++c)
+                        TR::unpack(*reinterpret_cast<const uint4 *>(stg + 2 * TB + (lane * NCH + c) * 16), &xp[c * EPC]);
+                    if (cur.d.pos0 + toff != 0) {
+                        V hv[EPC];
+                        TR::unpack(*reinterpret_cast<const uint4 *>(stg + NIN * TB), hv);
+                        x_below = hv[EPC - 1];
                     } else if (hstate) {
-                        below1 = hstate[row];
+                        x_below = hstate[row];
+                    }
+                }
+                const float4 pf = lane_prefix[stage * 32 + lane];
+                if constexpr (STAGED) {
+                    // the tile is in registers: its stage can take the matching tile of the item
+                    // after the next (whose number arrives during the first tile; the first stage
+                    // is refilled together with the second)
+                    __syncwarp();
+                    fence_async_smem();
+                    if (i >= 1) {
+                        learn_after();
+                        if (i == 1 && aft.d.valid) issue(aft.d, cur_slot, 0);
+                        if (aft.d.valid && i < aft.d.nt) issue(aft.d, cur_slot, i);
+                    }
+                }
+                if constexpr (PACKED) {
+                    auto J = [](int q) { return REV ? K - 1 - q : q; };
+                    const float x = fmaf(pf.x, x_in, pf.y);
+                    float2 Xv = make_float2(x, fmaf(pf.z, x, pf.w));       // states entering the two halves
+#pragma unroll
+                    for (int q = 0; q < H; ++q) {
+                        const float2 av = make_float2(a[J(q)], a[J(H + q)]);
+                        const float2 bv = make_float2(b[J(q)], b[J(H + q)]);
+                        Xv = __ffma2_rn(av, Xv, bv);
+                        b[J(q)] = Xv.x;
+                        b[J(H + q)] = Xv.y;
+                    }
+                } else {
+                    V x;
+                    if constexpr (sizeof(V) == 4) {
+                        x = vfma(pf.x, x_in, pf.y);
+                    } else {
+                        x = vfma(make_float2(pf.x, pf.y), x_in, make_float2(pf.z, pf.w));
+                    }
+#pragma unroll
+                    for (int q = 0; q < K; ++q) {
+                        const int j = REV ? K - 1 - q : q;
+                        x = vfma(a[j], x, b[j]);
+                        b[j] = x;
+                    }
+                }
+                if (BACK) {
+                    // d_gates[t] = conj(x[t-1]) * g[t]
+                    V dn = shfl_up(xp[K - 1], 1);
+                    if (lane == 0) dn = x_below;
+#pragma unroll
+                    for (int j = K - 1; j >= 1; --j) a[j] = vmul(vconj(xp[j - 1]), b[j]);
+                    a[0] = vmul(vconj(dn), b[0]);
+                }
+                if constexpr (STAGED) {
+                    // results into the staging tile (once the store before has read it), then out
+                    if (lane == 0) bulk_wait_read<0>();
+                    __syncwarp();
+#pragma unroll
+                    for (int c = 0; c < NCH; ++c)
+                        *reinterpret_cast<uint4 *>(staging + (lane * NCH + c) * 16) = TR::pack(&b[c * EPC]);
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        bulk_s2g(obase[0] + (cur.d.e_begin + toff) * TR::ESIZE, staging, static_cast<uint32_t>(nvalid) * TR::ESIZE);
+                        bulk_commit();
+                    }
+                } else {
+                    // results over the inputs of the stage, then out by bulk copies
+                    __syncwarp();
+#pragma unroll
+                    for (int c = 0; c < NCH; ++c) {
+                        *reinterpret_cast<uint4 *>(stg + 1 * TB + (lane * NCH + c) * 16) = TR::pack(&b[c * EPC]);
+                        if (NOUT > 1) *reinterpret_cast<uint4 *>(stg + 2 * TB + (lane * NCH + c) * 16) = TR::pack(&a[c * EPC]);
+                    }
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        const uint32_t bytes = static_cast<uint32_t>(nvalid) * TR::ESIZE;
+                        const int64_t goff = (cur.d.e_begin + toff) * TR::ESIZE;
+                        bulk_s2g(obase[0] + goff, stg + 1 * TB, bytes);
+                        if (NOUT > 1) bulk_s2g(obase[1] + goff, stg + 2 * TB, bytes);
+                        bulk_commit();
+                        // the store of the stage before this one has read its data: refill that stage
+                        if (i > 0) bulk_wait_read<1>();
+                    }
+                    __syncwarp();
+                    if (i > 0) {
+                        learn_after();
+                        if (aft.d.valid && i - 1 < aft.d.nt) issue(aft.d, cur_slot, i - 1);
                     }
                 }
             }
-            const float4 pf0 = lane_prefix[stage0 * 32 + lane];
-            const float4 pf1 = two ? lane_prefix[(stage0 + 1) * 32 + lane] : make_float4(1.0f, 0.0f, 1.0f, 0.0f);
-            if constexpr (PACKED) {
-                auto J = [](int q) { return REV ? K - 1 - q : q; };
-                const float x0 = fmaf(pf0.x, x_in, pf0.y), x1 = fmaf(pf1.x, x_in, pf1.y);
-                float2 X0 = make_float2(x0, fmaf(pf0.z, x0, pf0.w));       // states entering the two halves
-                float2 X1 = make_float2(x1, fmaf(pf1.z, x1, pf1.w));
-#pragma unroll
-                for (int q = 0; q < H; ++q) {
-                    X0 = __ffma2_rn(make_float2(a0[J(q)], a0[J(H + q)]), X0, make_float2(b0[J(q)], b0[J(H + q)]));
-                    X1 = __ffma2_rn(make_float2(a1[J(q)], a1[J(H + q)]), X1, make_float2(b1[J(q)], b1[J(H + q)]));
-                    b0[J(q)] = X0.x;
-                    b0[J(H + q)] = X0.y;
-                    b1[J(q)] = X1.x;
-                    b1[J(H + q)] = X1.y;
+            learn_after();
+            if constexpr (STAGED) {
+                // stages the loop did not refill: the only one of a one-tile item, and those the
+                // item after the next has beyond this item's tiles
+                if (aft.d.valid) {
+                    if (nt == 1) issue(aft.d, cur_slot, 0);
+                    for (int i = nt > 1 ? nt : 1; i < aft.d.nt; ++i) issue(aft.d, cur_slot, i);
                 }
             } else {
-                V x0, x1;
-                if constexpr (sizeof(V) == 4) {
-                    x0 = vfma(pf0.x, x_in, pf0.y);
-                    x1 = vfma(pf1.x, x_in, pf1.y);
-                } else {
-                    x0 = vfma(make_float2(pf0.x, pf0.y), x_in, make_float2(pf0.z, pf0.w));
-                    x1 = vfma(make_float2(pf1.x, pf1.y), x_in, make_float2(pf1.z, pf1.w));
+                if (lane == 0) bulk_wait_read<0>();
+                __syncwarp();
+                if (aft.d.valid) {
+                    for (int i = nt - 1; i < aft.d.nt; ++i) issue(aft.d, cur_slot, i);
                 }
-#pragma unroll
-                for (int q = 0; q < K; ++q) {
-                    const int j = REV ? K - 1 - q : q;
-                    x0 = vfma(a0[j], x0, b0[j]);
-                    x1 = vfma(a1[j], x1, b1[j]);
-                    b0[j] = x0;
-                    b1[j] = x1;
-                }
-            }
-            if (BACK) {
-                // d_gates[t] = conj(x[t-1]) * g[t]
-                V dn0 = shfl_up(xp0[K - 1], 1), dn1 = shfl_up(xp1[K - 1], 1);
-                if (lane == 0) {
-                    dn0 = below0;
-                    dn1 = below1;
-                }
-#pragma unroll
-                for (int j = K - 1; j >= 1; --j) {
-                    a0[j] = vmul(vconj(xp0[j - 1]), b0[j]);
-                    a1[j] = vmul(vconj(xp1[j - 1]), b1[j]);
-                }
-                a0[0] = vmul(vconj(dn0), b0[0]);
-                a1[0] = vmul(vconj(dn1), b1[0]);
-            }
-            // results over the inputs of the stages, then out by bulk copies
-            __syncwarp();
-#pragma unroll
-            for (int c = 0; c < NCH; ++c) {
-                *reinterpret_cast<uint4 *>(stg0 + 1 * TB + (lane * NCH + c) * 16) = TR::pack(&b0[c * EPC]);
-                if (NOUT > 1) *reinterpret_cast<uint4 *>(stg0 + 2 * TB + (lane * NCH + c) * 16) = TR::pack(&a0[c * EPC]);
-                if (two) {
-                    *reinterpret_cast<uint4 *>(stg1 + 1 * TB + (lane * NCH + c) * 16) = TR::pack(&b1[c * EPC]);
-                    if (NOUT > 1) *reinterpret_cast<uint4 *>(stg1 + 2 * TB + (lane * NCH + c) * 16) = TR::pack(&a1[c * EPC]);
-                }
-            }
-            fence_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-                const int64_t goff0 = (cur.d.e_begin + toff0) * TR::ESIZE;
-                bulk_s2g(obase[0] + goff0, stg0 + 1 * TB, static_cast<uint32_t>(nv0) * TR::ESIZE);
-                if (NOUT > 1) bulk_s2g(obase[1] + goff0, stg0 + 2 * TB, static_cast<uint32_t>(nv0) * TR::ESIZE);
-                if (two) {
-                    const int64_t goff1 = (cur.d.e_begin + toff1) * TR::ESIZE;
-                    bulk_s2g(obase[0] + goff1, stg1 + 1 * TB, static_cast<uint32_t>(nv1) * TR::ESIZE);
-                    if (NOUT > 1) bulk_s2g(obase[1] + goff1, stg1 + 2 * TB, static_cast<uint32_t>(nv1) * TR::ESIZE);
-                }
-                bulk_commit();
-            }
-            // the ticket has had the whole pass to arrive; once the stores have read the stages,
-            // the stages take the tiles of the item after the next
-            learn_after();
-            if (lane == 0) bulk_wait_read<0>();
-            __syncwarp();
-            if (aft.d.valid) {
-                for (int i = 0; i < aft.d.nt; ++i) issue(aft.d, cur_slot, i);
             }
         }
         cur = nxt;

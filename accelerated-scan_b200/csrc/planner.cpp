@@ -115,7 +115,7 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     const bool scan_kind = in.kind == ASCAN_KIND_FORWARD || in.kind == ASCAN_KIND_BACKWARD;
     {
         int lb_tiles = in.tune.lookback_tiles > 0 ? in.tune.lookback_tiles : 2;
-        if (lb_tiles > 2) lb_tiles = 2;
+        if (lb_tiles > 8) lb_tiles = 8;
         // below three rows per four SMs (measured on 148 SMs: at 96 rows look-back and teams of 12
         // warps tie, at 128 rows the teams win by 10-20 %)
         const int64_t lookback_rows = in.sm_count * 3 / 4;
@@ -127,9 +127,10 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
         if (possible && wanted && in.rows * segs < (1ll << 31)) {
             // two resident segments per warp (lb_warp_smem in lookback.cuh)
             const int stage = nin_of(in.kind) * 32 * 3 * 16 + (in.kind == ASCAN_KIND_BACKWARD ? 128 : 0);
-            const int wsm = 2 * lb_tiles * stage + 128 + 2 * lb_tiles * 32 * 16;
+            const int staging = in.kind == ASCAN_KIND_BACKWARD ? 0 : 32 * 3 * 16;
+            const int wsm = 2 * lb_tiles * stage + staging + 128 + 2 * lb_tiles * 32 * 16;
             int wpc = kMaxSmemPerCta / wsm;
-            const int cap = in.kind == ASCAN_KIND_BACKWARD ? 11 : 14;      // the kernels' launch bounds
+            const int cap = 16;
             if (wpc > cap) wpc = cap;
             if (in.tune.warps_per_cta > 0 && in.tune.warps_per_cta < wpc) wpc = in.tune.warps_per_cta;
             if (wpc < 1) return ASCAN_ERR_UNSUPPORTED;

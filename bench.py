@@ -974,6 +974,18 @@ def run_reference_gpu(args):
     line.update({"value": round(32 * n / ((tf + tb) * 1e-3) / 1e9, 1), "fwd_ms": round(tf, 4), "bwd_ms": round(tb, 4),
                  "fwd_GBps": round(12 * n / tf / 1e6, 1), "bwd_GBps": round(20 * n / tb / 1e6, 1), "steps": K,
                  "parity": parity_check(torch, "fp32", gates, tokens, grad_out, out, dg, dx, subset_rows(B, C))})
+    line["parity"]["inputs"] = "gates 0.999+0.001*U(0,1) (the benchmark's law: states remember thousands of steps)"
+    # the same comparison with the input law of the reference's own tests (tests/test_eq.py:16-19)
+    Ts = min(T, 4096)
+    g2 = torch.rand(B, C, Ts, device=dev, generator=gen)
+    x2 = torch.rand(B, C, Ts, device=dev, generator=gen)
+    go2 = torch.randn(B, C, Ts, device=dev, generator=gen)
+    o2, dg2, dx2 = torch.empty_like(x2), torch.empty_like(x2), torch.empty_like(x2)
+    mod.warpscan_forward(g2, x2, o2, False)
+    mod.warpscan_backward(g2, o2, go2, dg2, dx2)
+    torch.cuda.synchronize()
+    line["parity_uniform_gates"] = parity_check(torch, "fp32", g2, x2, go2, o2, dg2, dx2, subset_rows(B, C))
+    line["parity_uniform_gates"]["inputs"] = f"({B},{C},{Ts}), gates and tokens U(0,1)"
     print(json.dumps(line), flush=True)
 
 

@@ -133,9 +133,9 @@ def test_small_workspace_steps_down_to_chained(cuda_device):
     assert rel_err(to_np(out2), want) <= 1e-5
 
 
-@pytest.mark.parametrize("lb_tiles", [1, 2])
+@pytest.mark.parametrize("lb_tiles", [1, 3, 4])
 def test_lookback_with_other_segment_lengths(cuda_device, lb_tiles):
-    """The look-back plan with other segment lengths than the default (one tile per segment instead of two): same results, forward and backward."""
+    """The look-back plan with other segment lengths than the default (1, 3 and 4 tiles per segment): same results, forward and backward."""
     from accelerated_scan import _native
 
     default_tiles = _native.get_option(_native.OPT_LOOKBACK_TILES)
