@@ -6,16 +6,17 @@
 // the ticket counter by persistent warps, so the segments of a handful of rows are in
 // flight at any time, spread over every SM.
 //
-// A warp keeps its whole segment in shared memory.  It
-//   1. loads the segment's tiles with bulk asynchronous copies (one stage per tile),
+// A warp keeps whole segments in shared memory, two at a time.  For a segment it
+//   1. loads the tiles with bulk asynchronous copies (one stage per tile),
 //   2. computes the segment's AGGREGATE, the affine map x -> A*x + B from the state before
 //      the segment to the state after it, leaving in shared memory, per tile and lane, the
 //      map from the segment's start to the lane's first element,
 //   3. publishes the aggregate in the segment's record,
 //   4. composes the aggregates of all earlier segments of the row into its incoming state,
-//   5. runs the recurrence from shared memory (no second read of global memory), writes the
-//      results over the inputs in shared memory and stores them with bulk copies; a stage
-//      whose store has been read out is refilled with the matching tile of the next item.
+//   5. runs the recurrence from shared memory (no second read of global memory) and stores
+//      the results with bulk copies; stages that have drained are refilled with the tiles
+//      of a later item.
+// Steps 1-3 of the next segment run before steps 4-5 of this one (see the kernel).
 //
 // Step 4 never waits for another warp's step 4: it reads only aggregates, which depend on
 // nothing but their own segment's data.  Aggregates are kept at three levels -- segments,
