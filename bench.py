@@ -909,7 +909,10 @@ def run_e2e(args, torch, dist, warp, dev, world, dtype, esize):
     gbs = world * 8 * esize * n_elems / dt / 1e9
     return ({"value": round(gbs, 2), "unit": UNIT, "h2d_bytes_per_step": 3 * esize * n_elems,
              "d2h_bytes_per_step": 3 * esize * n_elems, "ms_per_step": round(dt * 1e3, 3), "steps": args.e2e_steps,
-             "api": f"accelerated_scan.warp.scan + autograd backward, {slabs} row slabs pipelined on {len(streams)} streams"}, launches)
+             "api": f"accelerated_scan.warp.scan + autograd backward, {slabs} row slabs pipelined on {len(streams)} streams",
+             "where_the_time_goes": f"host<->device copies: {3 * esize * n_elems / dt / 1e9:.1f} GB/s in each direction at once per GPU "
+                                    "(the kernels need about 2 % of the step); with several ranks the copies of all GPUs share "
+                                    "the host's memory and PCIe root"}, launches)
 
 
 def run_reference_gpu(args):

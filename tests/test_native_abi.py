@@ -47,7 +47,7 @@ def test_bad_arguments_rejected_without_gpu():
     assert lib.ascan_check(null, null) == 1
 
 
-@pytest.mark.parametrize("T", [1, 7, 32, 64, 128, 1024, 4096, 65536, 16323, 8000, 33753, 127323, 1 << 20])
+@pytest.mark.parametrize("T", [1, 7, 32, 64, 128, 256, 512, 1024, 4096, 65536, 16323, 8000, 33753, 127323, 1 << 20])
 @pytest.mark.parametrize("dtype", [_native.F32, _native.BF16, _native.F16, _native.C64])
 @pytest.mark.parametrize("kind", [0, 1, 2, 3])
 def test_planner_invariants(T, dtype, kind):
@@ -92,6 +92,13 @@ def test_planner_invariants(T, dtype, kind):
             assert (148 * per_cta) // pl["team_size"] <= max(rows, 148) or pl["team_size"] == per_cta
         else:
             assert pl["team_size"] == 1
+        if pl["row_grid"]:
+            # short rows on the tile grid: unseeded scan kinds, two chunks per lane, rows divide the tile, whole
+            # tiles per item, never split, bulk loader
+            assert kind in (0, 1) and pl["chunks_per_lane"] == 2 and pl["loader"] == 0 and pl["kernel"] == 0
+            assert pl["tile_elems"] % T == 0 and T % (pl["tile_elems"] // 32) == 0
+            assert (pl["rows_per_item"] * T) % pl["tile_elems"] == 0 and pl["segs_per_row"] == 1
+            assert _native.plan(rows, T, dtype, kind, sm_count=148, seeded=True)["row_grid"] == 0
         if pl["segs_per_row"] > 1:
             # split rows: one row per item, segments are whole tiles
             assert pl["rows_per_item"] == 1 and pl["seg_elems"] % pl["tile_elems"] == 0
