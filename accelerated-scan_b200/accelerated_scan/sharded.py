@@ -94,15 +94,21 @@ class PeerExchange:
             self.fwd = ptrs
             self.bwd = [p + self.nbytes for p in ptrs]
         else:
-            self.close()
+            self.close()        # (every rank gets here together: the flags were gathered)
 
-    def close(self):
+    def unmap(self):
+        """Unmaps the other ranks' buffers from this process."""
         for p in self.opened:
             try:
                 _native.peer_close(p)
             except RuntimeError:
                 pass
         self.opened = []
+        self.usable = False
+
+    def release(self):
+        """Frees this rank's own buffer.  Call it after every rank has unmapped (a buffer must
+        not be freed while another process still maps it)."""
         if self.local is not None:
             try:
                 _native.peer_free(self.local)
@@ -110,6 +116,14 @@ class PeerExchange:
                 pass
             self.local = None
         self.usable = False
+
+    def close(self):
+        """unmap, a host barrier of the group, release: collective over the group."""
+        self.unmap()
+        if dist.is_initialized():
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.group)
+        self.release()
 
     def next_call(self, backward: bool) -> int:
         self.calls[int(backward)] += 1
@@ -126,6 +140,7 @@ class PeerExchange:
 
     @classmethod
     def close_all(cls):
+        """Closes every exchange of this process (collective: all ranks call it at the same point)."""
         for ex in cls._cache.values():
             ex.close()
         cls._cache.clear()

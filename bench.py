@@ -840,6 +840,9 @@ def run_time_sharded(args, torch, dist, dev, world, rank):
         dist.all_reduce(flag)
         parity["ok"] = flag.item() == 0
     del parts
+    if world > 1:
+        barrier()
+        sharded.PeerExchange.close_all()        # unmap the peers' buffers, release the local one
     return {"workload": f"({Bt},{Ct},{Tt}) fp32 fwd+bwd, time-sharded over {world} GPU(s)", "scaling": "strong",
             "value": round(gbs, 1), "unit": UNIT, "ms_per_step": round(ms, 4), "steps": K,
             "path": "plain kernels" if world == 1 else ("single pass" if single_pass else "three steps"),
