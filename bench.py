@@ -513,6 +513,8 @@ def run_b200(args):
             "ms_per_launch": round(fwd_ms, 5),
         },
         "pct_of_nominal_8TBs": round(100 * value / world / 8000.0, 2),
+        # the fp32 half of the metric ("bf16/fp32"), from the `also` leg of this run (one GPU, same shape)
+        "value_fp32": (also[0]["value"] if also else None),
         "time_sharded": time_sharded,
         "time_sharded_slice_kernels": slice_kernels,
         "sweep": sweep,
