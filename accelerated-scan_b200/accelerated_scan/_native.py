@@ -119,7 +119,7 @@ EXPORTS = (
 )
 
 (OPT_STAGES, OPT_WARPS_PER_CTA, OPT_LOOKBACK_TILES, OPT_DISABLE_PLANS, OPT_TEST_DROP_CARRY, OPT_TEST_EPOCH_BITS,
- OPT_ITEMS_PER_WARP) = range(7)
+ OPT_ITEMS_PER_WARP, OPT_STATIC_BELOW) = range(8)
 
 
 def strerror(code: int) -> str:

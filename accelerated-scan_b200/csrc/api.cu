@@ -37,7 +37,7 @@ static int cached_sm_count(int *out) {
 
 // ---- options (ascan_set_option): process-wide, read on every call, never from the environment
 static std::atomic<int> g_opt_stages{2}, g_opt_wpc{0}, g_opt_lookback_tiles{0}, g_opt_disable_plans{0};
-static std::atomic<int> g_opt_drop_carry{0}, g_opt_epoch_bits{17}, g_opt_items_per_warp{4};
+static std::atomic<int> g_opt_drop_carry{0}, g_opt_epoch_bits{17}, g_opt_items_per_warp{4}, g_opt_static_below{8};
 static std::atomic<uint32_t> g_opt_generation{0};
 
 static PlanTuning current_tuning() {
@@ -47,6 +47,7 @@ static PlanTuning current_tuning() {
     t.lookback_tiles = g_opt_lookback_tiles.load(std::memory_order_relaxed);
     t.disable_plans = g_opt_disable_plans.load(std::memory_order_relaxed);
     t.items_per_warp = g_opt_items_per_warp.load(std::memory_order_relaxed);
+    t.static_below = g_opt_static_below.load(std::memory_order_relaxed);
     return t;
 }
 
@@ -379,6 +380,10 @@ int ascan_set_option(int option, int value) {
             if (value < 1 || value > 64) return ASCAN_ERR_INVALID_ARG;
             g_opt_items_per_warp.store(value);
             break;
+        case ASCAN_OPT_STATIC_BELOW:
+            if (value < 0 || value > 1024) return ASCAN_ERR_INVALID_ARG;
+            g_opt_static_below.store(value);
+            break;
         case ASCAN_OPT_TEST_DROP_CARRY: g_opt_drop_carry.store(value ? 1 : 0); break;
         case ASCAN_OPT_TEST_EPOCH_BITS:
             if (value < 1 || value > 17) return ASCAN_ERR_INVALID_ARG;
@@ -397,6 +402,7 @@ int ascan_get_option(int option) {
         case ASCAN_OPT_LOOKBACK_TILES: return g_opt_lookback_tiles.load();
         case ASCAN_OPT_DISABLE_PLANS: return g_opt_disable_plans.load();
         case ASCAN_OPT_ITEMS_PER_WARP: return g_opt_items_per_warp.load();
+        case ASCAN_OPT_STATIC_BELOW: return g_opt_static_below.load();
         case ASCAN_OPT_TEST_DROP_CARRY: return g_opt_drop_carry.load();
         case ASCAN_OPT_TEST_EPOCH_BITS: return g_opt_epoch_bits.load();
         default: return -1;

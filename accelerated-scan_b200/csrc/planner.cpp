@@ -314,9 +314,15 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
             grid = in.sm_count;
         }
     }
-    // A problem of at most two items per warp gains nothing from tickets: deal statically and
-    // save the ticket and exit-counter round trips (they are a fifth of a 15 us kernel).
-    if (pl.dynamic && team == 1 && pl.segs_per_row == 1 && pl.items <= 2 * grid * wpc) {
+    // A problem of a few items per warp gains less from tickets than they cost (an atomic, its
+    // broadcast and the exit counter per item): deal round-robin.  (8,1536,L) bf16 at about six
+    // one-row items per warp, forward / backward GB/s: L = 1024 2458 / 3614 -> 2836 / 4389, 2048
+    // 4092 / 4726 -> 4608 / 5343, 4096 5085 / 5715 -> 5671 / 5996, 8192 6142 / 5994 -> 6279 / 5994.
+    // Only for launches of up to 48 tiles per warp (some 100 us): beyond that the tickets' balancing
+    // wins again (fp32 (8,1536,4096) backward 6222 -> 5990, (8,1536,8192) 6205 -> 5915 without them).
+    const int64_t tiles_all = (in.rows * in.seqlen + te - 1) / te;
+    if (pl.dynamic && team == 1 && pl.segs_per_row == 1 && tiles_all <= 48 * grid * wpc &&
+        pl.items <= static_cast<int64_t>(in.tune.static_below > 0 ? in.tune.static_below : 0) * grid * wpc) {
         pl.dynamic = 0;
     }
     pl.team_size = team;

@@ -308,7 +308,8 @@ typedef enum {
     ASCAN_OPT_DISABLE_PLANS = 3,   /* bit 0 no look-back, bit 1 no team, bit 2 static deal, bit 3 plain loader, bit 4 no row grid */
     ASCAN_OPT_TEST_DROP_CARRY = 4, /* 1: drop one carry hand-over per launch (a wait expires)  */
     ASCAN_OPT_TEST_EPOCH_BITS = 5, /* width of the launch epoch, 1..17 (default 17)            */
-    ASCAN_OPT_ITEMS_PER_WARP = 6   /* items per warp that grouped short rows aim for (default 4) */
+    ASCAN_OPT_ITEMS_PER_WARP = 6,  /* items per warp that grouped short rows aim for (default 4) */
+    ASCAN_OPT_STATIC_BELOW = 7     /* unsplit rows: up to this many items per warp are dealt without tickets (default 8) */
 } ascan_option;
 int ascan_set_option(int option, int value);
 int ascan_get_option(int option);          /* -1 for an unknown option */
