@@ -258,6 +258,11 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
         if (fit < seg_tiles) seg_tiles = static_cast<int>(fit);
         int64_t rpi = (seg_tiles * te) / in.seqlen;
         if (rpi < 1) rpi = 1;
+        // Rows of a tile or more are never grouped: the kernels for grouped rows find the row
+        // boundaries per element and run at a third to a half of the one-row-per-item kernels'
+        // rate ((32,1536,L) bf16 forward / backward GB/s, grouped -> one row per item: L = 1024
+        // 2303 / 2409 -> 3511 / 4962, 2048 3429 / 3536 -> 5362 / 5922, 4096 4537 / 4499 -> 6411 / 6467).
+        if (in.seqlen >= te) rpi = 1;
         if (bulk) rpi = (rpi + align_rows - 1) / align_rows * align_rows;
         if (row_grid && te > in.seqlen) {
             // whole tiles per item: a multiple of the rows of one tile
