@@ -373,7 +373,7 @@ int ascan_set_option(int option, int value) {
             g_opt_lookback_tiles.store(value);
             break;
         case ASCAN_OPT_DISABLE_PLANS:
-            if (value < 0 || value > 31) return ASCAN_ERR_INVALID_ARG;
+            if (value < 0 || value > 63) return ASCAN_ERR_INVALID_ARG;
             g_opt_disable_plans.store(value);
             break;
         case ASCAN_OPT_ITEMS_PER_WARP:

@@ -87,6 +87,14 @@ static int launch_nch(const StreamParams &p, const ascan_plan &pl, cudaStream_t 
                 if (pl.kernel == 0) return launch_loader<TR, 2, KIND, REVERSE>(p, pl, stream);
             }
             return ASCAN_ERR_UNSUPPORTED;
+        case 4:
+            // four chunks per lane: the forward of the 16-bit dtypes on rows of exactly one 1024-element
+            // tile (instead of a full three-chunk tile and a ragged one)
+            if constexpr (KIND == K_SCAN && TR::EPC == 8) {
+                if (pl.kernel == 0 && pl.loader == 0 && pl.rows_per_item == 1 && !pl.row_grid)
+                    return launch_kernel(stream_kernel<TR, 4, KIND, REVERSE, true, false>, p, pl, stream);
+            }
+            return ASCAN_ERR_UNSUPPORTED;
         default: return ASCAN_ERR_UNSUPPORTED;
     }
 }

@@ -71,9 +71,18 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     const bool scan_kind_early = in.kind == ASCAN_KIND_FORWARD || in.kind == ASCAN_KIND_BACKWARD;
     const bool row_grid = in.allow_grid && scan_kind_early && in.aligned && !in.three_chunks && in.rows >= team_rows &&
                       in.seqlen % k2 == 0 && te2 % in.seqlen == 0 && (in.tune.disable_plans & (8 | 16)) == 0;
-    const int nch = (row_grid || (in.kind == ASCAN_KIND_BACKWARD && esize == 2 && in.rows >= team_rows && !in.three_chunks))
-                        ? 2
-                        : 3;
+    // Forward of the 16-bit dtypes on rows of exactly 1024 steps: four chunks per lane, so that a row
+    // is one tile instead of a full one and a ragged one of a third ((8,1536,1024) bf16 forward 2836 ->
+    // 3356 GB/s).  Longer rows keep three chunks: there the four-way conflicts of the 16-byte shared
+    // accesses cost more than the ragged tile (2048 steps 4608 -> 4096, 4096 steps 5671 -> 4757 GB/s).
+    const int64_t te4 = 32 * 4 * (16 / esize);
+    const bool four = !row_grid && in.kind == ASCAN_KIND_FORWARD && esize == 2 && in.aligned && !in.three_chunks &&
+                      in.allow_grid && in.rows >= team_rows && in.seqlen == te4 &&
+                      (in.tune.disable_plans & (8 | 32)) == 0;
+    const int nch = four ? 4
+                         : ((row_grid || (in.kind == ASCAN_KIND_BACKWARD && esize == 2 && in.rows >= team_rows && !in.three_chunks))
+                                ? 2
+                                : 3);
     pl.row_grid = row_grid ? 1 : 0;
     const int64_t te = 32 * nch * (16 / esize);
     // tickets and split-row item numbers are 32-bit
@@ -262,7 +271,7 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
         // boundaries per element and run at a third to a half of the one-row-per-item kernels'
         // rate ((32,1536,L) bf16 forward / backward GB/s, grouped -> one row per item: L = 1024
         // 2303 / 2409 -> 3511 / 4962, 2048 3429 / 3536 -> 5362 / 5922, 4096 4537 / 4499 -> 6411 / 6467).
-        if (in.seqlen >= te) rpi = 1;
+        if (in.seqlen >= te && !row_grid) rpi = 1;
         if (bulk) rpi = (rpi + align_rows - 1) / align_rows * align_rows;
         if (row_grid && te > in.seqlen) {
             // whole tiles per item: a multiple of the rows of one tile
@@ -323,10 +332,10 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     // broadcast and the exit counter per item): deal round-robin.  (8,1536,L) bf16 at about six
     // one-row items per warp, forward / backward GB/s: L = 1024 2458 / 3614 -> 2836 / 4389, 2048
     // 4092 / 4726 -> 4608 / 5343, 4096 5085 / 5715 -> 5671 / 5996, 8192 6142 / 5994 -> 6279 / 5994.
-    // Only for launches of up to 48 tiles per warp (some 100 us): beyond that the tickets' balancing
+    // Only for launches of up to 48 three-chunk tiles per warp (some 100 us): beyond that the tickets' balancing
     // wins again (fp32 (8,1536,4096) backward 6222 -> 5990, (8,1536,8192) 6205 -> 5915 without them).
-    const int64_t tiles_all = (in.rows * in.seqlen + te - 1) / te;
-    if (pl.dynamic && team == 1 && pl.segs_per_row == 1 && tiles_all <= 48 * grid * wpc &&
+    const int64_t bytes_all = in.rows * in.seqlen * esize;               // per stream
+    if (pl.dynamic && team == 1 && pl.segs_per_row == 1 && bytes_all <= 48 * 1536 * grid * wpc &&
         pl.items <= static_cast<int64_t>(in.tune.static_below > 0 ? in.tune.static_below : 0) * grid * wpc) {
         pl.dynamic = 0;
     }

@@ -24,7 +24,7 @@ struct PlanTuning {
     int lookback_tiles = 0;    // tiles per segment of the look-back plan; 0 = the default (2)
     int items_per_warp = 4;    // items per warp that grouped short rows aim for (at most two: dealt statically)
     int static_below = 8;      // unsplit rows: at most this many items per warp are dealt round-robin, without tickets
-    int disable_plans = 0;     // bit 0: no look-back, bit 1: no team, bit 2: static deal (no tickets), bit 3: plain loader, bit 4: no row grid
+    int disable_plans = 0;     // bit 0: no look-back, bit 1: no team, bit 2: static deal (no tickets), bit 3: plain loader, bit 4: no row grid, bit 5: no four-chunk tiles
 };
 
 struct PlanInput {

@@ -305,7 +305,7 @@ typedef enum {
     ASCAN_OPT_STAGES = 0,          /* shared-memory stages per warp, 1..8 (default 2)          */
     ASCAN_OPT_WARPS_PER_CTA = 1,   /* upper bound on warps per CTA, 0 = planner's choice       */
     ASCAN_OPT_LOOKBACK_TILES = 2,  /* tiles per segment of the look-back plan                  */
-    ASCAN_OPT_DISABLE_PLANS = 3,   /* bit 0 no look-back, bit 1 no team, bit 2 static deal, bit 3 plain loader, bit 4 no row grid */
+    ASCAN_OPT_DISABLE_PLANS = 3,   /* bit 0 no look-back, bit 1 no team, bit 2 static deal, bit 3 plain loader, bit 4 no row grid, bit 5 no four-chunk tiles */
     ASCAN_OPT_TEST_DROP_CARRY = 4, /* 1: drop one carry hand-over per launch (a wait expires)  */
     ASCAN_OPT_TEST_EPOCH_BITS = 5, /* width of the launch epoch, 1..17 (default 17)            */
     ASCAN_OPT_ITEMS_PER_WARP = 6,  /* items per warp that grouped short rows aim for (default 4) */
