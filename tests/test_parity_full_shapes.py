@@ -13,7 +13,7 @@ from oracle import scan_oracle
 
 pytestmark = pytest.mark.gpu
 
-BAR = {torch.float32: 1e-5, torch.complex64: 1e-5, torch.bfloat16: 2.0 ** -8}
+BAR = {torch.float32: 1e-5, torch.complex64: 1e-5, torch.bfloat16: 2.0 ** -8, torch.float16: 2.0 ** -10}
 
 
 def _subset(batch, dim, k=8):
@@ -105,3 +105,12 @@ def test_length_sweep_shapes_bf16(cuda_device, L):
     if L <= 256:
         assert _native.plan(8 * 1536, L, _native.BF16, _native.KIND_FORWARD)["rows_per_item"] > 1
     _check(cuda_device, (8, 1536, L), torch.bfloat16, "near_one", 200 + L, "native")
+
+
+def test_rows_of_one_four_chunk_tile_fp16(cuda_device):
+    """(8, 1536, 1024) fp16: the forward takes four chunks per lane (one 1024-element tile per row)."""
+    from accelerated_scan import _native
+
+    assert _native.plan(8 * 1536, 1024, _native.F16, _native.KIND_FORWARD)["chunks_per_lane"] == 4
+    assert _native.plan(8 * 1536, 1024, _native.BF16, _native.KIND_FORWARD)["chunks_per_lane"] == 4
+    _check(cuda_device, (8, 1536, 1024), torch.float16, "uniform", 301, "native")
