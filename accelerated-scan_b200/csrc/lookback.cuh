@@ -70,12 +70,7 @@ __host__ __device__ constexpr int lb_stage_bytes(int nch, int kind) {
 // The forward kinds send their results through a staging tile of their own, so that a stage can
 // be refilled as soon as its tile is in registers; the fused backward writes its two results over
 // the stage's inputs (a staging area would cost it two warps per CTA).
-#ifndef ASCAN_LB_FWD_STAGED
-#define ASCAN_LB_FWD_STAGED 1
-#endif
-__host__ __device__ constexpr int lb_staging_bytes(int nch, int kind) {
-    return (kind == K_BWD || !ASCAN_LB_FWD_STAGED) ? 0 : 32 * nch * 16;
-}
+__host__ __device__ constexpr int lb_staging_bytes(int nch, int kind) { return kind == K_BWD ? 0 : 32 * nch * 16; }
 // Two resident segments of `nt` tiles per warp, the staging tile, the mbarriers, and 16 bytes per
 // stage and lane of prefix maps.
 __host__ __device__ constexpr int lb_warp_smem(int nch, int nt, int kind) {
@@ -285,7 +280,7 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
     const int wib = threadIdx.x >> 5;
     const int wpc = blockDim.x >> 5;
     unsigned char *wsm = smem_raw + static_cast<size_t>(wib) * WARP_SMEM;
-    constexpr bool STAGED = !BACK && ASCAN_LB_FWD_STAGED;                            // results leave through a staging tile
+    constexpr bool STAGED = !BACK;                            // results leave through a staging tile
     constexpr int STAGING_BYTES = lb_staging_bytes(NCH, KIND);
     unsigned char *staging = wsm + 2 * NT * STAGE_BYTES;
     uint64_t *bars = reinterpret_cast<uint64_t *>(wsm + 2 * NT * STAGE_BYTES + STAGING_BYTES);

@@ -136,10 +136,7 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
         if (possible && wanted && in.rows * segs < (1ll << 31)) {
             // two resident segments per warp (lb_warp_smem in lookback.cuh)
             const int stage = nin_of(in.kind) * 32 * 3 * 16 + (in.kind == ASCAN_KIND_BACKWARD ? 128 : 0);
-            #ifndef ASCAN_LB_FWD_STAGED
-#define ASCAN_LB_FWD_STAGED 1
-#endif
-            const int staging = (in.kind == ASCAN_KIND_BACKWARD || !ASCAN_LB_FWD_STAGED) ? 0 : 32 * 3 * 16;
+            const int staging = in.kind == ASCAN_KIND_BACKWARD ? 0 : 32 * 3 * 16;
             const int wsm = 2 * lb_tiles * stage + staging + 128 + 2 * lb_tiles * 32 * 16;
             int wpc = kMaxSmemPerCta / wsm;
             const int cap = 16;
