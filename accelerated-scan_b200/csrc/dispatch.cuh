@@ -45,6 +45,12 @@ static int launch_kernel(KFN kfn, const StreamParams &p, const ascan_plan &pl, c
 template <class TR, int KIND, bool REVERSE>
 static int launch_lookback(const StreamParams &p, const ascan_plan &pl, cudaStream_t stream, const ShardParams *sp) {
     auto kfn = lookback_kernel<TR, 3, KIND, REVERSE>;
+    // the planner restates the kernel's shared-memory layout: refuse a plan that disagrees with it
+    const int workers = pl.warps_per_cta - 1;
+    if (workers < 1 || workers > LB_MAX_WORKERS || pl.stages < 1 || pl.stages > LB_MAX_TILES ||
+        pl.smem_bytes != static_cast<uint64_t>(workers) * lb_warp_smem(3, pl.stages, KIND) + LB_TEAM_BYTES ||
+        pl.seg_elems != static_cast<int64_t>(workers) * pl.stages * 32 * 3 * TR::EPC)
+        return ASCAN_ERR_UNSUPPORTED;
     int rc = ensure_smem(reinterpret_cast<const void *>(kfn));
     if (rc != ASCAN_OK) return rc;
     ShardParams none = {};

@@ -1,34 +1,42 @@
 // Look-back scan kernel: single pass, for matrices with clearly fewer rows than SMs and for
 // rows whose time axis is sharded over several GPUs.
 //
-// A row is cut into SEGMENTS of a few tiles; an item is one segment, items are numbered
-// row-major (all segments of row 0 in processing order, then row 1, ...) and drawn from
-// the ticket counter by persistent warps, so the segments of a handful of rows are in
-// flight at any time, spread over every SM.
+// A row is cut into SEGMENTS; an item is one segment, items are numbered row-major (all
+// segments of row 0 in processing order, then row 1, ...) and drawn from the ticket counter
+// by persistent CTAs, so the segments of a handful of rows are in flight at any time, spread
+// over every SM.
 //
-// A warp keeps whole segments in shared memory, two at a time.  For a segment it
-//   1. loads the tiles with bulk asynchronous copies (one stage per tile),
-//   2. computes the segment's AGGREGATE, the affine map x -> A*x + B from the state before
-//      the segment to the state after it, leaving in shared memory, per tile and lane, the
-//      map from the segment's start to the lane's first element,
-//   3. publishes the aggregate in the segment's record,
-//   4. composes the aggregates of all earlier segments of the row into its incoming state,
-//   5. runs the recurrence from shared memory (no second read of global memory) and stores
-//      the results with bulk copies; stages that have drained are refilled with the tiles
-//      of a later item.
-// Steps 1-3 of the next segment run before steps 4-5 of this one (see the kernel).
+// A CTA works on a segment as a team.  Its G worker warps each take NT consecutive tiles of
+// the segment (a segment is G * NT tiles) and keep them in shared memory; the last warp of
+// the CTA keeps the books.  For a segment
+//   1. every worker loads its tiles with bulk asynchronous copies (one stage per tile) and
+//      computes the AGGREGATE of its part, the affine map x -> A*x + B from the state before
+//      the part to the state after it, leaving in shared memory, per tile and lane, the map
+//      from the part's start to the lane's first element;
+//   2. the worker that finishes last composes the G parts into the segment's aggregate and
+//      publishes it in the segment's record;
+//   3. the bookkeeper composes the aggregates of all earlier segments of the row into the
+//      state entering the segment, and hands every worker the state entering its part;
+//   4. every worker runs the recurrence from shared memory (no second read of global memory)
+//      and stores the results with bulk copies; stages that have drained are refilled with
+//      the worker's tiles of the segment after the next.
+// Step 1 of the next segment runs before step 4 of this one, so two segments are resident
+// per CTA and step 3 has a whole aggregate pass to finish.  The bookkeeper also draws the
+// tickets, each only after the look-back of the segment two before it: nothing that a
+// published aggregate depends on ever waits for a look-back, so step 3 never waits for
+// another CTA's step 3 (such waits would chain up).  Tickets, records and look-backs cost
+// one warp's time per segment instead of every warp's time per few tiles.
 //
-// Step 4 never waits for another warp's step 4: it reads only aggregates, which depend on
-// nothing but their own segment's data.  Aggregates are kept at three levels -- segments,
-// blocks of 32 segments, super-blocks of 32 blocks; the warp that owns the last segment of a
-// block (super-block) composes and publishes the block's (super-block's) aggregate -- so a
-// look-back reads at most 31 records per level (plus one window per 32 super-blocks in very
-// long rows).  Which records are composed, and in which order, depends only on the segment's
-// number: results are bitwise reproducible.  Records are self-tagged 64-bit words (payload,
-// launch tag); every wait is bounded and ends in a status bit.
+// Aggregates are kept at three levels -- segments, blocks of 32 segments, super-blocks of 32
+// blocks; the warp that publishes the last segment of a block (super-block) composes and
+// publishes the block's (super-block's) aggregate -- so a look-back reads at most 31 records
+// per level (plus one window per 32 super-blocks in very long rows).  Which records are
+// composed, and in which order, depends only on the segment's number: results are bitwise
+// reproducible.  Records are self-tagged 64-bit words (payload, launch tag); every wait is
+// bounded and ends in a status bit.
 //
 // Time sharding over GPUs (ShardParams.world > 1): every rank runs this kernel on its time
-// slice of all rows.  The warp that owns the last segment of a row's slice composes the
+// slice of all rows.  The warp that publishes the last segment of a row's slice composes the
 // slice's aggregate and stores it, with plain 64-bit stores, into the exchange buffers of
 // the ranks that come later in processing order; a segment's incoming state is then the
 // fold, in rank order, of the earlier ranks' slice aggregates (read from this rank's own
@@ -41,9 +49,12 @@
 namespace ascan {
 
 constexpr int LB_RECORD_BYTES = 32;          // one affine pair of the compute type in tagged 64-bit words
-constexpr int LB_MAX_TILES = 8;              // tiles per segment, at most (a warp holds two segments: 2 stages per tile)
+constexpr int LB_MAX_TILES = 8;              // tiles per worker and segment, at most (a worker holds two segments: 2 stages per tile)
+constexpr int LB_MAX_WORKERS = 15;           // worker warps per CTA, at most (plus the bookkeeper)
+constexpr int LB_TEAM_BYTES = 1024;          // shared memory of the team: parts, incoming states, tickets, mbarriers
 constexpr int MAX_WORLD = 16;                // ranks of a time-sharded scan, at most
 constexpr uint32_t LB_WAIT_POLLS = 1u << 20;      // about a second
+constexpr uint32_t LB_TEAM_POLLS = 1u << 22;      // waits inside a CTA: a safety net, they end on the abort flag
 
 // Exchange buffer of one rank and one direction (forward or backward channel), written by the
 // other ranks with peer stores:
@@ -71,8 +82,8 @@ __host__ __device__ constexpr int lb_stage_bytes(int nch, int kind) {
 // be refilled as soon as its tile is in registers; the fused backward writes its two results over
 // the stage's inputs (a staging area would cost it two warps per CTA).
 __host__ __device__ constexpr int lb_staging_bytes(int nch, int kind) { return kind == K_BWD ? 0 : 32 * nch * 16; }
-// Two resident segments of `nt` tiles per warp, the staging tile, the mbarriers, and 16 bytes per
-// stage and lane of prefix maps.
+// Per worker: its `nt` tiles of two resident segments, the staging tile, the mbarriers, and 16
+// bytes per stage and lane of prefix maps.
 __host__ __device__ constexpr int lb_warp_smem(int nch, int nt, int kind) {
     return 2 * nt * lb_stage_bytes(nch, kind) + lb_staging_bytes(nch, kind) + 128 + 2 * nt * 32 * 16;
 }
@@ -239,24 +250,71 @@ __device__ __forceinline__ bool compose_three(const unsigned char *const base[3]
     return all;
 }
 
-// What a warp keeps about an item between its aggregate pass and its scan pass.
+// Bounded wait on an mbarrier of the team; ends early when a warp of the CTA has raised the
+// abort flag (after a wait of its own has expired).
+__device__ __forceinline__ bool team_wait(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag) {
+    for (uint32_t i = 0; i < LB_TEAM_POLLS; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(ok)
+            : "r"(smem_u32(bar)), "r"(parity), "r"(1000u)
+            : "memory");
+        if (ok) return true;
+        if ((i & 7u) == 7u && *abort_flag) return false;
+    }
+    return false;
+}
+
+// An affine pair in the team's shared memory (16 bytes per slot).
+__device__ __forceinline__ void store_part(unsigned char *p, float A, float B) {
+    volatile float *q = reinterpret_cast<volatile float *>(p);
+    q[0] = A;
+    q[1] = B;
+}
+__device__ __forceinline__ void store_part(unsigned char *p, float2 A, float2 B) {
+    volatile float *q = reinterpret_cast<volatile float *>(p);
+    q[0] = A.x;
+    q[1] = A.y;
+    q[2] = B.x;
+    q[3] = B.y;
+}
+__device__ __forceinline__ void load_part(const unsigned char *p, float &A, float &B) {
+    const volatile float *q = reinterpret_cast<const volatile float *>(p);
+    A = q[0];
+    B = q[1];
+}
+__device__ __forceinline__ void load_part(const unsigned char *p, float2 &A, float2 &B) {
+    const volatile float *q = reinterpret_cast<const volatile float *>(p);
+    A = make_float2(q[0], q[1]);
+    B = make_float2(q[2], q[3]);
+}
+
+// A segment, and what a worker keeps about its part of one.
+struct SegDesc {
+    int64_t row;       // row of the segment
+    int64_t pos0;      // position of its first element inside the row
+    int64_t n;         // elements
+    int32_t s;         // segment index in processing order
+    int32_t nts;       // tiles
+    bool valid;
+};
 template <class V>
 struct PendingItem {
     ItemDesc d;
-    V segA, segB;          // the segment's aggregate
-    V end_gate;            // backward: gate of the step right after the segment
-    bool waits_ok;
+    V end_gate;            // backward: gate of the step right after the part
 };
+constexpr uint32_t LB_NO_ITEM = 0xffffffffu;
 
 // KIND: K_SCAN (REVERSE selects the direction) or K_BWD.  Bulk loader, one segment per item.
-//
-// A warp holds TWO segments in shared memory (2 * NT stages) and works on them in the order
-//     aggregate(k+1), look-back(k), scan(k), aggregate(k+2), look-back(k+1), scan(k+1), ...
-// so the look-back of an item starts a whole aggregate pass after the item's own aggregate was
-// published: the aggregates it reads, all of items drawn earlier, are normally there already.
-// The number of item k+2 is drawn after look-back(k); from that draw to the publication of the
-// item's aggregate the warp waits for nothing but memory, so a drawn item is never held back
-// by its owner waiting in a look-back (such waits would chain up across warps).
+// The CTA's last warp is the bookkeeper, the others are workers.  The CTA's segments are
+// numbered k = 0, 1, 2, ... by all its warps alike; segment k uses the shared-memory buffers
+// k & 1 (parts, incoming states) and the ticket slot k & 3, and the phases of their mbarriers
+// follow from k.
 template <class TR, int NCH, int KIND, bool REVERSE>
 __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, const ShardParams sp) {
     using V = typename TR::V;
@@ -272,21 +330,33 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
     constexpr int STAGE_BYTES = lb_stage_bytes(NCH, KIND);
     constexpr bool PACKED = sizeof(V) == 4 && (K % 2 == 0);
     constexpr int H = K / 2;
-    const int NT = p.stages;                                  // tiles per segment; 2 * NT stages per warp
+    const int NT = p.stages;                                  // tiles per worker and segment; 2 * NT stages per worker
     const int WARP_SMEM = lb_warp_smem(NCH, NT, KIND);
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31;
     const int wib = threadIdx.x >> 5;
     const int wpc = blockDim.x >> 5;
-    unsigned char *wsm = smem_raw + static_cast<size_t>(wib) * WARP_SMEM;
+    const int G = wpc - 1;                                    // workers
+    const bool keeper = wib == G;
+    unsigned char *wsm = smem_raw + static_cast<size_t>(wib) * WARP_SMEM;      // (workers only)
     constexpr bool STAGED = !BACK;                            // results leave through a staging tile
     constexpr int STAGING_BYTES = lb_staging_bytes(NCH, KIND);
     unsigned char *staging = wsm + 2 * NT * STAGE_BYTES;
     uint64_t *bars = reinterpret_cast<uint64_t *>(wsm + 2 * NT * STAGE_BYTES + STAGING_BYTES);
-    // per stage and lane: the affine map from the segment's start to the lane's first element and,
+    // per stage and lane: the affine map from the part's start to the lane's first element and,
     // for the real types, the map over the first half of the lane's elements (4 floats in all)
     float4 *lane_prefix = reinterpret_cast<float4 *>(wsm + 2 * NT * STAGE_BYTES + STAGING_BYTES + 128);
+    // the team's memory
+    unsigned char *tsm = smem_raw + static_cast<size_t>(G) * WARP_SMEM;
+    unsigned char *parts = tsm;                                              // [2][16] pairs: the workers' aggregates
+    unsigned char *xin = tsm + 512;                                          // [2][16] values: the states entering the parts
+    volatile uint32_t *tickets = reinterpret_cast<volatile uint32_t *>(tsm + 768);   // [4] item numbers
+    uint64_t *pub = reinterpret_cast<uint64_t *>(tsm + 832);                 // [2] the segment's aggregate is published
+    uint64_t *xr = pub + 2;                                                  // [2] the incoming states are there
+    uint64_t *dr = pub + 4;                                                  // [4] the ticket is there
+    uint32_t *cnt = reinterpret_cast<uint32_t *>(tsm + 896);                 // [2] workers that have posted their part
+    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(tsm + 904);
 
     const int64_t W = static_cast<int64_t>(gridDim.x) * wpc;
     const int64_t T = p.T;
@@ -314,6 +384,19 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
     const uint32_t parity_slot = sp.call & 1u;
     unsigned char *xl = sharded ? sp.xchg[sp.rank] : nullptr;
     uint32_t status_bits = 0;
+
+    if (lane == 0) {
+        if (keeper) {
+            for (int s = 0; s < 8; ++s) mbar_init(&pub[s], 1);       // pub[2], xr[2], dr[4]
+            cnt[0] = 0;
+            cnt[1] = 0;
+            *abort_flag = 0;
+        } else {
+            for (int s = 0; s < 2 * NT; ++s) mbar_init(&bars[s], 1);
+        }
+        mbar_init_fence();
+    }
+    __syncthreads();
 
     // backward: the first gate of every row of this slice is the gate halo of the rank before
     if (BACK && sharded && sp.rank > 0) {
@@ -343,130 +426,61 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
         }
     }
 
-    // ---- items
-    auto draw = [&]() -> uint32_t {
-        uint32_t t = 0;
-        if (lane == 0) t = atomicAdd(p.ctrl + CTRL_TICKET, 1u);
-        return t;
+    // ---- segments and parts
+    auto describe_seg = [&](uint32_t q) -> SegDesc {
+        SegDesc g;
+        g.valid = q < static_cast<uint32_t>(p.items);
+        g.row = 0; g.pos0 = 0; g.n = 0; g.s = 0; g.nts = 0;
+        if (!g.valid) return g;
+        if (sharded) {
+            // row-major: a row's slice is finished, and its aggregate on its way to the next rank,
+            // as early as possible
+            const uint32_t ss = static_cast<uint32_t>(S);
+            const uint32_t row = q / ss;
+            g.row = row;
+            g.s = static_cast<int32_t>(q - row * ss);
+        } else {
+            // segment-major: the segment before this one in its row was drawn `rows` tickets ago, so
+            // its aggregate (and those of all earlier ones) is out when this one's look-back asks
+            const uint32_t rr = static_cast<uint32_t>(p.rows);
+            const uint32_t sq = q / rr;
+            g.s = static_cast<int32_t>(sq);
+            g.row = q - sq * rr;
+        }
+        const int64_t from_start = REV ? S - 1 - g.s : g.s;      // segments are aligned to the row start
+        g.pos0 = from_start * L;
+        const int64_t left = T - g.pos0;
+        g.n = left < L ? left : L;
+        g.nts = static_cast<int32_t>((g.n + TE - 1) / TE);
+        return g;
     };
-    auto resolve = [&](uint32_t raw) -> int64_t { return __shfl_sync(0xffffffffu, raw, 0); };
-    auto describe = [&](int64_t q) -> ItemDesc {
+    // worker `g` takes the tiles g*NT, ..., g*NT + NT - 1 of the segment in processing order
+    auto part_of = [&](const SegDesc &sg, int g) -> ItemDesc {
         ItemDesc d;
-        d.valid = q < p.items;
-        d.e_begin = 0; d.row0 = 0; d.pos0 = 0; d.s_log = 0; d.n = 0; d.nt = 0;
-        if (!d.valid) return d;
-        const uint32_t qq = static_cast<uint32_t>(q), ss = static_cast<uint32_t>(S);
-        const uint32_t row = qq / ss;
-        d.row0 = row;
-        d.s_log = static_cast<int32_t>(qq - row * ss);
-        const int64_t from_start = REV ? S - 1 - d.s_log : d.s_log;      // segments are aligned to the row start
-        d.pos0 = from_start * L;
-        d.e_begin = d.row0 * T + d.pos0;
-        const int64_t left = T - d.pos0;
-        d.n = left < L ? left : L;
-        d.nt = static_cast<int32_t>((d.n + TE - 1) / TE);
+        d.valid = sg.valid;
+        d.row0 = sg.row;
+        d.s_log = sg.s;
+        d.pos0 = sg.pos0;
+        d.e_begin = sg.row * T + sg.pos0;
+        d.n = 0;
+        d.nt = 0;
+        if (!sg.valid) return d;
+        int c = sg.nts - g * NT;
+        c = c < 0 ? 0 : (c > NT ? NT : c);
+        if (c == 0) return d;
+        const int m_lo = REV ? sg.nts - g * NT - c : g * NT;     // first tile of the part in memory order
+        d.nt = c;
+        d.pos0 = sg.pos0 + static_cast<int64_t>(m_lo) * TE;
+        d.e_begin = sg.row * T + d.pos0;
+        const int64_t left = sg.n - static_cast<int64_t>(m_lo) * TE;
+        const int64_t full = static_cast<int64_t>(c) * TE;
+        d.n = left < full ? left : full;
         return d;
     };
     auto tile_of_step = [&](const ItemDesc &d, int i) -> int { return REV ? d.nt - 1 - i : i; };
     auto tile_valid = [&](const ItemDesc &d, int t) -> int {
         const int64_t left = d.n - static_cast<int64_t>(t) * TE;
         return left < TE ? static_cast<int>(left) : TE;
-    };
-    // step i of an item in slot `slot` lives in stage slot * NT + i.  Lane 0 arms the stage's
-    // mbarrier, then one lane per stream issues its copy (and one more the 16 bytes of saved
-    // states just below the tile).
-    auto issue = [&](const ItemDesc &d, int slot, int i) {
-        const int t = tile_of_step(d, i);
-        const int stage = slot * NT + i;
-        const uint32_t bytes = static_cast<uint32_t>(tile_valid(d, t)) * TR::ESIZE;
-        const int64_t goff = (d.e_begin + static_cast<int64_t>(t) * TE) * TR::ESIZE;
-        const bool halo = BACK && goff > 0;
-        unsigned char *dst = wsm + stage * STAGE_BYTES;
-        if (lane == 0) mbar_expect_tx(&bars[stage], bytes * NIN + (halo ? 16u : 0u));
-        __syncwarp();
-        if (lane < NIN) bulk_g2s(dst + lane * TB, gbase[lane] + goff, bytes, &bars[stage]);
-        if (lane == NIN && halo) bulk_g2s(dst + NIN * TB, gbase[2] + goff - 16, 16, &bars[stage]);
-    };
-
-    if (lane == 0) {
-        for (int s = 0; s < 2 * NT; ++s) mbar_init(&bars[s], 1);
-        mbar_init_fence();
-    }
-    __syncwarp();
-
-    uint32_t phase_bits = 0;       // bit s: parity to wait for on stage s
-    bool failed = false;
-
-    // backward: the gate of the step right after a segment, loaded when the item is drawn (the
-    // load's latency hides behind the scan pass that runs meanwhile)
-    auto end_gate_raw = [&](const ItemDesc &d) -> Raw {
-        Raw r = 0;
-        if (BACK && d.valid && d.pos0 + d.n < T) r = TR::load_raw(p.in0, d.e_begin + d.n);
-        return r;
-    };
-    // ... and decoded, or taken from the halos, when the item's aggregate pass starts
-    auto end_gate = [&](const ItemDesc &d, Raw raw, bool &ok) -> V {
-        V g = vone(V());
-        if (!BACK) return g;
-        if (d.pos0 + d.n < T) return TR::decode(raw);
-        if (sharded && sp.rank + 1 < sp.world) {
-            // first gate of the next rank's slice, stored into this rank's exchange buffer
-            const unsigned char *slot = xl + xchg_halo_offset() + (static_cast<uint64_t>(parity_slot) * p.rows + d.row0) * 16;
-            bool got = false;
-            for (uint32_t poll = 0; poll < LB_WAIT_POLLS && !got; ++poll) {
-                if constexpr (sizeof(V) == 4) {
-                    got = get_word<true>(slot, sp.call, g);
-                } else {
-                    const bool a = get_word<true>(slot, sp.call, g.x);
-                    const bool b = get_word<true>(slot + 8, sp.call, g.y);
-                    got = a && b;
-                }
-                if (!got) __nanosleep(100);
-            }
-            if (!got) {
-                ok = false;
-                g = vone(V());
-            }
-            return g;
-        }
-        if (hgate) g = hgate[d.row0];
-        return g;
-    };
-
-    // One tile from its stage into registers, ready for the two passes: a[] = the gates that
-    // multiply the state entering each element (shifted by one step for the backward), b[] = the
-    // additive terms; beyond the row's end the identity.
-    auto fetch = [&](const PendingItem<V> &it, int slot, int i, V *a, V *b, V &next_gate, int &nvalid) {
-        const int t = tile_of_step(it.d, i);
-        nvalid = tile_valid(it.d, t);
-        const unsigned char *stg = wsm + (slot * NT + i) * STAGE_BYTES;
-#pragma unroll
-        for (int c = 0; c < NCH; ++c) {
-            TR::unpack(*reinterpret_cast<const uint4 *>(stg + 0 * TB + (lane * NCH + c) * 16), &a[c * EPC]);
-            TR::unpack(*reinterpret_cast<const uint4 *>(stg + 1 * TB + (lane * NCH + c) * 16), &b[c * EPC]);
-        }
-        if (BACK) {
-            const V g0 = a[0];
-            V up = shfl_down(g0, 1);
-            if (lane == 31) up = next_gate;
-#pragma unroll
-            for (int j = 0; j < K - 1; ++j) a[j] = vconj(a[j + 1]);
-            a[K - 1] = vconj(up);
-            next_gate = shfl_idx(g0, 0);
-        }
-        if (nvalid < TE) {
-            const int jv = nvalid - lane * K;
-            const V gate_end = BACK ? vconj(it.end_gate) : vone(V());
-#pragma unroll
-            for (int j = 0; j < K; ++j) {
-                if (j >= jv) {
-                    a[j] = vone(V());
-                    b[j] = vzero(V());
-                } else if (BACK && j + 1 >= jv) {
-                    a[j] = gate_end;
-                }
-            }
-        }
     };
 
     // The map from the slice's start to the start of segment `s` of a row, from the records of
@@ -503,354 +517,588 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
         return ok;
     };
 
-    // ---------------- aggregate pass of the item in `slot`: lane prefixes, the segment's
-    // aggregate, publication
-    auto aggregate = [&](PendingItem<V> &it, int slot, Raw gate_raw) {
-        it.waits_ok = true;
-        it.end_gate = end_gate(it.d, gate_raw, it.waits_ok);
-        V segA = vone(V()), segB = vzero(V());      // map from the segment's start to the current tile's start
-        V next_gate = it.end_gate;
-        for (int i = 0; i < it.d.nt; ++i) {
-            const int stage = slot * NT + i;
-            bool ok = mbar_wait_bounded_suspended(&bars[stage], (phase_bits >> stage) & 1u, LOAD_WAIT_POLLS, 2000);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) {
-                failed = true;
-                status_bits |= STATUS_LOAD_TIMEOUT;
-                return;
-            }
-            phase_bits ^= 1u << stage;
-            V a[K], b[K];
-            int nvalid;
-            fetch(it, slot, i, a, b, next_gate, nvalid);
-            V A, B;
-            V A0h = vone(V()), B0h = vzero(V());     // real types: the map over the first half of the lane's elements
-            if constexpr (PACKED) {
-                auto J = [](int q) { return REV ? K - 1 - q : q; };
-                float2 Av = make_float2(a[J(0)], a[J(H)]);
-                float2 Bv = make_float2(b[J(0)], b[J(H)]);
-#pragma unroll
-                for (int q = 1; q < H; ++q) {
-                    const float2 av = make_float2(a[J(q)], a[J(H + q)]);
-                    const float2 bv = make_float2(b[J(q)], b[J(H + q)]);
-                    Bv = __ffma2_rn(av, Bv, bv);
-                    Av = __fmul2_rn(Av, av);
-                }
-                A0h = Av.x;
-                B0h = Bv.x;
-                A = Av.x * Av.y;
-                B = fmaf(Av.y, Bv.x, Bv.y);
-            } else {
-                constexpr int JF = REV ? K - 1 : 0;
-                A = a[JF];
-                B = b[JF];
-#pragma unroll
-                for (int q = 1; q < K; ++q) {
-                    const int j = REV ? K - 1 - q : q;
-                    B = vfma(a[j], B, b[j]);
-                    A = vmul(A, a[j]);
-                }
-            }
-            // inclusive Kogge-Stone over the lanes in processing order; the map that enters the
-            // tile (segA, segB) goes in through the first lane
-            const int ll = REV ? 31 - lane : lane;
-            if (ll == 0) {
-                B = vfma(A, segB, B);
-                A = vmul(A, segA);
-            }
-#pragma unroll
-            for (int d = 1; d < 32; d <<= 1) {
-                const V Ap = REV ? shfl_down(A, d) : shfl_up(A, d);
-                const V Bp = REV ? shfl_down(B, d) : shfl_up(B, d);
-                if (ll >= d) {
-                    B = vfma(A, Bp, B);
-                    A = vmul(A, Ap);
-                }
-            }
-            // map from the segment's start to this lane's first element
-            V pA = REV ? shfl_down(A, 1) : shfl_up(A, 1);
-            V pB = REV ? shfl_down(B, 1) : shfl_up(B, 1);
-            if (ll == 0) {
-                pA = segA;
-                pB = segB;
-            }
-            if constexpr (sizeof(V) == 4) {
-                lane_prefix[stage * 32 + lane] = make_float4(pA, pB, A0h, B0h);
-            } else {
-                lane_prefix[stage * 32 + lane] = make_float4(pA.x, pA.y, pB.x, pB.y);
-            }
-            segA = shfl_idx(A, REV ? 0 : 31);
-            segB = shfl_idx(B, REV ? 0 : 31);
-        }
-        it.segA = segA;
-        it.segB = segB;
-        unsigned char *row_rec = records + static_cast<uint64_t>(it.d.row0) * per_row * LB_RECORD_BYTES;
-        const int s = it.d.s_log;
-        if (lane == 0) put_pair<false>(row_rec + static_cast<uint64_t>(s) * LB_RECORD_BYTES, segA, segB, tag);
-        // Closing duties.  The last segment of a block publishes the block's aggregate (this
-        // segment after the 31 before it), the last block of a super-block the super-block's.
-        // They wait only for aggregates of items drawn earlier, which nobody holds back, and the
-        // warp holds no unpublished item while it waits; the records are there long before the
-        // look-backs that read them.  Only full blocks and super-blocks are ever read.
-        if ((s & 31) == 31) {
-            V A0, B0;
-            bool ok = compose_window<V, false>(row_rec + static_cast<uint64_t>(s - 31) * LB_RECORD_BYTES, LB_RECORD_BYTES, 31,
-                                               tag, lane, A0, B0);
-            const V Ab = vmul(segA, A0), Bb = vfma(segA, B0, segB);
-            if (ok && lane == 0) put_pair<false>(row_rec + (static_cast<uint64_t>(S) + (s >> 5)) * LB_RECORD_BYTES, Ab, Bb, tag);
-            if (ok && ((s >> 5) & 31) == 31) {
-                V A1, B1;
-                ok = compose_window<V, false>(row_rec + (static_cast<uint64_t>(S) + (s >> 5) - 31) * LB_RECORD_BYTES,
-                                              LB_RECORD_BYTES, 31, tag, lane, A1, B1);
-                if (ok && lane == 0)
-                    put_pair<false>(row_rec + (static_cast<uint64_t>(S) + S1 + (s >> 10)) * LB_RECORD_BYTES, vmul(Ab, A1),
-                                    vfma(Ab, B1, Bb), tag);
-            }
-            if (!ok) it.waits_ok = false;
-        }
-        // The slice of the row ends with this segment: the slice's aggregate goes to the ranks that
-        // come later in processing order, as early as possible (they all wait for it).
-        if (sharded && s == S - 1 && n_after > 0 && it.waits_ok) {
-            V preA, preB;
-            bool ok = local_prefix(row_rec, s, preA, preB, nullptr);
-            const V Ps = vmul(segA, preA), Ss = vfma(segA, preB, segB);
-            if (ok && lane < n_after) {
-                const int target = REV ? sp.rank - 1 - lane : sp.rank + 1 + lane;
-                // the slot was last used two calls ago: the receiver must have finished that call
-                ok = sp.call <= 2;
-                for (uint32_t poll = 0; poll < LB_WAIT_POLLS && !ok; ++poll) {
-                    ok = static_cast<int32_t>(static_cast<uint32_t>(ld_relaxed_sys_u64(xl + 8 * target)) - (sp.call - 2)) >= 0;
-                    if (!ok) __nanosleep(200);
-                }
-                if (ok) {
-                    unsigned char *slot_rec = sp.xchg[target] + xchg_carry_offset(p.rows) +
-                                              ((static_cast<uint64_t>(parity_slot) * sp.world + sp.rank) * p.rows + it.d.row0) * LB_RECORD_BYTES;
-                    put_pair<true>(slot_rec, Ps, Ss, sp.call);
-                }
-            }
-            if (!__all_sync(0xffffffffu, ok)) it.waits_ok = false;
-        }
-    };
-
-    PendingItem<V> cur, nxt;
-    cur.d = describe(resolve(draw()));
-    cur.segA = vone(V()); cur.segB = vzero(V()); cur.end_gate = vone(V()); cur.waits_ok = true;
-    nxt = cur;
-    int cur_slot = 0;
-    if (cur.d.valid) {
-        for (int i = 0; i < cur.d.nt; ++i) issue(cur.d, 0, i);
-        const Raw g_raw = end_gate_raw(cur.d);
-        nxt.d = describe(resolve(draw()));
-        if (nxt.d.valid) {
-            for (int i = 0; i < nxt.d.nt; ++i) issue(nxt.d, 1, i);
-        }
-        aggregate(cur, 0, g_raw);
-    }
-    Raw nxt_gate_raw = end_gate_raw(nxt.d);
-
-    while (cur.d.valid && !failed) {
-        const int nxt_slot = cur_slot ^ 1;
-        const int64_t row = cur.d.row0;
-        const int s = cur.d.s_log;
-        unsigned char *row_rec = records + static_cast<uint64_t>(row) * per_row * LB_RECORD_BYTES;
-        // the records this item's look-back will read: segments of its block, blocks of its
-        // super-block, super-blocks before it
-        const int n0 = s & 31, n1 = (s >> 5) & 31, n2 = s >> 10;
-        const unsigned char *lb_base[3] = {
+    // the records a look-back of segment `s` reads first, loaded ahead of time (real types)
+    auto load_ahead = [&](unsigned char *row_rec, int s) -> RecordWords {
+        const int n2 = s >> 10;
+        const unsigned char *base[3] = {
             row_rec + (static_cast<uint64_t>(s >> 5) << 5) * LB_RECORD_BYTES,
             row_rec + (static_cast<uint64_t>(S) + (static_cast<uint64_t>(s >> 10) << 5)) * LB_RECORD_BYTES,
             row_rec + (static_cast<uint64_t>(S) + S1) * LB_RECORD_BYTES};
-        const int lb_n[3] = {n0, n1, n2 < 32 ? n2 : 32};
-        // real types: load them now, use them after the aggregate pass below (they were published
-        // an iteration ago, so this hides the round trip; what is missing is polled for later)
-        RecordWords ahead;
-        if constexpr (sizeof(V) == 4) ahead = load_record_words(lb_base, lb_n, lane);
+        const int n[3] = {s & 31, (s >> 5) & 31, n2 < 32 ? n2 : 32};
+        return load_record_words(base, n, lane);
+    };
 
-        // ---------------- aggregate pass of the item after this one
-        if (nxt.d.valid) aggregate(nxt, nxt_slot, nxt_gate_raw);
-        if (failed) break;
-
-        // ---------------- look back for this item
-        // A wait that expires ends this warp's work: the status bit is set and the warp leaves
-        // (none of its copies is in flight at this point: both resident segments have been
-        // aggregated).  Every warp gives up at its first expired wait, so a launch whose partner
-        // never shows up ends after about one bound, not one bound per item.
-        bool lb_ok = cur.waits_ok && nxt.waits_ok;
-        V preA = vone(V()), preB = vzero(V());         // map from the slice's start to the segment's start
-        if (lb_ok) lb_ok = local_prefix(row_rec, s, preA, preB, sizeof(V) == 4 ? &ahead : nullptr);
-        // state entering the slice: the caller's, or the fold of the earlier ranks' aggregates
-        V x_slice = cin ? cin[row] : vzero(V());
-        if (n_before > 0 && lb_ok) {
-            // lane i reads the aggregate of the i-th rank in processing order
-            const int first = REV ? sp.world - 1 : 0;
-            const int64_t step = (REV ? -1 : 1) * static_cast<int64_t>(p.rows) * LB_RECORD_BYTES;
-            const unsigned char *base = xl + xchg_carry_offset(p.rows) +
-                                        ((static_cast<uint64_t>(parity_slot) * sp.world + first) * p.rows + row) * LB_RECORD_BYTES;
-            V Ar, Br;
-            lb_ok = compose_window<V, true>(base, step, n_before, sp.call, lane, Ar, Br);
-            x_slice = vfma(Ar, x_slice, Br);
+    bool failed = false;
+    // A wait that expires ends this warp's work: the status bit is set, the abort flag tells the
+    // other warps of the CTA, whose waits on this warp then end at once.  Every warp gives up at
+    // its first expired wait, so a launch whose partner rank never shows up ends after about one
+    // bound, not one bound per item.
+    auto give_up = [&](uint32_t bit) {
+        status_bits |= bit;
+        failed = true;
+        if (lane == 0) *abort_flag = 1;
+    };
+    // the parts of buffer `b`, composed in worker order: inclusive in every lane (identity
+    // beyond the last worker, so lane 31 holds the whole segment)
+    auto compose_parts = [&](int b, V &a, V &bb) {
+        a = vone(V());
+        bb = vzero(V());
+        if (lane < G) load_part(parts + (b * 16 + lane) * 16, a, bb);
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const V Ap = shfl_up(a, d), Bp = shfl_up(bb, d);
+            if (lane >= d) {
+                bb = vfma(a, Bp, bb);
+                a = vmul(a, Ap);
+            }
         }
-        // forward: the state entering the slice is what the backward needs below its first step
-        if (!REV && s == 0 && sp.carry_save && lane == 0) static_cast<V *>(sp.carry_save)[row] = x_slice;
-        if (!lb_ok) {
-            status_bits |= STATUS_LOOKBACK_TIMEOUT;
-            failed = true;
-            break;
-        }
-        const V x_in = vfma(preA, x_slice, preB);
+    };
 
-        // ---------------- scan pass from shared memory; stages are refilled as they drain
-        // The number of the item after the next is drawn only now, after the look-back: from this
-        // draw to the publication of that item's aggregate the warp waits for nothing but memory,
-        // so a drawn item is never held back by its owner waiting in a look-back.  (Drawn before
-        // the look-back, such waits chained up across warps and cost 40 % of the throughput.)
-        const uint32_t raw_after = draw();
-        PendingItem<V> aft = cur;
-        aft.d.valid = false;
-        Raw aft_gate_raw = 0;
-        bool aft_known = false;
-        auto learn_after = [&]() {
-            if (!aft_known) {
-                aft.d = describe(nxt.d.valid ? resolve(raw_after) : p.items);
-                aft_gate_raw = end_gate_raw(aft.d);
-                aft_known = true;
+    if (!keeper) {
+        // =====================================================================================
+        // Worker.
+        const int g = wib;
+        uint32_t phase_bits = 0;       // bit s: parity to wait for on stage s
+
+        // step i of a part in slot `slot` lives in stage slot * NT + i.  Lane 0 arms the stage's
+        // mbarrier, then one lane per stream issues its copy (and one more the 16 bytes of saved
+        // states just below the tile).
+        auto issue = [&](const ItemDesc &d, int slot, int i) {
+            const int t = tile_of_step(d, i);
+            const int stage = slot * NT + i;
+            const uint32_t bytes = static_cast<uint32_t>(tile_valid(d, t)) * TR::ESIZE;
+            const int64_t goff = (d.e_begin + static_cast<int64_t>(t) * TE) * TR::ESIZE;
+            const bool halo = BACK && goff > 0;
+            unsigned char *dst = wsm + stage * STAGE_BYTES;
+            if (lane == 0) mbar_expect_tx(&bars[stage], bytes * NIN + (halo ? 16u : 0u));
+            __syncwarp();
+            if (lane < NIN) bulk_g2s(dst + lane * TB, gbase[lane] + goff, bytes, &bars[stage]);
+            if (lane == NIN && halo) bulk_g2s(dst + NIN * TB, gbase[2] + goff - 16, 16, &bars[stage]);
+        };
+        // the ticket of the CTA's k-th segment, once the bookkeeper has posted it
+        auto seg_ticket = [&](uint32_t k) -> uint32_t {
+            if (!__all_sync(0xffffffffu, team_wait(&dr[k & 3u], (k >> 2) & 1u, abort_flag))) {
+                if (!*abort_flag) give_up(STATUS_LOOKBACK_TIMEOUT);
+                failed = true;
+                return LB_NO_ITEM;
+            }
+            return tickets[k & 3u];
+        };
+        // backward: the gate of the step right after a part, loaded when the part is known (the
+        // load's latency hides behind the scan pass that runs meanwhile)
+        auto end_gate_raw = [&](const ItemDesc &d) -> Raw {
+            Raw r = 0;
+            if (BACK && d.valid && d.nt > 0 && d.pos0 + d.n < T) r = TR::load_raw(p.in0, d.e_begin + d.n);
+            return r;
+        };
+        // ... and decoded, or taken from the halos, when the part's aggregate pass starts
+        auto end_gate = [&](const ItemDesc &d, Raw raw, bool &ok) -> V {
+            V gt = vone(V());
+            if (!BACK || d.nt == 0) return gt;
+            if (d.pos0 + d.n < T) return TR::decode(raw);
+            if (sharded && sp.rank + 1 < sp.world) {
+                // first gate of the next rank's slice, stored into this rank's exchange buffer
+                const unsigned char *slot = xl + xchg_halo_offset() + (static_cast<uint64_t>(parity_slot) * p.rows + d.row0) * 16;
+                bool got = false;
+                for (uint32_t poll = 0; poll < LB_WAIT_POLLS && !got; ++poll) {
+                    if constexpr (sizeof(V) == 4) {
+                        got = get_word<true>(slot, sp.call, gt);
+                    } else {
+                        const bool a = get_word<true>(slot, sp.call, gt.x);
+                        const bool b = get_word<true>(slot + 8, sp.call, gt.y);
+                        got = a && b;
+                    }
+                    if (!got) __nanosleep(100);
+                }
+                if (!got) {
+                    ok = false;
+                    gt = vone(V());
+                }
+                return gt;
+            }
+            if (hgate) gt = hgate[d.row0];
+            return gt;
+        };
+
+        // One tile from its stage into registers, ready for the two passes: a[] = the gates that
+        // multiply the state entering each element (shifted by one step for the backward), b[] = the
+        // additive terms; beyond the row's end the identity.
+        auto fetch = [&](const PendingItem<V> &it, int slot, int i, V *a, V *b, V &next_gate, int &nvalid) {
+            const int t = tile_of_step(it.d, i);
+            nvalid = tile_valid(it.d, t);
+            const unsigned char *stg = wsm + (slot * NT + i) * STAGE_BYTES;
+#pragma unroll
+            for (int c = 0; c < NCH; ++c) {
+                TR::unpack(*reinterpret_cast<const uint4 *>(stg + 0 * TB + (lane * NCH + c) * 16), &a[c * EPC]);
+                TR::unpack(*reinterpret_cast<const uint4 *>(stg + 1 * TB + (lane * NCH + c) * 16), &b[c * EPC]);
+            }
+            if (BACK) {
+                const V g0 = a[0];
+                V up = shfl_down(g0, 1);
+                if (lane == 31) up = next_gate;
+#pragma unroll
+                for (int j = 0; j < K - 1; ++j) a[j] = vconj(a[j + 1]);
+                a[K - 1] = vconj(up);
+                next_gate = shfl_idx(g0, 0);
+            }
+            if (nvalid < TE) {
+                const int jv = nvalid - lane * K;
+                const V gate_end = BACK ? vconj(it.end_gate) : vone(V());
+#pragma unroll
+                for (int j = 0; j < K; ++j) {
+                    if (j >= jv) {
+                        a[j] = vone(V());
+                        b[j] = vzero(V());
+                    } else if (BACK && j + 1 >= jv) {
+                        a[j] = gate_end;
+                    }
+                }
             }
         };
-        {
-            V next_gate = cur.end_gate;
-            const int nt = cur.d.nt;
-            for (int i = 0; i < nt; ++i) {
+
+        // ---------------- aggregate pass of this worker's part of segment `kk` (in `slot`): lane
+        // prefixes, the part's aggregate into the team's memory; the worker that posts last
+        // publishes the segment
+        auto aggregate = [&](PendingItem<V> &it, const SegDesc &sg, int slot, uint32_t kk, Raw gate_raw) {
+            bool waits_ok = true;
+            it.end_gate = end_gate(it.d, gate_raw, waits_ok);
+            V segA = vone(V()), segB = vzero(V());      // map from the part's start to the current tile's start
+            V next_gate = it.end_gate;
+            for (int i = 0; i < it.d.nt; ++i) {
+                const int stage = slot * NT + i;
+                bool ok = mbar_wait_bounded_suspended(&bars[stage], (phase_bits >> stage) & 1u, LOAD_WAIT_POLLS, 2000);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) {
+                    give_up(STATUS_LOAD_TIMEOUT);
+                    return;
+                }
+                phase_bits ^= 1u << stage;
                 V a[K], b[K];
                 int nvalid;
-                fetch(cur, cur_slot, i, a, b, next_gate, nvalid);
-                const int t = tile_of_step(cur.d, i);
-                const int64_t toff = static_cast<int64_t>(t) * TE;
-                const int stage = cur_slot * NT + i;
-                unsigned char *stg = wsm + stage * STAGE_BYTES;
-                V xp[BACK ? K : 1];
-                V x_below = vzero(V());
-                if (BACK) {
-#pragma unroll
-                    for (int c = 0; c < NCH; ++c)
-                        TR::unpack(*reinterpret_cast<const uint4 *>(stg + 2 * TB + (lane * NCH + c) * 16), &xp[c * EPC]);
-                    if (cur.d.pos0 + toff != 0) {
-                        V hv[EPC];
-                        TR::unpack(*reinterpret_cast<const uint4 *>(stg + NIN * TB), hv);
-                        x_below = hv[EPC - 1];
-                    } else if (hstate) {
-                        x_below = hstate[row];
-                    }
-                }
-                const float4 pf = lane_prefix[stage * 32 + lane];
-                if constexpr (STAGED) {
-                    // the tile is in registers: its stage can take the matching tile of the item
-                    // after the next (whose number arrives during the first tile; the first stage
-                    // is refilled together with the second)
-                    __syncwarp();
-                    fence_async_smem();
-                    if (i >= 1) {
-                        learn_after();
-                        if (i == 1 && aft.d.valid) issue(aft.d, cur_slot, 0);
-                        if (aft.d.valid && i < aft.d.nt) issue(aft.d, cur_slot, i);
-                    }
-                }
+                fetch(it, slot, i, a, b, next_gate, nvalid);
+                V A, B;
+                V A0h = vone(V()), B0h = vzero(V());     // real types: the map over the first half of the lane's elements
                 if constexpr (PACKED) {
                     auto J = [](int q) { return REV ? K - 1 - q : q; };
-                    const float x = fmaf(pf.x, x_in, pf.y);
-                    float2 Xv = make_float2(x, fmaf(pf.z, x, pf.w));       // states entering the two halves
+                    float2 Av = make_float2(a[J(0)], a[J(H)]);
+                    float2 Bv = make_float2(b[J(0)], b[J(H)]);
 #pragma unroll
-                    for (int q = 0; q < H; ++q) {
+                    for (int q = 1; q < H; ++q) {
                         const float2 av = make_float2(a[J(q)], a[J(H + q)]);
                         const float2 bv = make_float2(b[J(q)], b[J(H + q)]);
-                        Xv = __ffma2_rn(av, Xv, bv);
-                        b[J(q)] = Xv.x;
-                        b[J(H + q)] = Xv.y;
+                        Bv = __ffma2_rn(av, Bv, bv);
+                        Av = __fmul2_rn(Av, av);
                     }
+                    A0h = Av.x;
+                    B0h = Bv.x;
+                    A = Av.x * Av.y;
+                    B = fmaf(Av.y, Bv.x, Bv.y);
                 } else {
-                    V x;
-                    if constexpr (sizeof(V) == 4) {
-                        x = vfma(pf.x, x_in, pf.y);
-                    } else {
-                        x = vfma(make_float2(pf.x, pf.y), x_in, make_float2(pf.z, pf.w));
-                    }
+                    constexpr int JF = REV ? K - 1 : 0;
+                    A = a[JF];
+                    B = b[JF];
 #pragma unroll
-                    for (int q = 0; q < K; ++q) {
+                    for (int q = 1; q < K; ++q) {
                         const int j = REV ? K - 1 - q : q;
-                        x = vfma(a[j], x, b[j]);
-                        b[j] = x;
+                        B = vfma(a[j], B, b[j]);
+                        A = vmul(A, a[j]);
                     }
                 }
-                if (BACK) {
-                    // d_gates[t] = conj(x[t-1]) * g[t]
-                    V dn = shfl_up(xp[K - 1], 1);
-                    if (lane == 0) dn = x_below;
-#pragma unroll
-                    for (int j = K - 1; j >= 1; --j) a[j] = vmul(vconj(xp[j - 1]), b[j]);
-                    a[0] = vmul(vconj(dn), b[0]);
+                // inclusive Kogge-Stone over the lanes in processing order; the map that enters the
+                // tile (segA, segB) goes in through the first lane
+                const int ll = REV ? 31 - lane : lane;
+                if (ll == 0) {
+                    B = vfma(A, segB, B);
+                    A = vmul(A, segA);
                 }
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+                    const V Ap = REV ? shfl_down(A, d) : shfl_up(A, d);
+                    const V Bp = REV ? shfl_down(B, d) : shfl_up(B, d);
+                    if (ll >= d) {
+                        B = vfma(A, Bp, B);
+                        A = vmul(A, Ap);
+                    }
+                }
+                // map from the part's start to this lane's first element
+                V pA = REV ? shfl_down(A, 1) : shfl_up(A, 1);
+                V pB = REV ? shfl_down(B, 1) : shfl_up(B, 1);
+                if (ll == 0) {
+                    pA = segA;
+                    pB = segB;
+                }
+                if constexpr (sizeof(V) == 4) {
+                    lane_prefix[stage * 32 + lane] = make_float4(pA, pB, A0h, B0h);
+                } else {
+                    lane_prefix[stage * 32 + lane] = make_float4(pA.x, pA.y, pB.x, pB.y);
+                }
+                segA = shfl_idx(A, REV ? 0 : 31);
+                segB = shfl_idx(B, REV ? 0 : 31);
+            }
+            // post the part; the worker that finds all others posted goes on for the segment
+            const int b = static_cast<int>(kk & 1u);
+            uint32_t posted = 0;
+            if (lane == 0) {
+                store_part(parts + (b * 16 + g) * 16, segA, segB);
+                __threadfence_block();
+                posted = atomicAdd(&cnt[b], 1u);
+            }
+            const bool last = __shfl_sync(0xffffffffu, posted, 0) == static_cast<uint32_t>(G - 1);
+            if (last) {
+                if (lane == 0) {
+                    cnt[b] = 0;
+                    __threadfence_block();
+                }
+                __syncwarp();
+                V ta, tb;
+                compose_parts(b, ta, tb);
+                const V totA = shfl_idx(ta, 31), totB = shfl_idx(tb, 31);
+                unsigned char *row_rec = records + static_cast<uint64_t>(sg.row) * per_row * LB_RECORD_BYTES;
+                const int s = sg.s;
+                if (lane == 0) {
+                    put_pair<false>(row_rec + static_cast<uint64_t>(s) * LB_RECORD_BYTES, totA, totB, tag);
+                    mbar_arrive(&pub[b]);
+                }
+                // Closing duties.  The last segment of a block publishes the block's aggregate (this
+                // segment after the 31 before it), the last block of a super-block the super-block's.
+                // They wait only for aggregates of segments drawn earlier, which nobody holds back; the
+                // records are there long before the look-backs that read them.  Only full blocks and
+                // super-blocks are ever read.
+                if ((s & 31) == 31) {
+                    V A0, B0;
+                    bool ok = compose_window<V, false>(row_rec + static_cast<uint64_t>(s - 31) * LB_RECORD_BYTES, LB_RECORD_BYTES, 31,
+                                                       tag, lane, A0, B0);
+                    const V Ab = vmul(totA, A0), Bb = vfma(totA, B0, totB);
+                    if (ok && lane == 0) put_pair<false>(row_rec + (static_cast<uint64_t>(S) + (s >> 5)) * LB_RECORD_BYTES, Ab, Bb, tag);
+                    if (ok && ((s >> 5) & 31) == 31) {
+                        V A1, B1;
+                        ok = compose_window<V, false>(row_rec + (static_cast<uint64_t>(S) + (s >> 5) - 31) * LB_RECORD_BYTES,
+                                                      LB_RECORD_BYTES, 31, tag, lane, A1, B1);
+                        if (ok && lane == 0)
+                            put_pair<false>(row_rec + (static_cast<uint64_t>(S) + S1 + (s >> 10)) * LB_RECORD_BYTES, vmul(Ab, A1),
+                                            vfma(Ab, B1, Bb), tag);
+                    }
+                    if (!ok) waits_ok = false;
+                }
+                // The slice of the row ends with this segment: the slice's aggregate goes to the ranks that
+                // come later in processing order, as early as possible (they all wait for it).
+                if (sharded && s == S - 1 && n_after > 0 && waits_ok) {
+                    V preA, preB;
+                    bool ok = local_prefix(row_rec, s, preA, preB, nullptr);
+                    const V Ps = vmul(totA, preA), Ss = vfma(totA, preB, totB);
+                    if (ok && lane < n_after) {
+                        const int target = REV ? sp.rank - 1 - lane : sp.rank + 1 + lane;
+                        // the slot was last used two calls ago: the receiver must have finished that call
+                        ok = sp.call <= 2;
+                        for (uint32_t poll = 0; poll < LB_WAIT_POLLS && !ok; ++poll) {
+                            ok = static_cast<int32_t>(static_cast<uint32_t>(ld_relaxed_sys_u64(xl + 8 * target)) - (sp.call - 2)) >= 0;
+                            if (!ok) __nanosleep(200);
+                        }
+                        if (ok) {
+                            unsigned char *slot_rec = sp.xchg[target] + xchg_carry_offset(p.rows) +
+                                                      ((static_cast<uint64_t>(parity_slot) * sp.world + sp.rank) * p.rows + sg.row) * LB_RECORD_BYTES;
+                            put_pair<true>(slot_rec, Ps, Ss, sp.call);
+                        }
+                    }
+                    if (!__all_sync(0xffffffffu, ok)) waits_ok = false;
+                }
+            }
+            if (!waits_ok) give_up(STATUS_LOOKBACK_TIMEOUT);
+        };
+
+        uint32_t k = 0;
+        SegDesc sc = describe_seg(seg_ticket(0));
+        SegDesc sn = sc;
+        sn.valid = false;
+        PendingItem<V> cur, nxt;
+        cur.d = part_of(sc, g);
+        cur.end_gate = vone(V());
+        nxt = cur;
+        nxt.d.valid = false;
+        nxt.d.nt = 0;
+        int cur_slot = 0;
+        Raw nxt_gate_raw = 0;
+        if (sc.valid && !failed) {
+            for (int i = 0; i < cur.d.nt; ++i) issue(cur.d, 0, i);
+            const Raw g_raw = end_gate_raw(cur.d);
+            sn = describe_seg(seg_ticket(1));
+            nxt.d = part_of(sn, g);
+            if (sn.valid) {
+                for (int i = 0; i < nxt.d.nt; ++i) issue(nxt.d, 1, i);
+            }
+            nxt_gate_raw = end_gate_raw(nxt.d);
+            if (!failed) aggregate(cur, sc, 0, 0, g_raw);
+        }
+
+        while (sc.valid && !failed) {
+            const int nxt_slot = cur_slot ^ 1;
+            const int64_t row = sc.row;
+
+            // ---------------- aggregate pass of the segment after this one
+            if (sn.valid) aggregate(nxt, sn, nxt_slot, k + 1, nxt_gate_raw);
+            if (failed) break;
+
+            // ---------------- the state entering this worker's part, from the bookkeeper
+            if (!__all_sync(0xffffffffu, team_wait(&xr[k & 1u], (k >> 1) & 1u, abort_flag))) {
+                if (!*abort_flag) give_up(STATUS_LOOKBACK_TIMEOUT);
+                break;
+            }
+            const V x_in = *reinterpret_cast<const V *>(xin + ((k & 1u) * 16 + g) * 8);
+            // the segment after the next: its tiles refill the stages as they drain.  Its ticket is
+            // drawn after this segment's look-back, so it is asked for only when the first stage
+            // has drained (the draw's latency hides behind the first tile).
+            SegDesc sa = sn;
+            sa.valid = false;
+            PendingItem<V> aft;
+            aft.d = part_of(sa, g);
+            aft.end_gate = vone(V());
+            Raw aft_gate_raw = 0;
+            int aft_nt = 0;
+            bool aft_known = false;
+            auto learn_after = [&]() {
+                if (!aft_known) {
+                    if (sn.valid) sa = describe_seg(seg_ticket(k + 2));
+                    aft.d = part_of(sa, g);
+                    aft_gate_raw = end_gate_raw(aft.d);
+                    aft_nt = sa.valid ? aft.d.nt : 0;
+                    aft_known = true;
+                }
+            };
+
+            // ---------------- scan pass from shared memory
+            {
+                V next_gate = cur.end_gate;
+                const int nt = cur.d.nt;
+                for (int i = 0; i < nt; ++i) {
+                    V a[K], b[K];
+                    int nvalid;
+                    fetch(cur, cur_slot, i, a, b, next_gate, nvalid);
+                    const int t = tile_of_step(cur.d, i);
+                    const int64_t toff = static_cast<int64_t>(t) * TE;
+                    const int stage = cur_slot * NT + i;
+                    unsigned char *stg = wsm + stage * STAGE_BYTES;
+                    V xp[BACK ? K : 1];
+                    V x_below = vzero(V());
+                    if (BACK) {
+#pragma unroll
+                        for (int c = 0; c < NCH; ++c)
+                            TR::unpack(*reinterpret_cast<const uint4 *>(stg + 2 * TB + (lane * NCH + c) * 16), &xp[c * EPC]);
+                        if (cur.d.pos0 + toff != 0) {
+                            V hv[EPC];
+                            TR::unpack(*reinterpret_cast<const uint4 *>(stg + NIN * TB), hv);
+                            x_below = hv[EPC - 1];
+                        } else if (hstate) {
+                            x_below = hstate[row];
+                        }
+                    }
+                    const float4 pf = lane_prefix[stage * 32 + lane];
+                    if constexpr (STAGED) {
+                        // the tile is in registers: its stage takes the matching tile of the segment
+                        // after the next
+                        __syncwarp();
+                        fence_async_smem();
+                        if (i >= 1) {
+                            learn_after();
+                            if (i == 1 && 0 < aft_nt) issue(aft.d, cur_slot, 0);
+                            if (i < aft_nt) issue(aft.d, cur_slot, i);
+                        }
+                    }
+                    if constexpr (PACKED) {
+                        auto J = [](int q) { return REV ? K - 1 - q : q; };
+                        const float x = fmaf(pf.x, x_in, pf.y);
+                        float2 Xv = make_float2(x, fmaf(pf.z, x, pf.w));       // states entering the two halves
+#pragma unroll
+                        for (int q = 0; q < H; ++q) {
+                            const float2 av = make_float2(a[J(q)], a[J(H + q)]);
+                            const float2 bv = make_float2(b[J(q)], b[J(H + q)]);
+                            Xv = __ffma2_rn(av, Xv, bv);
+                            b[J(q)] = Xv.x;
+                            b[J(H + q)] = Xv.y;
+                        }
+                    } else {
+                        V x;
+                        if constexpr (sizeof(V) == 4) {
+                            x = vfma(pf.x, x_in, pf.y);
+                        } else {
+                            x = vfma(make_float2(pf.x, pf.y), x_in, make_float2(pf.z, pf.w));
+                        }
+#pragma unroll
+                        for (int q = 0; q < K; ++q) {
+                            const int j = REV ? K - 1 - q : q;
+                            x = vfma(a[j], x, b[j]);
+                            b[j] = x;
+                        }
+                    }
+                    if (BACK) {
+                        // d_gates[t] = conj(x[t-1]) * g[t]
+                        V dn = shfl_up(xp[K - 1], 1);
+                        if (lane == 0) dn = x_below;
+#pragma unroll
+                        for (int j = K - 1; j >= 1; --j) a[j] = vmul(vconj(xp[j - 1]), b[j]);
+                        a[0] = vmul(vconj(dn), b[0]);
+                    }
+                    if constexpr (STAGED) {
+                        // results into the staging tile (once the store before has read it), then out
+                        if (lane == 0) bulk_wait_read<0>();
+                        __syncwarp();
+#pragma unroll
+                        for (int c = 0; c < NCH; ++c)
+                            *reinterpret_cast<uint4 *>(staging + (lane * NCH + c) * 16) = TR::pack(&b[c * EPC]);
+                        fence_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            bulk_s2g(obase[0] + (cur.d.e_begin + toff) * TR::ESIZE, staging, static_cast<uint32_t>(nvalid) * TR::ESIZE);
+                            bulk_commit();
+                        }
+                    } else {
+                        // results over the inputs of the stage, then out by bulk copies
+                        __syncwarp();
+#pragma unroll
+                        for (int c = 0; c < NCH; ++c) {
+                            *reinterpret_cast<uint4 *>(stg + 1 * TB + (lane * NCH + c) * 16) = TR::pack(&b[c * EPC]);
+                            if (NOUT > 1) *reinterpret_cast<uint4 *>(stg + 2 * TB + (lane * NCH + c) * 16) = TR::pack(&a[c * EPC]);
+                        }
+                        fence_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            const uint32_t bytes = static_cast<uint32_t>(nvalid) * TR::ESIZE;
+                            const int64_t goff = (cur.d.e_begin + toff) * TR::ESIZE;
+                            bulk_s2g(obase[0] + goff, stg + 1 * TB, bytes);
+                            if (NOUT > 1) bulk_s2g(obase[1] + goff, stg + 2 * TB, bytes);
+                            bulk_commit();
+                            // the store of the stage before this one has read its data: refill that stage
+                            if (i > 0) bulk_wait_read<1>();
+                        }
+                        __syncwarp();
+                        if (i > 0) {
+                            learn_after();
+                            if (i - 1 < aft_nt) issue(aft.d, cur_slot, i - 1);
+                        }
+                    }
+                }
+                learn_after();
                 if constexpr (STAGED) {
-                    // results into the staging tile (once the store before has read it), then out
+                    // stages the loop did not refill: the only one of a one-tile part, and those the
+                    // part after the next has beyond this part's tiles
+                    if (nt <= 1 && 0 < aft_nt) issue(aft.d, cur_slot, 0);
+                    for (int i = nt > 1 ? nt : 1; i < aft_nt; ++i) issue(aft.d, cur_slot, i);
+                } else {
                     if (lane == 0) bulk_wait_read<0>();
                     __syncwarp();
-#pragma unroll
-                    for (int c = 0; c < NCH; ++c)
-                        *reinterpret_cast<uint4 *>(staging + (lane * NCH + c) * 16) = TR::pack(&b[c * EPC]);
-                    fence_async_smem();
-                    __syncwarp();
-                    if (lane == 0) {
-                        bulk_s2g(obase[0] + (cur.d.e_begin + toff) * TR::ESIZE, staging, static_cast<uint32_t>(nvalid) * TR::ESIZE);
-                        bulk_commit();
-                    }
-                } else {
-                    // results over the inputs of the stage, then out by bulk copies
-                    __syncwarp();
-#pragma unroll
-                    for (int c = 0; c < NCH; ++c) {
-                        *reinterpret_cast<uint4 *>(stg + 1 * TB + (lane * NCH + c) * 16) = TR::pack(&b[c * EPC]);
-                        if (NOUT > 1) *reinterpret_cast<uint4 *>(stg + 2 * TB + (lane * NCH + c) * 16) = TR::pack(&a[c * EPC]);
-                    }
-                    fence_async_smem();
-                    __syncwarp();
-                    if (lane == 0) {
-                        const uint32_t bytes = static_cast<uint32_t>(nvalid) * TR::ESIZE;
-                        const int64_t goff = (cur.d.e_begin + toff) * TR::ESIZE;
-                        bulk_s2g(obase[0] + goff, stg + 1 * TB, bytes);
-                        if (NOUT > 1) bulk_s2g(obase[1] + goff, stg + 2 * TB, bytes);
-                        bulk_commit();
-                        // the store of the stage before this one has read its data: refill that stage
-                        if (i > 0) bulk_wait_read<1>();
-                    }
-                    __syncwarp();
-                    if (i > 0) {
-                        learn_after();
-                        if (aft.d.valid && i - 1 < aft.d.nt) issue(aft.d, cur_slot, i - 1);
-                    }
+                    for (int i = nt > 0 ? nt - 1 : 0; i < aft_nt; ++i) issue(aft.d, cur_slot, i);
                 }
             }
-            learn_after();
-            if constexpr (STAGED) {
-                // stages the loop did not refill: the only one of a one-tile item, and those the
-                // item after the next has beyond this item's tiles
-                if (aft.d.valid) {
-                    if (nt == 1) issue(aft.d, cur_slot, 0);
-                    for (int i = nt > 1 ? nt : 1; i < aft.d.nt; ++i) issue(aft.d, cur_slot, i);
-                }
-            } else {
-                if (lane == 0) bulk_wait_read<0>();
-                __syncwarp();
-                if (aft.d.valid) {
-                    for (int i = nt - 1; i < aft.d.nt; ++i) issue(aft.d, cur_slot, i);
-                }
-            }
+            if (failed) break;
+            cur = nxt;
+            sc = sn;
+            nxt = aft;
+            sn = sa;
+            nxt_gate_raw = aft_gate_raw;
+            cur_slot = nxt_slot;
+            ++k;
         }
-        cur = nxt;
-        nxt = aft;
-        nxt_gate_raw = aft_gate_raw;
-        cur_slot = nxt_slot;
+        if (lane == 0) bulk_wait_read<0>();
+        __syncwarp();
+    } else {
+        // =====================================================================================
+        // Bookkeeper: tickets and look-backs.
+        auto draw = [&]() -> uint32_t {
+            uint32_t t = 0;
+            if (lane == 0) t = atomicAdd(p.ctrl + CTRL_TICKET, 1u);
+            return __shfl_sync(0xffffffffu, t, 0);
+        };
+        auto post_ticket = [&](uint32_t k, uint32_t q) {
+            if (lane == 0) {
+                tickets[k & 3u] = q;
+                mbar_arrive(&dr[k & 3u]);
+            }
+            __syncwarp();
+        };
+        uint32_t q_cur = draw();
+        if (q_cur >= static_cast<uint32_t>(p.items)) q_cur = LB_NO_ITEM;
+        post_ticket(0, q_cur);
+        uint32_t q_nxt = LB_NO_ITEM;
+        if (q_cur != LB_NO_ITEM) {
+            q_nxt = draw();
+            if (q_nxt >= static_cast<uint32_t>(p.items)) q_nxt = LB_NO_ITEM;
+        }
+        post_ticket(1, q_nxt);
+
+        RecordWords ahead;
+        for (int w = 0; w < 6; ++w) ahead.w[w] = 0;
+        bool have_ahead = false;
+        for (uint32_t k = 0; q_cur != LB_NO_ITEM && !failed; ++k) {
+            const SegDesc sg = describe_seg(q_cur);
+            const int b = static_cast<int>(k & 1u);
+            if (!__all_sync(0xffffffffu, team_wait(&pub[b], (k >> 1) & 1u, abort_flag))) {
+                if (!*abort_flag) give_up(STATUS_LOOKBACK_TIMEOUT);
+                break;
+            }
+            // the map from the segment's start to the start of every worker's part
+            V pa, pb;
+            compose_parts(b, pa, pb);
+            pa = shfl_up(pa, 1);
+            pb = shfl_up(pb, 1);
+            if (lane == 0) {
+                pa = vone(V());
+                pb = vzero(V());
+            }
+            // ---------------- look back
+            const int64_t row = sg.row;
+            const int s = sg.s;
+            unsigned char *row_rec = records + static_cast<uint64_t>(row) * per_row * LB_RECORD_BYTES;
+            V preA, preB;                                  // map from the slice's start to the segment's start
+            bool lb_ok = local_prefix(row_rec, s, preA, preB, have_ahead ? &ahead : nullptr);
+            // state entering the slice: the caller's, or the fold of the earlier ranks' aggregates
+            V x_slice = cin ? cin[row] : vzero(V());
+            if (n_before > 0 && lb_ok) {
+                // lane i reads the aggregate of the i-th rank in processing order
+                const int first = REV ? sp.world - 1 : 0;
+                const int64_t step = (REV ? -1 : 1) * static_cast<int64_t>(p.rows) * LB_RECORD_BYTES;
+                const unsigned char *base = xl + xchg_carry_offset(p.rows) +
+                                            ((static_cast<uint64_t>(parity_slot) * sp.world + first) * p.rows + row) * LB_RECORD_BYTES;
+                V Ar, Br;
+                lb_ok = compose_window<V, true>(base, step, n_before, sp.call, lane, Ar, Br);
+                x_slice = vfma(Ar, x_slice, Br);
+            }
+            // forward: the state entering the slice is what the backward needs below its first step
+            if (!REV && s == 0 && sp.carry_save && lane == 0) static_cast<V *>(sp.carry_save)[row] = x_slice;
+            if (!lb_ok) {
+                give_up(STATUS_LOOKBACK_TIMEOUT);
+                break;
+            }
+            // The ticket of the segment after the next is drawn only now, after the look-back: from
+            // this draw to the publication of that segment's aggregate nothing waits for a look-back,
+            // so a drawn segment is never held back by this warp waiting for other CTAs.  (Drawn
+            // earlier, such waits chained up across CTAs.)  The number arrives while the states go
+            // out and the next look-back's records are asked for.
+            uint32_t raw_aft = 0;
+            if (q_nxt != LB_NO_ITEM && lane == 0) raw_aft = atomicAdd(p.ctrl + CTRL_TICKET, 1u);
+            const V x_seg = vfma(preA, x_slice, preB);
+            if (lane < G) *reinterpret_cast<V *>(xin + (b * 16 + lane) * 8) = vfma(pa, x_seg, pb);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&xr[b]);
+            // real types: the records the next segment's look-back will read, loaded now and used
+            // once that segment's aggregate is out (what is missing then is polled for)
+            have_ahead = false;
+            if constexpr (sizeof(V) == 4) {
+                if (q_nxt != LB_NO_ITEM) {
+                    const SegDesc sx = describe_seg(q_nxt);
+                    ahead = load_ahead(records + static_cast<uint64_t>(sx.row) * per_row * LB_RECORD_BYTES, sx.s);
+                    have_ahead = true;
+                }
+            }
+            uint32_t q_aft = LB_NO_ITEM;
+            if (q_nxt != LB_NO_ITEM) {
+                q_aft = __shfl_sync(0xffffffffu, raw_aft, 0);
+                if (q_aft >= static_cast<uint32_t>(p.items)) q_aft = LB_NO_ITEM;
+            }
+            post_ticket(k + 2, q_aft);
+            q_cur = q_nxt;
+            q_nxt = q_aft;
+        }
     }
 
-    if (lane == 0) bulk_wait_read<0>();
-    __syncwarp();
     // a rank that leaves tells the others: its reads of this call's exchange slots are over
     if (sharded) {
         uint32_t last = 0;

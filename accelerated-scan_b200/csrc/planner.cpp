@@ -132,17 +132,22 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
         const int64_t tiles_row3 = (in.seqlen + te3 - 1) / te3;
         const bool possible = can_split && bulk && scan_kind && in.rows > 0 && (in.tune.disable_plans & 1) == 0;
         const bool wanted = in.force_lookback || (in.allow_lookback && in.rows < lookback_rows && tiles_row3 >= 2 * lb_tiles);
-        const int64_t segs = (in.seqlen + lb_tiles * te3 - 1) / (lb_tiles * te3);
-        if (possible && wanted && in.rows * segs < (1ll << 31)) {
-            // two resident segments per warp (lb_warp_smem in lookback.cuh)
+        if (possible && wanted && in.rows * ((tiles_row3 + lb_tiles - 1) / lb_tiles) < (1ll << 31)) {
+            // A CTA is a team of worker warps plus one bookkeeper.  Per worker: its lb_tiles tiles
+            // of two resident segments (lb_warp_smem in lookback.cuh); 1024 bytes for the team.
             const int stage = nin_of(in.kind) * 32 * 3 * 16 + (in.kind == ASCAN_KIND_BACKWARD ? 128 : 0);
             const int staging = in.kind == ASCAN_KIND_BACKWARD ? 0 : 32 * 3 * 16;
             const int wsm = 2 * lb_tiles * stage + staging + 128 + 2 * lb_tiles * 32 * 16;
-            int wpc = kMaxSmemPerCta / wsm;
-            const int cap = 16;
-            if (wpc > cap) wpc = cap;
-            if (in.tune.warps_per_cta > 0 && in.tune.warps_per_cta < wpc) wpc = in.tune.warps_per_cta;
-            if (wpc < 1) return ASCAN_ERR_UNSUPPORTED;
+            int64_t workers = (kMaxSmemPerCta - 1024) / wsm;
+            if (workers > 15) workers = 15;
+            if (in.tune.warps_per_cta > 1 && in.tune.warps_per_cta - 1 < workers) workers = in.tune.warps_per_cta - 1;
+            if (workers < 1) return ASCAN_ERR_UNSUPPORTED;
+            // a segment is one part (lb_tiles tiles) per worker; rows are cut into segments of equal
+            // size, and short rows get no more workers than they have parts
+            const int64_t parts_row = (tiles_row3 + lb_tiles - 1) / lb_tiles;
+            const int64_t segs = (parts_row + workers - 1) / workers;
+            workers = (parts_row + segs - 1) / segs;
+            const int wpc = static_cast<int>(workers) + 1;
             pl.kernel = 1;
             pl.loader = 0;
             pl.chunks_per_lane = 3;
@@ -152,21 +157,17 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
             pl.team_size = 1;
             pl.rows_per_item = 1;
             pl.row_groups = in.rows;
-            pl.seg_elems = lb_tiles * te3;
+            pl.seg_elems = workers * lb_tiles * te3;
             pl.fine_elems = pl.seg_elems;
             pl.coarse_segs = 0;
             pl.fine_segs = segs;
             pl.segs_per_row = segs;
             pl.items = in.rows * segs;
             int64_t grid = in.sm_count;
-            if (pl.items < grid * wpc) {
-                int64_t w = (pl.items + grid - 1) / grid;
-                wpc = static_cast<int>(w < 1 ? 1 : w);
-                grid = (pl.items + wpc - 1) / wpc;
-            }
+            if (pl.items < grid) grid = pl.items;
             pl.warps_per_cta = wpc;
             pl.grid = static_cast<int32_t>(grid);
-            pl.smem_bytes = static_cast<uint64_t>(wpc) * wsm;
+            pl.smem_bytes = static_cast<uint64_t>(workers) * wsm + 1024;
             pl.workspace_bytes = static_cast<uint64_t>(kCtrlBytes) +
                                  static_cast<uint64_t>(in.rows) * lookback_records_per_row(segs) * kLookbackRecordBytes;
             *plan = pl;

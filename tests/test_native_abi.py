@@ -67,13 +67,17 @@ def test_planner_invariants(T, dtype, kind):
             assert pl["segs_per_row"] == 1 and pl["kernel"] == 0 and pl["workspace_bytes"] == 0
             assert pl["items"] <= 8 * pl["grid"] * pl["warps_per_cta"]
         elif pl["kernel"] == 1:
-            # look-back plan: fewer rows than 3/4 of the SMs; equal short segments, two of them resident per
-            # warp; 32-byte records per segment, block of 32 segments and super-block of 32 blocks
-            assert rows < 111 and kind in (0, 1) and pl["segs_per_row"] > 1
+            # look-back plan: fewer rows than 3/4 of the SMs; a CTA is a team of workers plus a bookkeeper, a
+            # segment is one part of `stages` tiles per worker; 32-byte records per segment, block of 32
+            # segments and super-block of 32 blocks
+            assert rows < 111 and kind in (0, 1)
+            workers = pl["warps_per_cta"] - 1
+            assert 1 <= workers <= 15 and pl["grid"] == min(148, pl["items"])
             segs = pl["segs_per_row"]
             blocks = (segs + 31) // 32
             assert pl["workspace_bytes"] == 256 + 32 * rows * (segs + blocks + (blocks + 31) // 32)
-            assert pl["seg_elems"] == pl["fine_elems"] == pl["stages"] * pl["tile_elems"]
+            assert pl["seg_elems"] == pl["fine_elems"] == workers * pl["stages"] * pl["tile_elems"]
+            assert (segs - 1) * pl["seg_elems"] < T
             assert pl["stages"] == 2 and pl["chunks_per_lane"] == 3
             chained = _native.plan(rows, T, dtype, kind, sm_count=148, lookback=False, team=False)
             assert chained["kernel"] == 0 and chained["workspace_bytes"] in (0, 256, 256 + 32 * rows)
