@@ -51,7 +51,7 @@ namespace ascan {
 constexpr int LB_RECORD_BYTES = 32;          // one affine pair of the compute type in tagged 64-bit words
 constexpr int LB_MAX_TILES = 8;              // tiles per worker and segment, at most (a worker holds two segments: 2 stages per tile)
 constexpr int LB_MAX_WORKERS = 15;           // worker warps per CTA, at most (plus the bookkeeper)
-constexpr int LB_TEAM_BYTES = 1024;          // shared memory of the team: parts, incoming states, tickets, mbarriers
+constexpr int LB_TEAM_BYTES = 3072;          // shared memory of the team: parts, incoming states, mbarriers, part descriptors
 constexpr int MAX_WORLD = 16;                // ranks of a time-sharded scan, at most
 constexpr uint32_t LB_WAIT_POLLS = 1u << 20;      // about a second
 constexpr uint32_t LB_TEAM_POLLS = 1u << 22;      // waits inside a CTA: a safety net, they end on the abort flag
@@ -253,6 +253,7 @@ __device__ __forceinline__ bool compose_three(const unsigned char *const base[3]
 // Bounded wait on an mbarrier of the team; ends early when a warp of the CTA has raised the
 // abort flag (after a wait of its own has expired).
 __device__ __forceinline__ bool team_wait(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag) {
+    if (mbar_test_wait(bar, parity)) return true;      // the usual case: the phase is over already
     for (uint32_t i = 0; i < LB_TEAM_POLLS; ++i) {
         uint32_t ok;
         asm volatile(
@@ -351,10 +352,10 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
     unsigned char *tsm = smem_raw + static_cast<size_t>(G) * WARP_SMEM;
     unsigned char *parts = tsm;                                              // [2][16] pairs: the workers' aggregates
     unsigned char *xin = tsm + 512;                                          // [2][16] values: the states entering the parts
-    volatile uint32_t *tickets = reinterpret_cast<volatile uint32_t *>(tsm + 768);   // [4] item numbers
+    unsigned char *pdesc = tsm + 1024;                                       // [4][16] part descriptors of 32 bytes
     uint64_t *pub = reinterpret_cast<uint64_t *>(tsm + 832);                 // [2] the segment's aggregate is published
     uint64_t *xr = pub + 2;                                                  // [2] the incoming states are there
-    uint64_t *dr = pub + 4;                                                  // [4] the ticket is there
+    uint64_t *dr = pub + 4;                                                  // [4] the part descriptors are there
     uint32_t *cnt = reinterpret_cast<uint32_t *>(tsm + 896);                 // [2] workers that have posted their part
     volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(tsm + 904);
 
@@ -575,14 +576,32 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
             if (lane < NIN) bulk_g2s(dst + lane * TB, gbase[lane] + goff, bytes, &bars[stage]);
             if (lane == NIN && halo) bulk_g2s(dst + NIN * TB, gbase[2] + goff - 16, 16, &bars[stage]);
         };
-        // the ticket of the CTA's k-th segment, once the bookkeeper has posted it
-        auto seg_ticket = [&](uint32_t k) -> uint32_t {
+        // this worker's part of the CTA's k-th segment, once the bookkeeper has posted it
+        // (32 bytes per worker: e_begin, pos0, n, nt, row, s; row < 0: no segment)
+        auto take_part = [&](uint32_t k, SegDesc &sg, ItemDesc &d) {
+            sg.valid = false;
+            sg.row = 0; sg.pos0 = 0; sg.n = 0; sg.s = 0; sg.nts = 0;
+            d.valid = false;
+            d.e_begin = 0; d.row0 = 0; d.pos0 = 0; d.n = 0; d.s_log = 0; d.nt = 0;
             if (!__all_sync(0xffffffffu, team_wait(&dr[k & 3u], (k >> 2) & 1u, abort_flag))) {
                 if (!*abort_flag) give_up(STATUS_LOOKBACK_TIMEOUT);
                 failed = true;
-                return LB_NO_ITEM;
+                return;
             }
-            return tickets[k & 3u];
+            const unsigned char *pd = pdesc + ((k & 3u) * 16 + g) * 32;
+            const longlong2 w0 = *reinterpret_cast<const longlong2 *>(pd);
+            const int4 w1 = *reinterpret_cast<const int4 *>(pd + 16);
+            if (w1.z < 0) return;
+            sg.valid = true;
+            sg.row = w1.z;
+            sg.s = w1.w;
+            d.valid = true;
+            d.e_begin = w0.x;
+            d.pos0 = w0.y;
+            d.n = w1.x;
+            d.nt = w1.y;
+            d.row0 = w1.z;
+            d.s_log = w1.w;
         };
         // backward: the gate of the step right after a part, loaded when the part is known (the
         // load's latency hides behind the scan pass that runs meanwhile)
@@ -807,11 +826,11 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
         };
 
         uint32_t k = 0;
-        SegDesc sc = describe_seg(seg_ticket(0));
-        SegDesc sn = sc;
-        sn.valid = false;
+        SegDesc sc, sn;
         PendingItem<V> cur, nxt;
-        cur.d = part_of(sc, g);
+        take_part(0, sc, cur.d);
+        sn = sc;
+        sn.valid = false;
         cur.end_gate = vone(V());
         nxt = cur;
         nxt.d.valid = false;
@@ -821,8 +840,7 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
         if (sc.valid && !failed) {
             for (int i = 0; i < cur.d.nt; ++i) issue(cur.d, 0, i);
             const Raw g_raw = end_gate_raw(cur.d);
-            sn = describe_seg(seg_ticket(1));
-            nxt.d = part_of(sn, g);
+            take_part(1, sn, nxt.d);
             if (sn.valid) {
                 for (int i = 0; i < nxt.d.nt; ++i) issue(nxt.d, 1, i);
             }
@@ -844,26 +862,19 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
                 break;
             }
             const V x_in = *reinterpret_cast<const V *>(xin + ((k & 1u) * 16 + g) * 8);
-            // the segment after the next: its tiles refill the stages as they drain.  Its ticket is
-            // drawn after this segment's look-back, so it is asked for only when the first stage
-            // has drained (the draw's latency hides behind the first tile).
+            // the segment after the next: its tiles refill the stages as they drain (the bookkeeper
+            // drew its ticket right after this segment's look-back, which is over by now)
             SegDesc sa = sn;
             sa.valid = false;
             PendingItem<V> aft;
-            aft.d = part_of(sa, g);
+            aft.d = nxt.d;
+            aft.d.valid = false;
+            aft.d.nt = 0;
+            if (sn.valid) take_part(k + 2, sa, aft.d);
+            if (failed) break;
             aft.end_gate = vone(V());
-            Raw aft_gate_raw = 0;
-            int aft_nt = 0;
-            bool aft_known = false;
-            auto learn_after = [&]() {
-                if (!aft_known) {
-                    if (sn.valid) sa = describe_seg(seg_ticket(k + 2));
-                    aft.d = part_of(sa, g);
-                    aft_gate_raw = end_gate_raw(aft.d);
-                    aft_nt = sa.valid ? aft.d.nt : 0;
-                    aft_known = true;
-                }
-            };
+            const Raw aft_gate_raw = end_gate_raw(aft.d);
+            const int aft_nt = sa.valid ? aft.d.nt : 0;
 
             // ---------------- scan pass from shared memory
             {
@@ -897,11 +908,7 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
                         // after the next
                         __syncwarp();
                         fence_async_smem();
-                        if (i >= 1) {
-                            learn_after();
-                            if (i == 1 && 0 < aft_nt) issue(aft.d, cur_slot, 0);
-                            if (i < aft_nt) issue(aft.d, cur_slot, i);
-                        }
+                        if (i < aft_nt) issue(aft.d, cur_slot, i);
                     }
                     if constexpr (PACKED) {
                         auto J = [](int q) { return REV ? K - 1 - q : q; };
@@ -970,18 +977,12 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
                             if (i > 0) bulk_wait_read<1>();
                         }
                         __syncwarp();
-                        if (i > 0) {
-                            learn_after();
-                            if (i - 1 < aft_nt) issue(aft.d, cur_slot, i - 1);
-                        }
+                        if (i > 0 && i - 1 < aft_nt) issue(aft.d, cur_slot, i - 1);
                     }
                 }
-                learn_after();
                 if constexpr (STAGED) {
-                    // stages the loop did not refill: the only one of a one-tile part, and those the
-                    // part after the next has beyond this part's tiles
-                    if (nt <= 1 && 0 < aft_nt) issue(aft.d, cur_slot, 0);
-                    for (int i = nt > 1 ? nt : 1; i < aft_nt; ++i) issue(aft.d, cur_slot, i);
+                    // stages beyond this part's tiles
+                    for (int i = nt; i < aft_nt; ++i) issue(aft.d, cur_slot, i);
                 } else {
                     if (lane == 0) bulk_wait_read<0>();
                     __syncwarp();
@@ -1007,12 +1008,17 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
             if (lane == 0) t = atomicAdd(p.ctrl + CTRL_TICKET, 1u);
             return __shfl_sync(0xffffffffu, t, 0);
         };
+        // the parts of segment `q` (the CTA's k-th), one descriptor per worker
         auto post_ticket = [&](uint32_t k, uint32_t q) {
-            if (lane == 0) {
-                tickets[k & 3u] = q;
-                mbar_arrive(&dr[k & 3u]);
+            const SegDesc sg = describe_seg(q);
+            const ItemDesc d = part_of(sg, lane < G ? lane : 0);
+            if (lane < G) {
+                unsigned char *pd = pdesc + ((k & 3u) * 16 + lane) * 32;
+                *reinterpret_cast<longlong2 *>(pd) = make_longlong2(d.e_begin, d.pos0);
+                *reinterpret_cast<int4 *>(pd + 16) = make_int4(static_cast<int>(d.n), d.nt, sg.valid ? static_cast<int>(sg.row) : -1, sg.s);
             }
             __syncwarp();
+            if (lane == 0) mbar_arrive(&dr[k & 3u]);
         };
         uint32_t q_cur = draw();
         if (q_cur >= static_cast<uint32_t>(p.items)) q_cur = LB_NO_ITEM;

@@ -134,11 +134,11 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
         const bool wanted = in.force_lookback || (in.allow_lookback && in.rows < lookback_rows && tiles_row3 >= 2 * lb_tiles);
         if (possible && wanted && in.rows * ((tiles_row3 + lb_tiles - 1) / lb_tiles) < (1ll << 31)) {
             // A CTA is a team of worker warps plus one bookkeeper.  Per worker: its lb_tiles tiles
-            // of two resident segments (lb_warp_smem in lookback.cuh); 1024 bytes for the team.
+            // of two resident segments (lb_warp_smem in lookback.cuh); 3072 bytes for the team.
             const int stage = nin_of(in.kind) * 32 * 3 * 16 + (in.kind == ASCAN_KIND_BACKWARD ? 128 : 0);
             const int staging = in.kind == ASCAN_KIND_BACKWARD ? 0 : 32 * 3 * 16;
             const int wsm = 2 * lb_tiles * stage + staging + 128 + 2 * lb_tiles * 32 * 16;
-            int64_t workers = (kMaxSmemPerCta - 1024) / wsm;
+            int64_t workers = (kMaxSmemPerCta - 3072) / wsm;
             if (workers > 15) workers = 15;
             if (in.tune.warps_per_cta > 1 && in.tune.warps_per_cta - 1 < workers) workers = in.tune.warps_per_cta - 1;
             if (workers < 1) return ASCAN_ERR_UNSUPPORTED;
@@ -167,7 +167,7 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
             if (pl.items < grid) grid = pl.items;
             pl.warps_per_cta = wpc;
             pl.grid = static_cast<int32_t>(grid);
-            pl.smem_bytes = static_cast<uint64_t>(workers) * wsm + 1024;
+            pl.smem_bytes = static_cast<uint64_t>(workers) * wsm + 3072;
             pl.workspace_bytes = static_cast<uint64_t>(kCtrlBytes) +
                                  static_cast<uint64_t>(in.rows) * lookback_records_per_row(segs) * kLookbackRecordBytes;
             *plan = pl;
