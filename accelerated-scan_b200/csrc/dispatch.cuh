@@ -48,7 +48,7 @@ static int launch_lookback(const StreamParams &p, const ascan_plan &pl, cudaStre
     // the planner restates the kernel's shared-memory layout: refuse a plan that disagrees with it
     const int workers = pl.warps_per_cta - 1;
     if (workers < 1 || workers > LB_MAX_WORKERS || pl.stages < 1 || pl.stages > LB_MAX_TILES ||
-        pl.smem_bytes != static_cast<uint64_t>(workers) * lb_warp_smem(3, pl.stages, KIND) + LB_TEAM_BYTES ||
+        pl.smem_bytes != static_cast<uint64_t>(workers) * lb_warp_smem(3, pl.stages, KIND, sizeof(typename TR::V) == 8) + LB_TEAM_BYTES ||
         pl.seg_elems != static_cast<int64_t>(workers) * pl.stages * 32 * 3 * TR::EPC)
         return ASCAN_ERR_UNSUPPORTED;
     int rc = ensure_smem(reinterpret_cast<const void *>(kfn));

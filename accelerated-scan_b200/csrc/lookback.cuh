@@ -82,10 +82,15 @@ __host__ __device__ constexpr int lb_stage_bytes(int nch, int kind) {
 // be refilled as soon as its tile is in registers; the fused backward writes its two results over
 // the stage's inputs (a staging area would cost it two warps per CTA).
 __host__ __device__ constexpr int lb_staging_bytes(int nch, int kind) { return kind == K_BWD ? 0 : 32 * nch * 16; }
-// Per worker: its `nt` tiles of two resident segments, the staging tile, the mbarriers, and 16
-// bytes per stage and lane of prefix maps.
-__host__ __device__ constexpr int lb_warp_smem(int nch, int nt, int kind) {
-    return 2 * nt * lb_stage_bytes(nch, kind) + lb_staging_bytes(nch, kind) + 128 + 2 * nt * 32 * 16;
+// Prefix maps, per stage and lane: the affine map from the part's start to the lane's first
+// element (two values of the compute type), and for the forward kinds of the real types also
+// the map over the first half of the lane's elements.  The fused backward of the real types
+// does without the second one: the kilobyte it saves per worker buys another worker.
+__host__ __device__ constexpr int lb_prefix_bytes(int kind, bool complex_type) { return (kind == K_BWD && !complex_type) ? 8 : 16; }
+// Per worker: its `nt` tiles of two resident segments, the staging tile, the mbarriers, the
+// prefix maps.
+__host__ __device__ constexpr int lb_warp_smem(int nch, int nt, int kind, bool complex_type) {
+    return 2 * nt * lb_stage_bytes(nch, kind) + lb_staging_bytes(nch, kind) + 128 + 2 * nt * 32 * lb_prefix_bytes(kind, complex_type);
 }
 // Workspace of the look-back plan: control block, then the records of the three levels.
 __host__ __device__ constexpr uint64_t lb_level_count(int64_t n) { return static_cast<uint64_t>((n + 31) / 32); }
@@ -329,10 +334,11 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
     constexpr int NIN = stream_nin(KIND);
     constexpr int NOUT = stream_nout(KIND);
     constexpr int STAGE_BYTES = lb_stage_bytes(NCH, KIND);
-    constexpr bool PACKED = sizeof(V) == 4 && (K % 2 == 0);
+    constexpr bool PACKED = sizeof(V) == 4 && (K % 2 == 0) && !BACK;     // the lane's elements as two halves side by side
+    constexpr int PREFIX_BYTES = lb_prefix_bytes(KIND, sizeof(V) == 8);
     constexpr int H = K / 2;
     const int NT = p.stages;                                  // tiles per worker and segment; 2 * NT stages per worker
-    const int WARP_SMEM = lb_warp_smem(NCH, NT, KIND);
+    const int WARP_SMEM = lb_warp_smem(NCH, NT, KIND, sizeof(V) == 8);
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int lane = threadIdx.x & 31;
@@ -345,9 +351,7 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
     constexpr int STAGING_BYTES = lb_staging_bytes(NCH, KIND);
     unsigned char *staging = wsm + 2 * NT * STAGE_BYTES;
     uint64_t *bars = reinterpret_cast<uint64_t *>(wsm + 2 * NT * STAGE_BYTES + STAGING_BYTES);
-    // per stage and lane: the affine map from the part's start to the lane's first element and,
-    // for the real types, the map over the first half of the lane's elements (4 floats in all)
-    float4 *lane_prefix = reinterpret_cast<float4 *>(wsm + 2 * NT * STAGE_BYTES + STAGING_BYTES + 128);
+    unsigned char *lane_prefix = wsm + 2 * NT * STAGE_BYTES + STAGING_BYTES + 128;     // PREFIX_BYTES per stage and lane
     // the team's memory
     unsigned char *tsm = smem_raw + static_cast<size_t>(G) * WARP_SMEM;
     unsigned char *parts = tsm;                                              // [2][16] pairs: the workers' aggregates
@@ -746,10 +750,12 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
                     pA = segA;
                     pB = segB;
                 }
-                if constexpr (sizeof(V) == 4) {
-                    lane_prefix[stage * 32 + lane] = make_float4(pA, pB, A0h, B0h);
+                if constexpr (PREFIX_BYTES == 8) {
+                    *reinterpret_cast<float2 *>(lane_prefix + (stage * 32 + lane) * 8) = make_float2(pA, pB);
+                } else if constexpr (sizeof(V) == 4) {
+                    *reinterpret_cast<float4 *>(lane_prefix + (stage * 32 + lane) * 16) = make_float4(pA, pB, A0h, B0h);
                 } else {
-                    lane_prefix[stage * 32 + lane] = make_float4(pA.x, pA.y, pB.x, pB.y);
+                    *reinterpret_cast<float4 *>(lane_prefix + (stage * 32 + lane) * 16) = make_float4(pA.x, pA.y, pB.x, pB.y);
                 }
                 segA = shfl_idx(A, REV ? 0 : 31);
                 segB = shfl_idx(B, REV ? 0 : 31);
@@ -902,7 +908,13 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
                             x_below = hstate[row];
                         }
                     }
-                    const float4 pf = lane_prefix[stage * 32 + lane];
+                    float4 pf;
+                    if constexpr (PREFIX_BYTES == 8) {
+                        const float2 h = *reinterpret_cast<const float2 *>(lane_prefix + (stage * 32 + lane) * 8);
+                        pf = make_float4(h.x, h.y, 1.0f, 0.0f);
+                    } else {
+                        pf = *reinterpret_cast<const float4 *>(lane_prefix + (stage * 32 + lane) * 16);
+                    }
                     if constexpr (STAGED) {
                         // the tile is in registers: its stage takes the matching tile of the segment
                         // after the next
