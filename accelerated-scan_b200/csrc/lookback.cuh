@@ -83,14 +83,12 @@ __host__ __device__ constexpr int lb_stage_bytes(int nch, int kind) {
 // the stage's inputs (a staging area would cost it two warps per CTA).
 __host__ __device__ constexpr int lb_staging_bytes(int nch, int kind) { return kind == K_BWD ? 0 : 32 * nch * 16; }
 // Prefix maps, per stage and lane: the affine map from the part's start to the lane's first
-// element (two values of the compute type), and for the forward kinds of the real types also
-// the map over the first half of the lane's elements.  The fused backward of the real types
-// does without the second one: the kilobyte it saves per worker buys another worker.
-__host__ __device__ constexpr int lb_prefix_bytes(int kind, bool complex_type) { return (kind == K_BWD && !complex_type) ? 8 : 16; }
+// element (two values of the compute type).
+__host__ __device__ constexpr int lb_prefix_bytes(bool complex_type) { return complex_type ? 16 : 8; }
 // Per worker: its `nt` tiles of two resident segments, the staging tile, the mbarriers, the
 // prefix maps.
 __host__ __device__ constexpr int lb_warp_smem(int nch, int nt, int kind, bool complex_type) {
-    return 2 * nt * lb_stage_bytes(nch, kind) + lb_staging_bytes(nch, kind) + 128 + 2 * nt * 32 * lb_prefix_bytes(kind, complex_type);
+    return 2 * nt * lb_stage_bytes(nch, kind) + lb_staging_bytes(nch, kind) + 128 + 2 * nt * 32 * lb_prefix_bytes(complex_type);
 }
 // Workspace of the look-back plan: control block, then the records of the three levels.
 __host__ __device__ constexpr uint64_t lb_level_count(int64_t n) { return static_cast<uint64_t>((n + 31) / 32); }
@@ -334,9 +332,7 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
     constexpr int NIN = stream_nin(KIND);
     constexpr int NOUT = stream_nout(KIND);
     constexpr int STAGE_BYTES = lb_stage_bytes(NCH, KIND);
-    constexpr bool PACKED = sizeof(V) == 4 && (K % 2 == 0) && !BACK;     // the lane's elements as two halves side by side
-    constexpr int PREFIX_BYTES = lb_prefix_bytes(KIND, sizeof(V) == 8);
-    constexpr int H = K / 2;
+    constexpr int PREFIX_BYTES = lb_prefix_bytes(sizeof(V) == 8);
     const int NT = p.stages;                                  // tiles per worker and segment; 2 * NT stages per worker
     const int WARP_SMEM = lb_warp_smem(NCH, NT, KIND, sizeof(V) == 8);
 
@@ -700,23 +696,7 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
                 int nvalid;
                 fetch(it, slot, i, a, b, next_gate, nvalid);
                 V A, B;
-                V A0h = vone(V()), B0h = vzero(V());     // real types: the map over the first half of the lane's elements
-                if constexpr (PACKED) {
-                    auto J = [](int q) { return REV ? K - 1 - q : q; };
-                    float2 Av = make_float2(a[J(0)], a[J(H)]);
-                    float2 Bv = make_float2(b[J(0)], b[J(H)]);
-#pragma unroll
-                    for (int q = 1; q < H; ++q) {
-                        const float2 av = make_float2(a[J(q)], a[J(H + q)]);
-                        const float2 bv = make_float2(b[J(q)], b[J(H + q)]);
-                        Bv = __ffma2_rn(av, Bv, bv);
-                        Av = __fmul2_rn(Av, av);
-                    }
-                    A0h = Av.x;
-                    B0h = Bv.x;
-                    A = Av.x * Av.y;
-                    B = fmaf(Av.y, Bv.x, Bv.y);
-                } else {
+                {
                     constexpr int JF = REV ? K - 1 : 0;
                     A = a[JF];
                     B = b[JF];
@@ -750,12 +730,10 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
                     pA = segA;
                     pB = segB;
                 }
-                if constexpr (PREFIX_BYTES == 8) {
-                    *reinterpret_cast<float2 *>(lane_prefix + (stage * 32 + lane) * 8) = make_float2(pA, pB);
-                } else if constexpr (sizeof(V) == 4) {
-                    *reinterpret_cast<float4 *>(lane_prefix + (stage * 32 + lane) * 16) = make_float4(pA, pB, A0h, B0h);
+                if constexpr (sizeof(V) == 4) {
+                    *reinterpret_cast<float2 *>(lane_prefix + (stage * 32 + lane) * PREFIX_BYTES) = make_float2(pA, pB);
                 } else {
-                    *reinterpret_cast<float4 *>(lane_prefix + (stage * 32 + lane) * 16) = make_float4(pA.x, pA.y, pB.x, pB.y);
+                    *reinterpret_cast<float4 *>(lane_prefix + (stage * 32 + lane) * PREFIX_BYTES) = make_float4(pA.x, pA.y, pB.x, pB.y);
                 }
                 segA = shfl_idx(A, REV ? 0 : 31);
                 segB = shfl_idx(B, REV ? 0 : 31);
@@ -908,12 +886,14 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
                             x_below = hstate[row];
                         }
                     }
-                    float4 pf;
-                    if constexpr (PREFIX_BYTES == 8) {
-                        const float2 h = *reinterpret_cast<const float2 *>(lane_prefix + (stage * 32 + lane) * 8);
-                        pf = make_float4(h.x, h.y, 1.0f, 0.0f);
+                    // the state entering this lane's first element
+                    V x;
+                    if constexpr (sizeof(V) == 4) {
+                        const float2 pf = *reinterpret_cast<const float2 *>(lane_prefix + (stage * 32 + lane) * PREFIX_BYTES);
+                        x = vfma(pf.x, x_in, pf.y);
                     } else {
-                        pf = *reinterpret_cast<const float4 *>(lane_prefix + (stage * 32 + lane) * 16);
+                        const float4 pf = *reinterpret_cast<const float4 *>(lane_prefix + (stage * 32 + lane) * PREFIX_BYTES);
+                        x = vfma(make_float2(pf.x, pf.y), x_in, make_float2(pf.z, pf.w));
                     }
                     if constexpr (STAGED) {
                         // the tile is in registers: its stage takes the matching tile of the segment
@@ -922,31 +902,11 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
                         fence_async_smem();
                         if (i < aft_nt) issue(aft.d, cur_slot, i);
                     }
-                    if constexpr (PACKED) {
-                        auto J = [](int q) { return REV ? K - 1 - q : q; };
-                        const float x = fmaf(pf.x, x_in, pf.y);
-                        float2 Xv = make_float2(x, fmaf(pf.z, x, pf.w));       // states entering the two halves
 #pragma unroll
-                        for (int q = 0; q < H; ++q) {
-                            const float2 av = make_float2(a[J(q)], a[J(H + q)]);
-                            const float2 bv = make_float2(b[J(q)], b[J(H + q)]);
-                            Xv = __ffma2_rn(av, Xv, bv);
-                            b[J(q)] = Xv.x;
-                            b[J(H + q)] = Xv.y;
-                        }
-                    } else {
-                        V x;
-                        if constexpr (sizeof(V) == 4) {
-                            x = vfma(pf.x, x_in, pf.y);
-                        } else {
-                            x = vfma(make_float2(pf.x, pf.y), x_in, make_float2(pf.z, pf.w));
-                        }
-#pragma unroll
-                        for (int q = 0; q < K; ++q) {
-                            const int j = REV ? K - 1 - q : q;
-                            x = vfma(a[j], x, b[j]);
-                            b[j] = x;
-                        }
+                    for (int q = 0; q < K; ++q) {
+                        const int j = REV ? K - 1 - q : q;
+                        x = vfma(a[j], x, b[j]);
+                        b[j] = x;
                     }
                     if (BACK) {
                         // d_gates[t] = conj(x[t-1]) * g[t]

@@ -137,8 +137,8 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
             // of two resident segments (lb_warp_smem in lookback.cuh); 3072 bytes for the team.
             const int stage = nin_of(in.kind) * 32 * 3 * 16 + (in.kind == ASCAN_KIND_BACKWARD ? 128 : 0);
             const int staging = in.kind == ASCAN_KIND_BACKWARD ? 0 : 32 * 3 * 16;
-            // prefix maps: 16 bytes per stage and lane, 8 for the fused backward of the real types
-            const int prefix = (in.kind == ASCAN_KIND_BACKWARD && in.dtype != ASCAN_C64) ? 8 : 16;
+            // prefix maps: two values of the compute type per stage and lane
+            const int prefix = in.dtype != ASCAN_C64 ? 8 : 16;
             const int wsm = 2 * lb_tiles * stage + staging + 128 + 2 * lb_tiles * 32 * prefix;
             int64_t workers = (kMaxSmemPerCta - 3072) / wsm;
             if (workers > 15) workers = 15;
