@@ -50,6 +50,7 @@ namespace ascan {
 
 constexpr int LB_RECORD_BYTES = 32;          // one affine pair of the compute type in tagged 64-bit words
 constexpr int LB_MAX_TILES = 8;              // tiles per worker and segment, at most (a worker holds two segments: 2 stages per tile)
+constexpr uint32_t LB_SHARDED_GROUP_ROWS = 32;  // rows whose segments are interleaved in ticket order when time is sharded
 constexpr int LB_MAX_WORKERS = 15;           // worker warps per CTA, at most (plus the bookkeeper)
 constexpr int LB_TEAM_BYTES = 3072;          // shared memory of the team: parts, incoming states, mbarriers, part descriptors
 constexpr int MAX_WORLD = 16;                // ranks of a time-sharded scan, at most
@@ -433,21 +434,20 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
         g.valid = q < static_cast<uint32_t>(p.items);
         g.row = 0; g.pos0 = 0; g.n = 0; g.s = 0; g.nts = 0;
         if (!g.valid) return g;
-        if (sharded) {
-            // row-major: a row's slice is finished, and its aggregate on its way to the next rank,
-            // as early as possible
-            const uint32_t ss = static_cast<uint32_t>(S);
-            const uint32_t row = q / ss;
-            g.row = row;
-            g.s = static_cast<int32_t>(q - row * ss);
-        } else {
-            // segment-major: the segment before this one in its row was drawn `rows` tickets ago, so
-            // its aggregate (and those of all earlier ones) is out when this one's look-back asks
-            const uint32_t rr = static_cast<uint32_t>(p.rows);
-            const uint32_t sq = q / rr;
-            g.s = static_cast<int32_t>(sq);
-            g.row = q - sq * rr;
-        }
+        // Tickets run over groups of rows, segment-major inside a group: the segment before this one
+        // in its row was drawn a group's worth of tickets ago, so its aggregate (and those of all
+        // earlier ones) is out when this one's look-back asks.  Unsharded, all rows are one group.
+        // Sharded, a row's slice aggregate is due at the next rank as early as possible, and a
+        // row is finished only a group's worth of segments after it was begun: groups of 32 rows.
+        const uint32_t rows_u = static_cast<uint32_t>(p.rows), ss = static_cast<uint32_t>(S);
+        const uint32_t R = sharded ? (rows_u < LB_SHARDED_GROUP_ROWS ? rows_u : LB_SHARDED_GROUP_ROWS) : rows_u;
+        const uint32_t gi = q / (R * ss);
+        const uint32_t left_rows = rows_u - gi * R;
+        const uint32_t Rg = left_rows < R ? left_rows : R;
+        const uint32_t w = q - gi * R * ss;
+        const uint32_t sq = w / Rg;
+        g.s = static_cast<int32_t>(sq);
+        g.row = gi * R + (w - sq * Rg);
         const int64_t from_start = REV ? S - 1 - g.s : g.s;      // segments are aligned to the row start
         g.pos0 = from_start * L;
         const int64_t left = T - g.pos0;
