@@ -64,10 +64,10 @@ typedef enum {
  * of warp.cuh:282-380.  Pure host arithmetic, usable without a GPU when
  * sm_count > 0 is passed. */
 typedef struct {
-    int32_t kernel;            /* 0 = stream: one warp per item, segments of a row chained; 1 = look-back (very few rows, or rows sharded along time: short segments kept in shared memory and scanned concurrently, incoming states from segment aggregates); 2 = team (fewer than four rows per warp: several warps share an item) */
+    int32_t kernel;            /* 0 = stream: one warp per item, segments of a row chained; 1 = look-back (very few rows, or rows sharded along time: a CTA keeps a segment in shared memory, one part per worker warp, segments are scanned concurrently, incoming states come from segment aggregates; warps_per_cta counts the workers and the CTA's bookkeeper warp); 2 = team (fewer than four rows per warp: several warps share an item) */
     int32_t loader;            /* 0 = bulk-async copies into shared-memory stages, 1 = plain element loads (unaligned data) */
     int32_t chunks_per_lane;   /* 16-byte chunks each lane owns per tile                  */
-    int32_t stages;            /* shared-memory stages per warp (look-back: tiles per segment) */
+    int32_t stages;            /* shared-memory stages per warp (look-back: tiles per worker and segment) */
     int32_t warps_per_cta;
     int32_t grid;              /* persistent CTAs                                          */
     int32_t tile_elems;        /* elements per warp tile                                   */
@@ -304,7 +304,7 @@ int ascan_check(void *ws, void *stream);
 typedef enum {
     ASCAN_OPT_STAGES = 0,          /* shared-memory stages per warp, 1..8 (default 2)          */
     ASCAN_OPT_WARPS_PER_CTA = 1,   /* upper bound on warps per CTA, 0 = planner's choice       */
-    ASCAN_OPT_LOOKBACK_TILES = 2,  /* tiles per segment of the look-back plan                  */
+    ASCAN_OPT_LOOKBACK_TILES = 2,  /* tiles per worker and segment of the look-back plan      */
     ASCAN_OPT_DISABLE_PLANS = 3,   /* bit 0 no look-back, bit 1 no team, bit 2 static deal, bit 3 plain loader, bit 4 no row grid, bit 5 no four-chunk tiles */
     ASCAN_OPT_TEST_DROP_CARRY = 4, /* 1: drop one carry hand-over per launch (a wait expires)  */
     ASCAN_OPT_TEST_EPOCH_BITS = 5, /* width of the launch epoch, 1..17 (default 17)            */

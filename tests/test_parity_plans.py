@@ -163,3 +163,42 @@ def _lookback_case(cuda_device):
     assert rel_err(to_np(dx), want_dx) <= 1e-5
     assert rel_err(to_np(dg), want_dg) <= 1e-5
     _native.check_status(cuda_device)
+
+
+# Lengths around the boundaries of the look-back plan's decomposition (fp32: tiles of 384 steps,
+# parts of 2 tiles, segments of up to 15 parts forward and 11 backward): rows shorter than a
+# full team, exactly one segment, one step or one tile more, workers whose part is empty in
+# the last segment, a ragged last tile.  (Multiples of four steps: rows of whole 16-byte chunks.)
+LOOKBACK_LENGTHS = [1156, 1536, 1540, 2308, 4608, 8444, 8448, 8452, 11516, 11520, 11524, 11908, 16900, 23040, 23044, 34568]
+
+
+@pytest.mark.parametrize("rows", [1, 3])
+@pytest.mark.parametrize("T", LOOKBACK_LENGTHS)
+def test_lookback_segment_boundaries(cuda_device, rows, T):
+    """Forward, reversed forward, seeded forward and fused backward of the look-back plan against the CPU oracle."""
+    from accelerated_scan import _native
+
+    for kind in (_native.KIND_FORWARD, _native.KIND_BACKWARD):
+        pl = _native.plan(rows, T, _native.F32, kind)
+        assert pl["kernel"] == 1, pl
+        assert (pl["segs_per_row"] - 1) * pl["seg_elems"] < T <= pl["segs_per_row"] * pl["seg_elems"]
+    gates, tokens, grad_out = real_inputs(1000 + T, (1, rows, T), law="near_one")
+    seed = torch.linspace(-1.0, 1.0, rows)
+    want = scan_oracle.scan(gates.numpy(), tokens.numpy())
+    want_rev = scan_oracle.scan(gates.numpy(), tokens.numpy(), reverse=True)
+    # a scan started from a state is the plain scan plus the running product of the gates times that state
+    want_seeded = want + np.cumprod(gates.numpy().astype(np.float64), axis=-1) * seed.numpy().astype(np.float64).reshape(1, rows, 1)
+    want_dg, want_dx = scan_oracle.scan_backward(gates.numpy(), want, grad_out.numpy())
+    g, x, go = (t.to(cuda_device) for t in (gates, tokens, grad_out))
+    out = torch.empty_like(x)
+    _native.forward(g, x, out)
+    assert rel_err(to_np(out), want) <= 1e-5
+    dg, dx = torch.empty_like(x), torch.empty_like(x)
+    _native.backward(g, out, go, dg, dx)
+    assert rel_err(to_np(dx), want_dx) <= 1e-5
+    assert rel_err(to_np(dg), want_dg) <= 1e-5
+    _native.forward(g, x, out, reverse=True)
+    assert rel_err(to_np(out), want_rev) <= 1e-5
+    _native.forward(g, x, out, carry_in=seed.to(cuda_device))
+    assert rel_err(to_np(out), want_seeded) <= 1e-5
+    _native.check_status(cuda_device)
