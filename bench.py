@@ -567,15 +567,18 @@ TRAFFIC_BWD_BYTES_PER_ELEM = 9.86
 
 
 def run_also(torch, _native, dev):
-    """fwd+bwd of the same kernels for fp32 (8,1536,65536) and complex64 (4,1024,16384), and of
-    the sigmoid-gate variant in bf16; inputs resident, every tensor larger than L2, 10 timed
-    steps after warm-up."""
+    """fwd+bwd of the same kernels for fp32 (8,1536,65536) and complex64 (4,1024,16384), of the
+    look-back plan on (1,64,1048576) and (1,1,16777216) fp32, and of the sigmoid-gate variant in
+    bf16; inputs resident, 10 timed steps after warm-up (tensors of 64 MB and more: between two
+    launches of a kind the other kind's tensors pass through L2)."""
     import math
 
     peak, _ = measured_peak()
     results = []
     for name, shape, dt in (("fp32 (8,1536,65536)", (B, C, 65536), torch.float32),
-                            ("complex64 (4,1024,16384)", (4, 1024, 16384), torch.complex64)):
+                            ("complex64 (4,1024,16384)", (4, 1024, 16384), torch.complex64),
+                            ("fp32 (1,64,1048576), fewer rows than SMs: look-back plan", (1, 64, 1 << 20), torch.float32),
+                            ("fp32 (1,1,16777216), one row: look-back plan", (1, 1, 1 << 24), torch.float32)):
         gen = torch.Generator(device=dev).manual_seed(4321)
         if dt == torch.complex64:
             r = 0.9 + 0.099 * torch.rand(*shape, device=dev, generator=gen)
