@@ -1,10 +1,12 @@
 // Look-back scan kernel: single pass, for matrices with clearly fewer rows than SMs and for
 // rows whose time axis is sharded over several GPUs.
 //
-// A row is cut into SEGMENTS; an item is one segment, items are numbered row-major (all
-// segments of row 0 in processing order, then row 1, ...) and drawn from the ticket counter
-// by persistent CTAs, so the segments of a handful of rows are in flight at any time, spread
-// over every SM.
+// A row is cut into SEGMENTS; an item is one segment, drawn from the ticket counter by
+// persistent CTAs, so segments of many rows are in flight at any time, spread over every SM.
+// Tickets run over groups of rows, segment-major inside a group (all rows' first segments in
+// processing order, then all second ones, ...): when a segment is drawn, the one before it in
+// its row was drawn a group's worth of tickets earlier and its aggregate is published by the
+// time it is asked for.
 //
 // A CTA works on a segment as a team.  Its G worker warps each take NT consecutive tiles of
 // the segment (a segment is G * NT tiles) and keep them in shared memory; the last warp of
@@ -50,7 +52,7 @@ namespace ascan {
 
 constexpr int LB_RECORD_BYTES = 32;          // one affine pair of the compute type in tagged 64-bit words
 constexpr int LB_MAX_TILES = 8;              // tiles per worker and segment, at most (a worker holds two segments: 2 stages per tile)
-constexpr uint32_t LB_SHARDED_GROUP_ROWS = 16;  // rows whose segments are interleaved in ticket order when time is sharded
+constexpr uint32_t LB_SHARDED_GROUP_ROWS = 16;  // rows whose segments are interleaved in ticket order when time is sharded (half as many from eight ranks on)
 constexpr int LB_MAX_WORKERS = 15;           // worker warps per CTA, at most (plus the bookkeeper)
 constexpr int LB_TEAM_BYTES = 3072;          // shared memory of the team: parts, incoming states, mbarriers, part descriptors
 constexpr int MAX_WORLD = 16;                // ranks of a time-sharded scan, at most
@@ -149,11 +151,20 @@ __device__ __forceinline__ bool get_pair(const unsigned char *rec, uint32_t tag,
 // lane holds (A, B) with  x -> A*x + B  = record n-1 after ... after record 0.  Lane i reads
 // record i and polls until it carries `tag`; false when the bound expires.  The combine is a
 // Kogge-Stone scan over the lanes with identity in the unused lanes: a fixed tree.
+// `ahead` (real types, optional): this lane's two words loaded ahead of time; used if they carry
+// the tag already.
 template <class V, bool SYS>
 __device__ __forceinline__ bool compose_window(const unsigned char *base, int64_t stride, int n, uint32_t tag, int lane,
-                                               V &A, V &B) {
+                                               V &A, V &B, const uint64_t *ahead = nullptr) {
     V a = vone(V()), b = vzero(V());
     bool ok = lane >= n;
+    if constexpr (sizeof(V) == 4) {
+        if (ahead && !ok && static_cast<uint32_t>(ahead[0] >> 32) == tag && static_cast<uint32_t>(ahead[1] >> 32) == tag) {
+            a = __uint_as_float(static_cast<uint32_t>(ahead[0]));
+            b = __uint_as_float(static_cast<uint32_t>(ahead[1]));
+            ok = true;
+        }
+    }
     bool all = false;
     for (uint32_t poll = 0; poll < LB_WAIT_POLLS; ++poll) {
         if (!ok) ok = get_pair<SYS>(base + lane * stride, tag, a, b);
@@ -438,9 +449,13 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
         // in its row was drawn a group's worth of tickets ago, so its aggregate (and those of all
         // earlier ones) is out when this one's look-back asks.  Unsharded, all rows are one group.
         // Sharded, a row's slice aggregate is due at the next rank as early as possible, and a
-        // row is finished only a group's worth of segments after it was begun: groups of 16 rows (measured on 1024 rows: 8 rows already give the look-back enough time, 16 a few percent more).
+        // row is finished only a group's worth of segments after it was begun: groups of 16 rows,
+        // 8 from eight ranks on, where every microsecond of lag per rank boundary is paid fourteen
+        // times per step (measured on 1024 rows, a rank's slice of eight, forward / backward TB/s:
+        // row-major 5.1 / 4.8, groups of 8 rows 5.5 / 5.3, 16 rows 5.5 / 5.4, 64 rows 5.6 / 5.5).
         const uint32_t rows_u = static_cast<uint32_t>(p.rows), ss = static_cast<uint32_t>(S);
-        const uint32_t R = sharded ? (rows_u < LB_SHARDED_GROUP_ROWS ? rows_u : LB_SHARDED_GROUP_ROWS) : rows_u;
+        const uint32_t group = sp.world >= 8 ? LB_SHARDED_GROUP_ROWS / 2 : LB_SHARDED_GROUP_ROWS;
+        const uint32_t R = sharded ? (rows_u < group ? rows_u : group) : rows_u;
         const uint32_t gi = q / (R * ss);
         const uint32_t left_rows = rows_u - gi * R;
         const uint32_t Rg = left_rows < R ? left_rows : R;
@@ -1005,6 +1020,13 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
         RecordWords ahead;
         for (int w = 0; w < 6; ++w) ahead.w[w] = 0;
         bool have_ahead = false;
+        uint64_t xahead[2] = {0, 0};                  // time sharding: the earlier ranks' slice aggregates of the next segment's row
+        // lane i reads the aggregate of the i-th rank in processing order
+        const int xfirst = REV ? sp.world - 1 : 0;
+        const int64_t xstep = (REV ? -1 : 1) * static_cast<int64_t>(p.rows) * LB_RECORD_BYTES;
+        auto xbase = [&](int64_t row) -> const unsigned char * {
+            return xl + xchg_carry_offset(p.rows) + ((static_cast<uint64_t>(parity_slot) * sp.world + xfirst) * p.rows + row) * LB_RECORD_BYTES;
+        };
         for (uint32_t k = 0; q_cur != LB_NO_ITEM && !failed; ++k) {
             const SegDesc sg = describe_seg(q_cur);
             const int b = static_cast<int>(k & 1u);
@@ -1030,13 +1052,8 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
             // state entering the slice: the caller's, or the fold of the earlier ranks' aggregates
             V x_slice = cin ? cin[row] : vzero(V());
             if (n_before > 0 && lb_ok) {
-                // lane i reads the aggregate of the i-th rank in processing order
-                const int first = REV ? sp.world - 1 : 0;
-                const int64_t step = (REV ? -1 : 1) * static_cast<int64_t>(p.rows) * LB_RECORD_BYTES;
-                const unsigned char *base = xl + xchg_carry_offset(p.rows) +
-                                            ((static_cast<uint64_t>(parity_slot) * sp.world + first) * p.rows + row) * LB_RECORD_BYTES;
                 V Ar, Br;
-                lb_ok = compose_window<V, true>(base, step, n_before, sp.call, lane, Ar, Br);
+                lb_ok = compose_window<V, true>(xbase(row), xstep, n_before, sp.call, lane, Ar, Br, have_ahead ? xahead : nullptr);
                 x_slice = vfma(Ar, x_slice, Br);
             }
             // forward: the state entering the slice is what the backward needs below its first step
@@ -1063,6 +1080,11 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
                 if (q_nxt != LB_NO_ITEM) {
                     const SegDesc sx = describe_seg(q_nxt);
                     ahead = load_ahead(records + static_cast<uint64_t>(sx.row) * per_row * LB_RECORD_BYTES, sx.s);
+                    if (lane < n_before) {
+                        const unsigned char *xb = xbase(sx.row) + lane * xstep;
+                        xahead[0] = ld_relaxed_sys_u64(xb);
+                        xahead[1] = ld_relaxed_sys_u64(xb + 8);
+                    }
                     have_ahead = true;
                 }
             }
