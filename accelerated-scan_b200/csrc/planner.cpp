@@ -125,9 +125,11 @@ int make_plan(const PlanInput &in, ascan_plan *plan) {
     {
         int lb_tiles = in.tune.lookback_tiles > 0 ? in.tune.lookback_tiles : 2;
         if (lb_tiles > 8) lb_tiles = 8;
-        // below three rows per four SMs (measured on 148 SMs: at 96 rows look-back and teams of 12
-        // warps tie, at 128 rows the teams win by 10-20 %)
-        const int64_t lookback_rows = in.sm_count * 3 / 4;
+        // The fused backward: below three rows per four SMs (measured on 148 SMs, fp32, 268 MB per
+        // tensor: at 128 rows teams of 12 warps run at 5.9 TB/s, look-back at 5.5).  The forward:
+        // below three rows per two SMs (teams / look-back at 128 rows 4.2 / 5.4 TB/s, 147 rows
+        // 4.7 / 5.4, 200 rows 5.2 / 5.4, 296 rows 5.9 / 5.4; bf16 the same way).
+        const int64_t lookback_rows = in.kind == ASCAN_KIND_FORWARD ? in.sm_count * 3 / 2 : in.sm_count * 3 / 4;
         const int64_t te3 = 32 * 3 * (16 / esize);
         const int64_t tiles_row3 = (in.seqlen + te3 - 1) / te3;
         const bool possible = can_split && bulk && scan_kind && in.rows > 0 && (in.tune.disable_plans & 1) == 0;

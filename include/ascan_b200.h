@@ -259,7 +259,7 @@ int ascan_peer_free(void *ptr);
  * Scratch bytes a call of `kind` with these sizes can use: a control block
  * (status word, work ticket) plus one carry record per row, or 32 bytes per segment,
  * block of 32 segments and super-block when the look-back plan applies (clearly fewer
- * rows than SMs).  With that much scratch
+ * rows than SMs: 3/4 of them, 3/2 for the forward kind).  With that much scratch
  * the kernels balance work over the SMs dynamically and split long rows across
  * warps and CTAs; with less they step down to the chained plan (256 + 32*rows
  * bytes), and with none (NULL) to a static deal of whole rows: correct, slower.

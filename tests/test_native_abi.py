@@ -70,7 +70,7 @@ def test_planner_invariants(T, dtype, kind):
             # look-back plan: fewer rows than 3/4 of the SMs; a CTA is a team of workers plus a bookkeeper, a
             # segment is one part of `stages` tiles per worker; 32-byte records per segment, block of 32
             # segments and super-block of 32 blocks
-            assert rows < 111 and kind in (0, 1)
+            assert rows < (222 if kind == 0 else 111) and kind in (0, 1)
             workers = pl["warps_per_cta"] - 1
             assert 1 <= workers <= 15 and pl["grid"] == min(148, pl["items"])
             segs = pl["segs_per_row"]
