@@ -128,6 +128,39 @@ def test_planner_invariants(T, dtype, kind):
         assert static["dynamic"] == 0 and static["segs_per_row"] == 1 and static["workspace_bytes"] == 0
 
 
+@pytest.mark.parametrize("dtype", [0, 1, 3])
+@pytest.mark.parametrize("kind", [0, 1])
+def test_lookback_plan_decomposition(dtype, kind):
+    """The look-back plan over row counts and lengths: rows are cut into segments of equal size, one part of `stages`
+    tiles per worker warp, no more workers than a row has parts and than shared memory holds, one CTA per segment
+    in flight at most, and the scratch that the plan asks for matches its records."""
+    esize = {0: 4, 1: 2, 3: 8}[dtype]
+    tile = 32 * 3 * (16 // esize)
+    # bytes per worker: its tiles of two resident segments (inputs, and 128 bytes of halo per stage in the backward),
+    # a staging tile (forward), mbarriers, prefix maps of two compute-type values per stage and lane
+    nin = 3 if kind == 1 else 2
+    stage = nin * 32 * 3 * 16 + (128 if kind == 1 else 0)
+    prefix = 16 if dtype == 3 else 8
+    per_worker = 2 * 2 * stage + (0 if kind == 1 else 32 * 3 * 16) + 128 + 2 * 2 * 32 * prefix
+    max_workers = min(15, (227 * 1024 - 3072) // per_worker)
+    for rows in (1, 2, 7, 64, 110):
+        for tiles in (4, 5, 29, 30, 31, 60, 61, 342, 1366, 2731, 43691):
+            for ragged in (0, 16 // esize):
+                T = tiles * tile - ragged
+                pl = _native.plan(rows, T, dtype, kind, aligned=True, sm_count=148)
+                assert pl["kernel"] == 1, (rows, T, pl)
+                workers = pl["warps_per_cta"] - 1
+                segs = pl["segs_per_row"]
+                parts = (tiles + 1) // 2
+                assert 1 <= workers <= max_workers
+                assert segs == -(-parts // max_workers) and workers == -(-parts // segs)
+                assert pl["seg_elems"] == workers * 2 * tile and (segs - 1) * pl["seg_elems"] < T <= segs * pl["seg_elems"]
+                assert pl["smem_bytes"] == workers * per_worker + 3072 <= 227 * 1024
+                assert pl["items"] == rows * segs and pl["grid"] == min(148, pl["items"])
+                blocks = (segs + 31) // 32
+                assert pl["workspace_bytes"] == 256 + 32 * rows * (segs + blocks + (blocks + 31) // 32)
+
+
 def test_planner_rejects_bad_input():
     pl = _native.Plan()
     assert _native.lib.ascan_plan_describe(4, 0, 0, 0, 1, 148, ctypes.byref(pl)) == 1
