@@ -346,6 +346,12 @@ __device__ __forceinline__ void bulk_s2g_hint(void *dst_gmem, const void *src_sm
                  : "memory");
 }
 
+// Asks for a range of global memory to be brought into L2 (a hint: no completion to wait for).
+// Address 16-byte aligned, size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_prefetch_l2(const void *src_gmem, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src_gmem), "r"(bytes) : "memory");
+}
+
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 
 // Waits until at most N committed bulk groups still have to READ their shared source.

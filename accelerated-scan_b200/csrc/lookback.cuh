@@ -1006,6 +1006,10 @@ __global__ void __launch_bounds__(512, 1) lookback_kernel(const StreamParams p, 
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&dr[k & 3u]);
+            // the segment's inputs on their way into L2 already: the workers ask for their tiles a
+            // scan pass later and need them right after it
+            if (sg.valid && lane < NIN)
+                bulk_prefetch_l2(gbase[lane] + (sg.row * T + sg.pos0) * TR::ESIZE, static_cast<uint32_t>(sg.n * TR::ESIZE));
         };
         uint32_t q_cur = draw();
         if (q_cur >= static_cast<uint32_t>(p.items)) q_cur = LB_NO_ITEM;
